@@ -249,6 +249,21 @@ class Group:
 
         return self.submit(name, job, None, nbytes, async_op)
 
+    def empty(self, numel, dtype, device=None, zero=True):
+        """A flat tensor for communication buffers.  On GPU ranks it comes from
+        the symmetric heap (mapped by every peer), which makes collectives on it
+        zero-copy; every rank must make the same sequence of empty()/release()
+        calls.  Elsewhere it is an ordinary tensor."""
+        device = torch.device(device) if device is not None else self.device
+        if self._sym is not None and device.type == "cuda":
+            return self._sym.alloc(numel, dtype, zero)
+        return (torch.zeros if zero else torch.empty)(numel, dtype=dtype, device=device)
+
+    def release(self, t):
+        """Returns a tensor from empty() to the symmetric heap."""
+        if self._sym is not None and t.is_cuda:
+            self._sym.free(t)
+
     def check(self):
         """Raises CommError if a GPU collective gave up waiting for a peer."""
         if self._sym is not None:

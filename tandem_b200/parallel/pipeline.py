@@ -1,0 +1,149 @@
+"""Pipeline parallelism: contiguous runs of model.units() become stages, one per
+rank; a batch is cut into micro-batches whose activations flow forward and
+whose gradients flow back.
+
+Schedules (same contract as the reference's tandem/pipeline.py:35-166):
+  gpipe  all forwards, then all backwards (Huang et al., 2019).
+  1f1b   (stages - rank - 1) warm-up forwards, then one forward / one backward
+         alternately, then drain (PipeDream-Flush, Megatron-LM).  Steady-state
+         transfers are paired (send one tensor while receiving the other), so
+         neighbouring stages never wait on each other.
+Backwards run in micro-batch order on every stage, so gradients accumulate as in
+one process accumulating over the same micro-batches.
+
+The schedule is written once as a list of actions per stage (`plan`); running it
+is a small interpreter.  On GPU ranks the transfers are NCCL send/recv pairs and
+activations travel in the model's compute dtype.
+"""
+
+import torch
+
+from ..models.gpt import loss_fn
+from ..utils.profile import Timeline
+
+
+def split_units(n_units, stages):
+    """Contiguous (lo, hi) ranges of units, one per stage, as even as possible."""
+    base, extra = divmod(n_units, stages)
+    out, lo = [], 0
+    for s in range(stages):
+        hi = lo + base + (1 if s < extra else 0)
+        out.append((lo, hi))
+        lo = hi
+    return out
+
+
+def plan(schedule, stages, rank, m):
+    """The stage's step as a list of actions:
+      ("F", i) / ("B", i)          compute micro-batch i forward / backward
+      ("recv_act",) ("send_act",) ("recv_grad",) ("send_grad",)
+      ("send_act_recv_grad",) ("send_grad_recv_act",)   paired transfers
+    Transfers that do not exist at the first / last stage are left out by the runner."""
+    acts = []
+    if schedule == "gpipe":
+        for i in range(m):
+            acts += [("recv_act",), ("F", i), ("send_act",)]
+        for i in range(m):
+            acts += [("recv_grad",), ("B", i), ("send_grad",)]
+        return acts
+    if schedule != "1f1b":
+        raise ValueError(f"unknown schedule {schedule}")
+    warm = min(stages - rank - 1, m)
+    steady = m - warm
+    for i in range(warm):
+        acts += [("recv_act",), ("F", i), ("send_act",)]
+    if steady > 0:
+        acts.append(("recv_act",))
+    for k in range(steady):
+        acts += [("F", warm + k), ("send_act_recv_grad",), ("B", k)]
+        acts.append(("send_grad",) if k == steady - 1 else ("send_grad_recv_act",))
+    for k in range(steady, m):
+        acts += [("recv_grad",), ("B", k), ("send_grad",)]
+    return acts
+
+
+class Pipeline:
+    def __init__(self, model, group, micro_batches, schedule="1f1b", timeline=None):
+        if schedule not in ("gpipe", "1f1b"):
+            raise ValueError(f"unknown schedule {schedule}")
+        self.g, self.m, self.schedule = group, micro_batches, schedule
+        units = model.units()
+        lo, hi = split_units(len(units), group.size)[group.rank]
+        self.units = torch.nn.ModuleList(units[lo:hi])
+        self.first, self.last = group.rank == 0, group.rank == group.size - 1
+        self.dim = model.config.dim
+        self.kernels = getattr(model.config, "kernels", "torch")
+        self.timeline = timeline or Timeline(enabled=False)
+        self.act_dtype = None  # None: the dtype of this stage's parameters
+
+    def parameters(self):
+        return self.units.parameters()
+
+    def _run_units(self, x):
+        for u in self.units:
+            x = u(x)
+        return x
+
+    def train_step(self, x, y):
+        """Forward and backward over the global batch (x, y), which every rank
+        passes (stage 0 reads x, the last stage reads y).  Gradients accumulate
+        in this stage's parameters.  Returns the mean loss on the last stage,
+        None elsewhere."""
+        xs, ys = x.chunk(self.m), y.chunk(self.m)
+        if len(xs) != self.m or any(c.shape[0] != xs[0].shape[0] for c in xs):
+            raise ValueError("the batch must divide evenly into micro-batches")
+        first_param = next(self.parameters())
+        dev = first_param.device
+        dtype = self.act_dtype or (torch.get_autocast_dtype(dev.type) if torch.is_autocast_enabled(dev.type)
+                                   else first_param.dtype)
+        shape = (xs[0].shape[0], xs[0].shape[1], self.dim)
+        g, up, down = self.g, self.g.rank - 1, self.g.rank + 1
+        saved, losses = {}, []
+        act = grad = out = None
+
+        def fresh():
+            return torch.empty(shape, device=dev, dtype=dtype)
+
+        for a in plan(self.schedule, g.size, g.rank, self.m):
+            kind = a[0]
+            if kind == "F":
+                i = a[1]
+                with self.timeline.span(f"F{i}"):
+                    inp = xs[i].to(dev) if self.first else act.requires_grad_()
+                    out = self._run_units(inp)
+                    if self.last:
+                        out = loss_fn(out, ys[i].to(dev), self.kernels) / self.m
+                        losses.append(out.detach())
+                    saved[i] = (inp, out)
+            elif kind == "B":
+                i = a[1]
+                with self.timeline.span(f"B{i}"):
+                    inp, res = saved.pop(i)
+                    if self.last:
+                        res.backward()
+                    else:
+                        res.backward(grad)
+                    grad = None if self.first else inp.grad
+            elif kind == "recv_act":
+                if not self.first:
+                    act = fresh()
+                    g.recv(act, up)
+            elif kind == "send_act":
+                if not self.last:
+                    g.send(out.detach().contiguous(), down)
+            elif kind == "recv_grad":
+                if not self.last:
+                    grad = fresh()
+                    g.recv(grad, down)
+            elif kind == "send_grad":
+                if not self.first:
+                    g.send(grad.contiguous(), up)
+            elif kind == "send_act_recv_grad":
+                if not self.last:
+                    grad = fresh()
+                    g.sendrecv(out.detach().contiguous(), down, grad, down)
+            elif kind == "send_grad_recv_act":
+                if not self.first:
+                    act = fresh()
+                    g.sendrecv(grad.contiguous(), up, act, up)
+        return sum(losses) if self.last else None

@@ -1,0 +1,356 @@
+"""ZeRO stages 1-3: data parallelism that shards optimizer state, then gradients,
+then parameters (Rajbhandari et al., 2020).
+
+Contract and flat layouts follow the reference's tandem/zero.py:29-336:
+  ZeRO(stage=1|2)  all parameters are views of one flat buffer in
+                   module.parameters() order; rank r owns chunk r of
+                   torch.tensor_split(numel, world).  Stage 1 all-reduces bucket
+                   slices of a full flat gradient; stage 2 reduce-scatters each
+                   bucket with per-rank sizes = the overlap of the bucket's range
+                   with each shard (often zero) and keeps only a shard of the
+                   gradient.  step() = sharded AdamW + all-gather of the buffer.
+  FSDP             the same per unit of model.units(): a unit's full parameters
+                   exist only around its forward and its backward; the next
+                   unit's gather is started early; a unit's gradients are
+                   reduce-scattered as soon as they are complete.
+Train with: loss = z(x, y); loss.backward(); z.step(); z.zero_grad().
+
+Underneath, on GPUs, the flat buffers, gradient staging and unit shards live in
+the group's symmetric heap, so reduce-scatter / all-gather are single kernels
+that read or write the peers' copies in place, with the divide fused in.
+"""
+
+import warnings
+
+import torch
+from torch.autograd import Variable
+
+from .optim import ShardedAdamW
+
+
+def split_sizes(numel, world):
+    """Chunk lengths of torch.tensor_split(numel, world)."""
+    base, extra = divmod(numel, world)
+    return [base + (1 if r < extra else 0) for r in range(world)]
+
+
+class FlatLayout:
+    """Offsets of parameters inside one flat buffer, and the rank shards of it."""
+
+    def __init__(self, params, world, rank):
+        self.params = params
+        self.offset, at = {}, 0
+        for p in params:
+            self.offset[p] = at
+            at += p.numel()
+        self.numel = at
+        self.sizes = split_sizes(at, world)
+        self.lo = sum(self.sizes[:rank])
+        self.hi = self.lo + self.sizes[rank]
+
+    def span(self, p):
+        return self.offset[p], self.offset[p] + p.numel()
+
+    def bucket_sizes(self, a, b):
+        """How many elements of the flat range [a, b) fall in each rank's shard."""
+        out, lo = [], 0
+        for s in self.sizes:
+            out.append(max(0, min(b, lo + s) - max(a, lo)))
+            lo += s
+        return out
+
+
+class _Range:
+    """A contiguous run of parameters reduced together."""
+
+    def __init__(self, params, a, b):
+        self.params, self.a, self.b = params, a, b
+        self.ready = 0
+        self.work = None
+        self.staging = None
+
+
+def _flatten_into(buf, layout):
+    for p in layout.params:
+        a, b = layout.span(p)
+        buf[a:b].copy_(p.detach().reshape(-1))
+
+
+def _point_into(buf, layout):
+    for p in layout.params:
+        a, b = layout.span(p)
+        p.data = buf[a:b].view_as(p)
+
+
+class ZeRO(torch.nn.Module):
+    """Stages 1 and 2."""
+
+    def __init__(self, module, group, stage=1, optimizer=None, bucket_bytes=25 << 20):
+        super().__init__()
+        if stage not in (1, 2):
+            raise ValueError("ZeRO handles stages 1 and 2; stage 3 is FSDP")
+        self.module, self.g, self.stage = module, group, stage
+        self.opt = optimizer or ShardedAdamW()
+        params = [p for p in module.parameters() if p.requires_grad]
+        dev, dtype = params[0].device, params[0].dtype
+        if any(p.dtype != dtype or p.device != dev for p in params):
+            raise ValueError("ZeRO needs all parameters on one device with one dtype")
+        self.flat = FlatLayout(params, group.size, group.rank)
+        self.buf = group.empty(self.flat.numel, dtype, dev)
+        with torch.no_grad():
+            _flatten_into(self.buf, self.flat)
+            group.broadcast(self.buf, root=0)
+            _point_into(self.buf, self.flat)
+        if stage == 1:
+            self.grad = group.empty(self.flat.numel, dtype, dev)
+        else:
+            self.grad_shard = torch.zeros(self.flat.hi - self.flat.lo, device=dev, dtype=dtype)
+        # Ranges run from the end of the buffer, the order backward produces gradients in.
+        self.buckets, self.bucket_of = [], {}
+        run, size = [], 0
+        for p in reversed(params):
+            nbytes = p.numel() * p.element_size()
+            if run and size + nbytes > bucket_bytes:
+                self._close(run)
+                run, size = [], 0
+            run.append(p)
+            size += nbytes
+        if run:
+            self._close(run)
+        self._next = 0
+        self._queued = False
+        for p in params:
+            p.register_post_accumulate_grad_hook(self._on_grad)
+
+    def _close(self, params):
+        a = min(self.flat.offset[p] for p in params)
+        b = max(self.flat.offset[p] + p.numel() for p in params)
+        r = _Range(params, a, b)
+        for p in params:
+            self.bucket_of[p] = r
+        self.buckets.append(r)
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+    def _on_grad(self, p):
+        r = self.bucket_of[p]
+        a, b = self.flat.span(p)
+        if self.stage == 1:
+            view = self.grad[a:b].view_as(p)
+            if p.grad is not view:
+                view.copy_(p.grad)
+                p.grad = view
+        else:
+            if r.staging is None:
+                r.staging = self.g.empty(r.b - r.a, p.dtype, p.device, zero=False)
+            r.staging[a - r.a:b - r.a].copy_(p.grad.reshape(-1))
+            p.grad = None  # the full-size gradient is not kept
+        if not self._queued:
+            self._queued = True
+            Variable._execution_engine.queue_callback(self._finish_backward)
+        r.ready += 1
+        while self._next < len(self.buckets) and self.buckets[self._next].ready == len(self.buckets[self._next].params):
+            nxt = self.buckets[self._next]
+            if self.stage == 1:
+                nxt.work = self.g.all_reduce(self.grad[nxt.a:nxt.b], op="avg", async_op=True)
+            else:
+                nxt.work = self.g.reduce_scatter(nxt.staging, self.flat.bucket_sizes(nxt.a, nxt.b), op="avg",
+                                                 async_op=True)
+            self._next += 1
+
+    def _finish_backward(self):
+        self._queued = False
+        incomplete = any(r.ready != len(r.params) for r in self.buckets)
+        for r in self.buckets:
+            if r.work is not None:
+                mine = r.work.wait()
+                if self.stage == 2 and mine.numel():
+                    at = max(r.a, self.flat.lo) - self.flat.lo
+                    self.grad_shard[at:at + mine.numel()].add_(mine)
+            if self.stage == 2 and r.staging is not None:
+                self.g.release(r.staging)
+                r.staging = None
+            r.ready, r.work = 0, None
+        self._next = 0
+        if incomplete:
+            raise RuntimeError("tandem_b200 ZeRO: every parameter must receive a gradient")
+
+    @torch.no_grad()
+    def step(self):
+        lo, hi = self.flat.lo, self.flat.hi
+        grad = self.grad[lo:hi] if self.stage == 1 else self.grad_shard
+        self.opt.update("flat", self.buf[lo:hi], grad)
+        self.g.all_gather(self.buf, self.flat.sizes)
+
+    def zero_grad(self):
+        if self.stage == 1:
+            for p in self.flat.params:
+                p.grad = None
+        else:
+            self.grad_shard.zero_()
+
+
+class _Unit:
+    def __init__(self, index, module, params, group, device, dtype):
+        self.index, self.module = index, module
+        self.flat = FlatLayout(params, group.size, group.rank)
+        self.full = torch.empty(self.flat.numel, device=device, dtype=dtype)
+        self.nbytes = self.full.untyped_storage().nbytes()
+        self.shard = None
+        self.grad_shard = torch.zeros(self.flat.hi - self.flat.lo, device=device, dtype=dtype)
+        self.gathered = True
+        self.pending = None  # all-gather in flight
+        self.ready = 0
+        self.rs = None  # reduce-scatter in flight
+        self.staging = None
+
+
+class FSDP(torch.nn.Module):
+    """ZeRO stage 3 over model.units() (for the GPT: embedding, each block, head)."""
+
+    def __init__(self, model, group, optimizer=None, prefetch=True):
+        super().__init__()
+        self.module, self.g = model, group
+        self.opt = optimizer or ShardedAdamW()
+        self.prefetch = prefetch
+        # The embedding's input needs no gradient, so torch warns that its full
+        # backward hook fires on the outputs -- which is when we want it.
+        warnings.filterwarnings("ignore", message="Full backward hook is firing when gradients are computed with respect to module outputs")
+        self.live = 0  # units whose full parameters exist right now
+        self.max_live = 0
+        self.units, self.unit_of = [], {}
+        taken = set()
+        for i, m in enumerate(model.units()):
+            ps = [p for p in m.parameters() if p.requires_grad and id(p) not in taken]
+            taken.update(id(p) for p in ps)
+            if not ps:
+                raise ValueError(f"unit {i} has no parameters of its own")
+            u = _Unit(i, m, ps, group, ps[0].device, ps[0].dtype)
+            with torch.no_grad():
+                _flatten_into(u.full, u.flat)
+                group.broadcast(u.full, root=0)
+                _point_into(u.full, u.flat)
+                u.shard = group.empty(u.flat.hi - u.flat.lo, u.full.dtype, u.full.device, zero=False)
+                u.shard.copy_(u.full[u.flat.lo:u.flat.hi])
+            for p in ps:
+                self.unit_of[p] = u
+                p.register_post_accumulate_grad_hook(self._on_grad)
+            m.register_forward_pre_hook(self._before_forward(u))
+            m.register_forward_hook(self._after_forward(u))
+            m.register_full_backward_pre_hook(self._before_backward(u))
+            self.live += 1
+            self._free(u)
+            self.units.append(u)
+        if len(taken) != sum(1 for p in model.parameters() if p.requires_grad):
+            raise ValueError("every parameter must belong to one of model.units()")
+        self._queued = False
+        self.max_live = 0
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+    # ---- a unit's full parameters: gather, wait, free
+    def _start_gather(self, u):
+        if u.gathered or u.pending is not None:
+            return
+        u.full.untyped_storage().resize_(u.nbytes)
+        self.live += 1
+        self.max_live = max(self.max_live, self.live)
+        u.full[u.flat.lo:u.flat.hi].copy_(u.shard)
+        u.pending = self.g.all_gather(u.full, u.flat.sizes, async_op=True)
+
+    def _gather(self, u):
+        self._start_gather(u)
+        if u.pending is not None:
+            u.pending.wait()
+            u.pending = None
+            u.gathered = True
+
+    def _free(self, u):
+        if u.pending is not None:
+            u.pending.wait()
+            u.pending = None
+        if u.full.untyped_storage().nbytes():
+            self.live -= 1
+        u.full.untyped_storage().resize_(0)
+        u.gathered = False
+
+    # ---- hooks
+    def _before_forward(self, u):
+        def hook(mod, args):
+            self._gather(u)
+            if self.prefetch and u.index + 1 < len(self.units):
+                self._start_gather(self.units[u.index + 1])
+
+        return hook
+
+    def _after_forward(self, u):
+        def hook(mod, args, out):
+            if torch.is_grad_enabled() and u.index == len(self.units) - 1:
+                return  # the last unit's backward comes first: keep it
+            self._free(u)
+
+        return hook
+
+    def _before_backward(self, u):
+        def hook(mod, grad_out):
+            if not self._queued:
+                self._queued = True
+                Variable._execution_engine.queue_callback(self._finish_backward)
+            self._gather(u)
+            if self.prefetch and u.index > 0:
+                self._start_gather(self.units[u.index - 1])
+
+        return hook
+
+    def _on_grad(self, p):
+        u = self.unit_of[p]
+        if u.staging is None:
+            u.staging = self.g.empty(u.flat.numel, p.dtype, p.device, zero=False)
+        a, b = u.flat.span(p)
+        u.staging[a:b].copy_(p.grad.reshape(-1))
+        p.grad = None
+        u.ready += 1
+        if u.ready == len(u.flat.params):
+            # Backward through the unit is over: drop its parameters, ship its gradients.
+            self._free(u)
+            u.rs = self.g.reduce_scatter(u.staging, u.flat.sizes, op="avg", async_op=True)
+
+    def _finish_backward(self):
+        self._queued = False
+        incomplete = False
+        for u in self.units:
+            if u.ready != len(u.flat.params):
+                incomplete = True
+            if u.rs is not None:
+                mine = u.rs.wait()
+                if mine.numel():
+                    u.grad_shard.add_(mine)
+            if u.staging is not None:
+                self.g.release(u.staging)
+            u.rs, u.staging, u.ready = None, None, 0
+            if u.gathered:
+                self._free(u)
+        if incomplete:
+            raise RuntimeError("tandem_b200 FSDP: every parameter must receive a gradient")
+
+    @torch.no_grad()
+    def step(self):
+        for u in self.units:
+            self.opt.update(u.index, u.shard, u.grad_shard)
+
+    def zero_grad(self):
+        for u in self.units:
+            u.grad_shard.zero_()
+
+    @torch.no_grad()
+    def full_parameters(self):
+        """All parameters gathered into one flat tensor, in units() order (for checkpoints and tests)."""
+        out = []
+        for u in self.units:
+            full = torch.empty(u.flat.numel, device=u.shard.device, dtype=u.shard.dtype)
+            full[u.flat.lo:u.flat.hi].copy_(u.shard)
+            self.g.all_gather(full, u.flat.sizes)
+            out.append(full)
+        return torch.cat(out)
