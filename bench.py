@@ -1,0 +1,383 @@
+"""Flagship benchmark: training throughput of the 85.8M-parameter GPT
+(12 layers, d_model 768, 12 heads, MLP 3072, vocab 65, seq 512, global batch 16)
+in tokens/s, on N GPUs of one node.
+
+  python bench.py --gpus 1 --steps 20 --warmup 5
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+      bench.py --gpus N --steps K --warmup W
+
+--impl ours       tandem_b200: DDP / ZeRO-1/2 / FSDP wrappers on the sm_100a kernels, bf16 compute,
+                  fp32 master weights (default strategy: ddp).
+--impl reference  the unmodified reference package installed under baseline/_ref, through its own
+                  launch() / DDP / model and stock fp32 code path.
+--impl torch      torch DistributedDataParallel over NCCL with bf16 autocast (context only).
+
+Data are synthetic: token ids uniform in [0, vocab) from a seed; weights are random-init.
+The global batch is fixed, so per-GPU work shrinks as N grows ("strong" scaling).
+Rank 0 prints one JSON line.  `value` is timed on the device with CUDA events over exactly
+--steps steps (inputs already resident), max over ranks; `e2e` repeats the measurement with,
+every step, the host-to-device copy of that step's tokens from pinned memory and a
+device-to-host read of the loss.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch
+
+MODEL = dict(vocab=65, seq=512, layers=12, heads=12, dim=768)
+GLOBAL_BATCH = 16
+LR, WD = 3e-4, 0.1
+PUBLISHED_TOKENS_PER_S = 10265.0  # the reference's own "tandem DDP" row: 2x T4, fp32 (its README / bench/t4 results)
+
+
+# ---------------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks-", suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    parts = [p.strip() for p in line.split(",")]
+                    if len(parts) < 8:
+                        continue
+                    try:
+                        sm.append(float(parts[0]))
+                        mx.append(float(parts[1]))
+                    except ValueError:
+                        continue
+                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[4:8]):
+                        if v.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ---------------------------------------------------------------------------------------------- data
+def token_batches(count, per_rank, rank, world, vocab, seq, seed=1234):
+    """`count` pinned host batches (x, y) of this rank's rows of the global batch: token ids uniform in
+    [0, vocab) drawn from a per-step seed (every rank draws the whole batch and keeps its rows)."""
+    out = []
+    for step in range(count):
+        gen = torch.Generator().manual_seed(seed * 1_000_003 + step)
+        rows = torch.randint(0, vocab, (per_rank * world, seq + 1), generator=gen)[rank * per_rank:(rank + 1) * per_rank]
+        out.append((rows[:, :-1].contiguous().pin_memory(), rows[:, 1:].contiguous().pin_memory()))
+    return out
+
+
+def timed_loops(step_fn, batches, steps, warmup, device, barrier, reduce_max, launches=None):
+    """Returns (device-timed ms/step with resident inputs, e2e ms/step incl. H2D + loss read, h2d bytes, d2h bytes, launches)."""
+    resident = [(x.to(device), y.to(device)) for x, y in batches]
+    for i in range(warmup):
+        loss = step_fn(*resident[i % len(resident)])
+    loss.item()
+    barrier()
+    torch.cuda.synchronize(device)
+    if launches is not None:
+        launches(True)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        loss = step_fn(*resident[i % len(resident)])
+    t1.record()
+    torch.cuda.synchronize(device)
+    barrier()
+    n_launch = launches(False) if launches is not None else 0
+    dev_ms = reduce_max(t0.elapsed_time(t1) / steps)
+
+    # end to end: pinned host tokens -> device every step, loss back to the host every step
+    for i in range(min(warmup, 3)):
+        x, y = batches[i % len(batches)]
+        step_fn(x.to(device, non_blocking=True), y.to(device, non_blocking=True)).item()
+    barrier()
+    torch.cuda.synchronize(device)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        x, y = batches[i % len(batches)]
+        loss = step_fn(x.to(device, non_blocking=True), y.to(device, non_blocking=True))
+        last = loss.item()
+    t1.record()
+    torch.cuda.synchronize(device)
+    barrier()
+    e2e_ms = reduce_max(t0.elapsed_time(t1) / steps)
+    x, y = batches[0]
+    h2d = x.numel() * x.element_size() + y.numel() * y.element_size()
+    return dev_ms, e2e_ms, h2d, 4, n_launch, last
+
+
+def result_line(args, impl, strategy, dev_ms, e2e_ms, h2d, d2h, launches, clocks, dtype, extra=None):
+    tokens = GLOBAL_BATCH * MODEL["seq"]
+    value = tokens / (dev_ms / 1e3)
+    row = {
+        "metric": f"gpt_85.8M_{strategy}_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / PUBLISHED_TOKENS_PER_S, "dtype": dtype, "data": "synthetic uniform-random token ids, random-init weights",
+        "impl": impl,
+        "config": {"model": "gpt-85.8M (L12 d768 h12 mlp3072 vocab65)", "global_batch": GLOBAL_BATCH, "seq_len": MODEL["seq"],
+                   "parallelism": f"{strategy}{args.gpus}", "optimizer": "AdamW lr 3e-4 wd 0.1",
+                   "l2": "no explicit flush: each step streams parameters, gradients, optimizer state and activations "
+                         "(>1.3 GB) through the 126 MB L2", "timing": "CUDA events on the training stream, max over ranks"},
+        "clocks": clocks,
+        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+    }
+    if extra:
+        row.update(extra)
+    return row
+
+
+# ---------------------------------------------------------------------------------------------- ours
+def run_ours(args):
+    import tandem_b200
+    from tandem_b200.ddp import DDP, BucketAdamW
+    from tandem_b200.model import GPT, Config
+    from tandem_b200.optim import ShardedAdamW
+    from tandem_b200.parallel.symm import cuda_lib
+    from tandem_b200.zero import FSDP, ZeRO
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    g = tandem_b200.Group.from_env(device="cuda")
+    dev = g.device
+    lib = cuda_lib()
+    torch.manual_seed(0)
+    kernels = args.kernels
+    model = GPT(Config(kernels=kernels, **MODEL)).to(dev)
+    pure_bf16 = kernels == "b200"
+    if pure_bf16:
+        model = model.bfloat16()  # fp32 master weights live in the optimizer
+    if args.strategy == "ddp":
+        wrapped = DDP(model, g, rebuild=False)
+        opt = BucketAdamW(wrapped, lr=LR, weight_decay=WD)
+        finish = lambda: (opt.step(), opt.zero_grad())
+    elif args.strategy in ("zero1", "zero2"):
+        wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD))
+        finish = lambda: (wrapped.step(), wrapped.zero_grad())
+    elif args.strategy == "zero3":
+        wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD))
+        finish = lambda: (wrapped.step(), wrapped.zero_grad())
+    else:
+        raise SystemExit(f"unknown strategy {args.strategy}")
+
+    def step_fn(x, y):
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=not pure_bf16):
+            loss = wrapped(x, y)
+        loss.backward()
+        finish()
+        return loss
+
+    def reduce_max(v):
+        if world == 1:
+            return v
+        gathered = torch.zeros(world, dtype=torch.float64)
+        gathered[rank] = v
+        g.all_reduce(gathered)  # CPU tensor: host control plane
+        return float(gathered.max())
+
+    per_rank = GLOBAL_BATCH // world
+    batches = token_batches(8, per_rank, rank, world, MODEL["vocab"], MODEL["seq"])
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    dev_ms, e2e_ms, h2d, d2h, launches, last = timed_loops(
+        step_fn, batches, args.steps, args.warmup, dev, g.barrier, reduce_max,
+        lambda reset: lib.tb_launch_count(1 if reset else 0))
+    clocks = sampler.stop() if rank == 0 else None
+    g.close()
+    if rank == 0:
+        print(json.dumps(result_line(args, "ours", args.strategy, dev_ms, e2e_ms, h2d, d2h, int(launches), clocks, "bf16",
+                                     {"kernels": kernels, "final_loss": last})), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------- torch DDP (context)
+def run_torch(args):
+    import torch.distributed as dist
+    from torch.nn.parallel import DistributedDataParallel
+
+    from tandem_b200.model import GPT, Config
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(0)
+    model = GPT(Config(**MODEL)).to(dev)
+    wrapped = DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    opt = torch.optim.AdamW(model.parameters(), lr=LR, weight_decay=WD, fused=True)
+
+    def step_fn(x, y):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = wrapped(x, y)
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def reduce_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    batches = token_batches(8, GLOBAL_BATCH // world, rank, world, MODEL["vocab"], MODEL["seq"])
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    dev_ms, e2e_ms, h2d, d2h, _, last = timed_loops(step_fn, batches, args.steps, args.warmup, dev, barrier, reduce_max)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        print(json.dumps(result_line(args, "torch", "ddp", dev_ms, e2e_ms, h2d, d2h, 0, clocks, "bf16", {"final_loss": last})),
+              flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------- reference
+def reference_rank(g, steps, warmup, strategy):
+    """Runs inside the reference's launch(): its GPT, its DDP / ZeRO / FSDP, torch AdamW as its bench does."""
+    import torch
+    from tandem.ddp import DDP
+    from tandem.model import GPT, Config
+    from tandem.optim import ShardedAdamW
+    from tandem.zero import FSDP, ZeRO
+
+    sys.path.insert(0, ROOT)
+    dev = g.device
+    torch.manual_seed(0)
+    model = GPT(Config(**MODEL)).to(dev)
+    if strategy == "ddp":
+        wrapped = DDP(model, g)
+        opt = torch.optim.AdamW(model.parameters(), lr=LR, weight_decay=WD, foreach=False)
+        finish = lambda: (opt.step(), opt.zero_grad())
+    elif strategy in ("zero1", "zero2"):
+        wrapped = ZeRO(model, g, int(strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD))
+        finish = lambda: (wrapped.step(), wrapped.zero_grad())
+    else:
+        wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD))
+        finish = lambda: (wrapped.step(), wrapped.zero_grad())
+
+    def step_fn(x, y):
+        loss = wrapped(x, y)
+        loss.backward()
+        finish()
+        return loss
+
+    batches = token_batches(8, GLOBAL_BATCH // g.size, g.rank, g.size, MODEL["vocab"], MODEL["seq"])
+    sampler = ClockSampler(dev.index)
+    if g.rank == 0:
+        sampler.start()
+    dev_ms, e2e_ms, h2d, d2h, _, last = timed_loops(step_fn, batches, steps, warmup, dev, g.barrier, lambda v: v)
+    clocks = sampler.stop() if g.rank == 0 else None
+    return {"dev_ms": dev_ms, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": d2h, "clocks": clocks, "loss": last}
+
+
+def run_reference(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    done_flag = os.path.join(tempfile.gettempdir(), f"tb2-ref-done-{os.environ.get('MASTER_PORT', '0')}-{os.getppid()}")
+    if rank != 0:
+        # The reference starts its own ranks with launch(); the other torchrun ranks only wait for it.
+        deadline = time.time() + 3600
+        while not os.path.exists(done_flag) and time.time() < deadline:
+            time.sleep(0.5)
+        return
+    try:
+        if not os.path.isdir(os.path.join(ref, "tandem")):
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/tandem is missing (reference not installed)"}), flush=True)
+            return
+        sys.path.insert(0, ref)
+        os.environ["PYTHONPATH"] = ref + os.pathsep + ROOT + os.pathsep + os.environ.get("PYTHONPATH", "")
+        try:
+            import tandem
+
+            out = tandem.launch(reference_rank, args.gpus, args.steps, args.warmup, args.strategy, device="cuda",
+                                backend=args.ref_backend)
+        except Exception as e:
+            print(json.dumps({"impl": "reference", "unavailable": f"the reference failed to run: {repr(e)[:300]}"}), flush=True)
+            return
+        dev_ms = max(o["dev_ms"] for o in out)
+        e2e_ms = max(o["e2e_ms"] for o in out)
+        print(json.dumps(result_line(args, "reference", args.strategy, dev_ms, e2e_ms, out[0]["h2d"], out[0]["d2h"], 0,
+                                     out[0]["clocks"], "fp32", {"engine": args.ref_backend, "final_loss": out[0]["loss"]})),
+              flush=True)
+    finally:
+        if world > 1:
+            open(done_flag, "w").close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
+    ap.add_argument("--strategy", default="ddp", choices=["ddp", "zero1", "zero2", "zero3"])
+    ap.add_argument("--kernels", default=os.environ.get("TANDEM_BENCH_KERNELS", "b200"), choices=["torch", "b200"])
+    ap.add_argument("--ref-backend", default="python", choices=["python", "cpp"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.impl == "torch":
+        run_torch(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

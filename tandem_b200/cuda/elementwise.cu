@@ -1,0 +1,106 @@
+// Fused element-wise kernels: multi-tensor AdamW and bucket pack/unpack.
+//
+// adamw: one pass over {param, grad, exp_avg, exp_avg_sq} instead of the nine
+// ATen kernels of torch's single-tensor AdamW (the reference's ShardedAdamW,
+// tandem/optim.py:28-37, and torch.optim.AdamW(foreach=False) used by its DDP
+// path); the arithmetic is in adam.cuh.  Optionally also writes a bf16 copy of
+// the updated parameter (the compute copy under mixed precision).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "adam.cuh"
+
+namespace {
+
+template <typename G>
+__device__ __forceinline__ float grad_of(G g);
+template <>
+__device__ __forceinline__ float grad_of<float>(float g) { return g; }
+template <>
+__device__ __forceinline__ float grad_of<__nv_bfloat16>(__nv_bfloat16 g) { return __bfloat162float(g); }
+
+template <typename G>
+__global__ void __launch_bounds__(256)
+k_adamw(float* __restrict__ param, const G* __restrict__ grad, float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
+        __nv_bfloat16* __restrict__ shadow, long long n, AdamScalars s, float grad_scale) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float g = grad_of<G>(grad[i]);
+    if (grad_scale != 1.f) g = __fmul_rn(g, grad_scale);
+    float p = param[i], m = exp_avg[i], v = exp_avg_sq[i];
+    adam_update(p, m, v, g, s);
+    param[i] = p;
+    exp_avg[i] = m;
+    exp_avg_sq[i] = v;
+    if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(p);
+  }
+}
+
+// ---------------------------------------------------------------- multi-tensor copy
+#define TB_COPY_MAX 48
+struct CopyTable {
+  const char* src[TB_COPY_MAX];
+  char* dst[TB_COPY_MAX];
+  long long bytes[TB_COPY_MAX];
+  int count;
+};
+
+// blockIdx.y picks the tensor, blockIdx.x strides over it.
+__global__ void __launch_bounds__(256) k_multi_copy(CopyTable t) {
+  const int k = blockIdx.y;
+  const char* s = t.src[k];
+  char* d = t.dst[k];
+  const long long n = t.bytes[k];
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  const bool aligned = ((((uintptr_t)s) | ((uintptr_t)d)) & 15) == 0;
+  const long long nvec = aligned ? n / 16 : 0;
+  for (long long v = tid; v < nvec; v += nth) reinterpret_cast<uint4*>(d)[v] = reinterpret_cast<const uint4*>(s)[v];
+  for (long long i = nvec * 16 + tid; i < n; i += nth) d[i] = s[i];
+}
+
+}  // namespace
+
+extern "C" void tb_note_launch(int n);
+
+extern "C" {
+
+// scalars: {1-lr*wd, 1-beta1, beta2, 1-beta2, sqrt(bias_correction2), eps, -lr/bias_correction1}
+int tb_adamw(void* param, const void* grad, int grad_is_bf16, void* exp_avg, void* exp_avg_sq, void* shadow_bf16, long long n,
+             const float* scalars, int do_decay, float grad_scale, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  AdamScalars s{scalars[0], scalars[1], scalars[2], scalars[3], 1.0f / scalars[4], scalars[5], scalars[6], do_decay};
+  long long want = (n + 256 * 4 - 1) / (256 * 4);
+  int blocks = (int)(want > 148 * 8 ? 148 * 8 : want);
+  tb_note_launch(1);
+  if (grad_is_bf16)
+    k_adamw<__nv_bfloat16><<<blocks, 256, 0, stream>>>((float*)param, (const __nv_bfloat16*)grad, (float*)exp_avg,
+                                                        (float*)exp_avg_sq, (__nv_bfloat16*)shadow_bf16, n, s, grad_scale);
+  else
+    k_adamw<float><<<blocks, 256, 0, stream>>>((float*)param, (const float*)grad, (float*)exp_avg, (float*)exp_avg_sq,
+                                                (__nv_bfloat16*)shadow_bf16, n, s, grad_scale);
+  return (int)cudaGetLastError();
+}
+
+// Copies count tensors (src[k] -> dst[k], bytes[k] each) with ceil(count / 48) launches.
+int tb_multi_copy(const void* const* src, void* const* dst, const long long* bytes, int count, cudaStream_t stream) {
+  for (int base = 0; base < count; base += TB_COPY_MAX) {
+    CopyTable t{};
+    long long most = 0;
+    t.count = count - base < TB_COPY_MAX ? count - base : TB_COPY_MAX;
+    for (int k = 0; k < t.count; ++k) {
+      t.src[k] = (const char*)src[base + k];
+      t.dst[k] = (char*)dst[base + k];
+      t.bytes[k] = bytes[base + k];
+      if (t.bytes[k] > most) most = t.bytes[k];
+    }
+    long long want = (most + 256 * 16 * 4 - 1) / (256 * 16 * 4);
+    dim3 grid((unsigned)(want < 1 ? 1 : (want > 64 ? 64 : want)), t.count);
+    tb_note_launch(1);
+    k_multi_copy<<<grid, 256, 0, stream>>>(t);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

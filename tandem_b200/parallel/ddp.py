@@ -169,3 +169,63 @@ class DDP(torch.nn.Module):
                 p.grad = view
         else:
             self._order = []
+
+
+class BucketAdamW:
+    """AdamW over a DDP wrapper's buckets: one fused kernel per bucket.
+
+    Parameters are re-laid as views of one flat buffer per bucket, in the
+    bucket's gradient order, so a bucket's {parameters, gradients, moments} are
+    four parallel flat arrays and a step is `len(buckets)` launches instead of
+    nine ATen kernels per parameter (torch.optim.AdamW(foreach=False), which the
+    reference pairs with its DDP: bench/run.py:102).  With 16-bit parameters the
+    optimizer keeps fp32 master weights and moments and writes the 16-bit
+    parameters back as a shadow copy in the same kernel.
+
+    Create it once the buckets are final: pass rebuild=False to DDP, or create it
+    after the first backward.
+    """
+
+    def __init__(self, ddp, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2):
+        from .optim import ShardedAdamW
+
+        self.ddp = ddp
+        self.rule = ShardedAdamW(lr, betas, eps, weight_decay)
+        self.step_count = 0.0
+        self.slots = []
+        with torch.no_grad():
+            for b in ddp.buckets:
+                first = b.params[0]
+                flat = torch.empty(b.flat.numel(), dtype=first.dtype, device=first.device)
+                at = 0
+                for p in b.params:
+                    view = flat[at:at + p.numel()].view_as(p)
+                    view.copy_(p)
+                    p.data = view
+                    at += p.numel()
+                master = flat if first.dtype == torch.float32 else flat.float()
+                self.slots.append({"bucket": b, "flat": flat, "master": master, "m": torch.zeros_like(master),
+                                   "v": torch.zeros_like(master)})
+
+    @torch.no_grad()
+    def step(self):
+        from ..ops import fused_adamw
+
+        if self.ddp._rebuild:
+            raise RuntimeError("the buckets are not final yet: create BucketAdamW after the first backward or use rebuild=False")
+        self.step_count += 1.0
+        sc = self.rule.scalars(self.step_count)
+        for s in self.slots:
+            b = s["bucket"]
+            shadow = None if s["master"] is s["flat"] else s["flat"]
+            if b.flat.is_cuda:
+                fused_adamw(s["master"], b.flat, s["m"], s["v"], sc, self.rule.weight_decay != 0, shadow)
+            else:
+                self.rule.state["b"] = [self.step_count - 1.0, s["m"], s["v"]]
+                self.rule.update("b", s["master"], b.flat.float(), shadow)
+
+    def zero_grad(self):
+        self.ddp.zero_grad()
+
+    def state_bytes(self):
+        return sum(s[k].numel() * s[k].element_size() for s in self.slots for k in ("m", "v"))

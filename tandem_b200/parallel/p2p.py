@@ -1,0 +1,62 @@
+"""Point-to-point transfers between GPU ranks: NCCL send/recv through
+torch.distributed, started on first use.  Pipeline stages exchange activations
+and gradients with these (the reference moves them through its own slot
+transport: tandem/comm.py:411-448, tandem/csrc/collectives.cpp:350-379).
+Transfers are ordered after the caller's stream, and `wait()` is a stream
+dependency, so a stage can queue compute behind a receive without blocking
+the host."""
+
+import os
+import tempfile
+
+import torch
+
+
+class _NcclWork:
+    def __init__(self, name, group, works, result, nbytes, keep):
+        self.name, self._group, self._works, self.result, self._nbytes, self._keep = name, group, works, result, nbytes, keep
+
+    def wait(self):
+        for w in self._works:
+            w.wait()
+        self._keep = ()
+        return self.result
+
+    def is_completed(self):
+        return all(w.is_completed() for w in self._works)
+
+
+class NcclP2P:
+    def __init__(self, group):
+        import torch.distributed as dist
+
+        self.dist, self.g = dist, group
+        self._own = False
+        if dist.is_initialized():
+            if dist.get_world_size() != group.size or dist.get_rank() != group.rank:
+                raise RuntimeError("the torch.distributed process group does not match this Group")
+        else:
+            path = os.path.join(tempfile.gettempdir(), f"tb2-nccl-{group.job}")
+            dist.init_process_group("nccl", init_method=f"file://{path}", rank=group.rank, world_size=group.size,
+                                    device_id=group.device)
+            self._own = True
+
+    def _done(self, name, works, result, nbytes, async_op, keep):
+        work = _NcclWork(name, self.g, works, result, nbytes, keep)
+        return work if async_op else work.wait()
+
+    def send(self, flat, dst, result, nbytes, async_op):
+        return self._done(f"send->{dst}", [self.dist.isend(flat, dst)], result, nbytes, async_op, (flat,))
+
+    def recv(self, flat, src, result, nbytes, async_op):
+        return self._done(f"recv<-{src}", [self.dist.irecv(flat, src)], result, nbytes, async_op, (flat,))
+
+    def sendrecv(self, sf, dst, rf, src, result, nbytes, async_op):
+        ops = [self.dist.P2POp(self.dist.isend, sf, dst), self.dist.P2POp(self.dist.irecv, rf, src)]
+        return self._done(f"sendrecv->{dst}<-{src}", self.dist.batch_isend_irecv(ops), result, nbytes, async_op, (sf, rf))
+
+    def close(self):
+        if self._own and self.dist.is_initialized():
+            torch.cuda.synchronize(self.g.device)
+            self.dist.destroy_process_group()
+            self._own = False

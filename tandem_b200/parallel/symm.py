@@ -1,0 +1,509 @@
+"""Symmetric memory and the GPU collectives built on it.
+
+Each rank cudaMalloc's heap segments and exports them through CUDA IPC; every
+rank maps every peer's segments, so the same (segment, offset) names a buffer
+on all ranks.  The allocator is deterministic: ranks that make the same
+sequence of alloc()/free() calls get the same offsets, with no communication
+per allocation.  Collectives are single kernels from libtb200_cuda.so
+(tandem_b200/cuda/collectives.cu) launched on one high-priority stream.
+
+A tensor that lives in the heap (DDP buckets, ZeRO flat buffers, FSDP shards,
+anything from Group.empty()) is reduced or gathered in place, zero-copy.  Any
+other CUDA tensor is staged through a symmetric scratch area inside the same
+kernel (copy-in, collective, copy-out fused), in pieces if it is larger.
+
+This replaces the reference's per-peer slot arrays, interprocess events and
+host-driven piece loop (tandem/csrc/cuda_links.cpp:43-160).
+"""
+
+import ctypes
+import functools
+import os
+import time
+
+import numpy as np
+import torch
+
+MAX_RANKS = 8
+MAX_BLOCKS = 128
+ALIGN = 256
+FLAG_BYTES = MAX_BLOCKS * MAX_RANKS * 4
+ALGO = {"auto": 0, "oneshot": 1, "twoshot": 2}
+
+
+class AdamArgs(ctypes.Structure):
+    _fields_ = [("param", ctypes.c_void_p), ("exp_avg", ctypes.c_void_p), ("exp_avg_sq", ctypes.c_void_p),
+                ("shadow", ctypes.c_void_p), ("decay", ctypes.c_float), ("w1", ctypes.c_float), ("b2", ctypes.c_float),
+                ("w2", ctypes.c_float), ("inv_bias2_sqrt", ctypes.c_float), ("eps", ctypes.c_float),
+                ("neg_step", ctypes.c_float), ("do_decay", ctypes.c_int)]
+
+    @classmethod
+    def make(cls, param, exp_avg, exp_avg_sq, scalars, do_decay, shadow=None):
+        decay, w1, b2, w2, bias2_sqrt, eps, neg_step = scalars
+        inv = float(np.float32(1.0) / np.float32(bias2_sqrt))
+        return cls(param.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(),
+                   shadow.data_ptr() if shadow is not None else None, decay, w1, b2, w2, inv, eps, neg_step, int(do_decay))
+
+
+@functools.cache
+def cuda_lib():
+    """libtb200_cuda.so through ctypes, built in-tree if it is missing or stale."""
+    from ..utils import build
+
+    path = build.build_cuda(verbose=os.environ.get("TANDEM_BUILD_VERBOSE") == "1")
+    if path is None or not os.path.exists(path):
+        raise RuntimeError("libtb200_cuda.so is missing and could not be built (is nvcc installed?)")
+    lib = ctypes.CDLL(path)
+    vp, i, ll, d, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_double, ctypes.c_float
+    pp = ctypes.POINTER(ctypes.c_void_p)
+    pll = ctypes.POINTER(ctypes.c_longlong)
+    sig = {
+        "tb_last_error": ([], ctypes.c_char_p),
+        "tb_error_string": ([i], ctypes.c_char_p),
+        "tb_launch_count": ([i], ll),
+        "tb_malloc": ([pp, ctypes.c_size_t], i),
+        "tb_free": ([vp], i),
+        "tb_ipc_export": ([vp, vp], i),
+        "tb_ipc_open": ([vp, pp], i),
+        "tb_ipc_close": ([vp], i),
+        "tb_enable_peer": ([i], i),
+        "tb_can_access_peer": ([i, i], i),
+        "tb_status_alloc": ([pp, pp, ctypes.c_size_t], i),
+        "tb_status_free": ([vp], i),
+        "tb_memset_async": ([vp, i, ctypes.c_size_t, vp], i),
+        "tb_memcpy_async": ([vp, vp, ctypes.c_size_t, vp], i),
+        "tb_device_sync": ([], i),
+        "tb_comm_create": ([i, i, i, pp, pp, vp, d, i], vp),
+        "tb_comm_destroy": ([vp], None),
+        "tb_comm_set_timeout": ([vp, d], None),
+        "tb_comm_set_max_blocks": ([vp, i], None),
+        "tb_barrier": ([vp, vp], i),
+        "tb_all_reduce": ([vp, pp, pp, pp, ll, i, i, i, i, vp], i),
+        "tb_reduce_scatter": ([vp, pp, pp, ll, pll, i, i, i, pp, ctypes.POINTER(AdamArgs), vp], i),
+        "tb_gather_pull": ([vp, pp, pp, pll, pll, pll, pp, i, vp], i),
+        "tb_adamw": ([vp, vp, i, vp, vp, vp, ll, ctypes.POINTER(f), i, f, vp], i),
+        "tb_multi_copy": ([pp, pp, pll, i, vp], i),
+    }
+    for name, (argtypes, restype) in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = argtypes, restype
+    return lib
+
+
+def check_rc(rc, what):
+    if rc != 0:
+        lib = cuda_lib()
+        msg = lib.tb_error_string(rc).decode() if rc > 0 else f"code {rc}"
+        raise RuntimeError(f"{what} failed: {msg} ({lib.tb_last_error().decode()})")
+
+
+def _ptr_array(values, n=None):
+    n = n or len(values)
+    arr = (ctypes.c_void_p * n)()
+    for k, v in enumerate(values):
+        arr[k] = v
+    return arr
+
+
+def _ll_array(values):
+    return (ctypes.c_longlong * len(values))(*values)
+
+
+class _Raw:
+    """A device address range exposed through the CUDA array interface."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def tensor_at(ptr, numel, dtype, device):
+    """A tensor over memory this library owns (it does not free it)."""
+    nbytes = max(numel * torch.empty(0, dtype=dtype).element_size(), 1)
+    t = torch.as_tensor(_Raw(ptr, nbytes), device=device)
+    return t.view(dtype)[:numel]
+
+
+def split_offsets(numel, n, sizes=None):
+    """Element offsets [o_0 .. o_n] of the rank chunks (torch.tensor_split, or explicit sizes)."""
+    if sizes is None:
+        base, extra = divmod(numel, n)
+        sizes = [base + (1 if r < extra else 0) for r in range(n)]
+    offs = [0]
+    for s in sizes:
+        offs.append(offs[-1] + int(s))
+    return offs
+
+
+class Heap:
+    """Deterministic first-fit allocator over equally sized segments on every rank."""
+
+    def __init__(self):
+        self.segments = []  # [(bytes, [base pointer per rank])]
+        self.free = []  # [(segment, offset, bytes)], sorted
+        self.used = {}  # (segment, offset) -> bytes
+
+    def add_segment(self, nbytes, bases):
+        self.segments.append((nbytes, bases))
+        self.free.append((len(self.segments) - 1, 0, nbytes))
+
+    def take(self, nbytes):
+        nbytes = (max(nbytes, 1) + ALIGN - 1) // ALIGN * ALIGN
+        for k, (seg, off, size) in enumerate(self.free):
+            if size >= nbytes:
+                if size == nbytes:
+                    self.free.pop(k)
+                else:
+                    self.free[k] = (seg, off + nbytes, size - nbytes)
+                self.used[(seg, off)] = nbytes
+                return seg, off
+        return None
+
+    def give(self, seg, off):
+        nbytes = self.used.pop((seg, off))
+        self.free.append((seg, off, nbytes))
+        self.free.sort()
+        merged = []
+        for s, o, b in self.free:
+            if merged and merged[-1][0] == s and merged[-1][1] + merged[-1][2] == o:
+                merged[-1] = (s, merged[-1][1], merged[-1][2] + b)
+            else:
+                merged.append((s, o, b))
+        self.free = merged
+
+    def locate(self, rank, ptr, nbytes):
+        for seg, (size, bases) in enumerate(self.segments):
+            base = bases[rank]
+            if base <= ptr and ptr + nbytes <= base + size:
+                return seg, ptr - base
+        return None
+
+    def peers(self, seg, off):
+        return [b + off for b in self.segments[seg][1]]
+
+
+class SymmetricComm:
+    """The GPU side of a Group (one process per GPU)."""
+
+    def __init__(self, group):
+        from ..comm import DTYPE_CODE, CommError
+
+        self._codes, self._error = DTYPE_CODE, CommError
+        self.g = group
+        self.lib = cuda_lib()
+        self.n, self.rank, self.device = group.size, group.rank, group.device
+        if self.n > MAX_RANKS:
+            raise CommError(f"the GPU collectives support at most {MAX_RANKS} ranks")
+        torch.cuda.set_device(self.device)
+        torch.cuda.current_stream(self.device).synchronize()  # make sure a context exists
+        self.stream = torch.cuda.Stream(self.device, priority=group.priority)
+        self.segment_bytes = int(os.environ.get("TANDEM_SYMM_BYTES", str(1 << 30)))
+        self.heap = Heap()
+        self._owned = []  # this rank's cudaMalloc'd segments
+        self._opened = []  # peers' segments mapped here
+        self._add_segment(max(self.segment_bytes, 4 << 20))
+        # control block: flags in the heap (peers write them), barrier counters private
+        seg, off = self.heap.take(FLAG_BYTES)
+        flags = self.heap.peers(seg, off)
+        self._epoch = ctypes.c_void_p()
+        check_rc(self.lib.tb_malloc(ctypes.byref(self._epoch), MAX_BLOCKS * 4), "cudaMalloc")
+        host, dev = ctypes.c_void_p(), ctypes.c_void_p()
+        check_rc(self.lib.tb_status_alloc(ctypes.byref(host), ctypes.byref(dev), 64), "cudaHostAlloc")
+        self._status_host = host
+        self._status = (ctypes.c_uint32 * 16).from_address(host.value)
+        self.device_timeout = float(os.environ.get("TANDEM_DEVICE_TIMEOUT", str(min(group.timeout, 120.0))))
+        self.max_blocks = int(os.environ.get("TANDEM_COMM_BLOCKS", "32"))
+        epochs = [self._epoch.value if q == self.rank else None for q in range(self.n)]
+        self.comm = self.lib.tb_comm_create(self.n, self.rank, 0, _ptr_array(flags), _ptr_array(epochs), dev,
+                                            self.device_timeout, self.max_blocks)
+        self.scratch_half = int(os.environ.get("TANDEM_SCRATCH_BYTES", str(32 << 20)))
+        self._scratch = [self._take(self.scratch_half) for _ in range(2)]
+        self._half = 0
+        self.exact16 = os.environ.get("TANDEM_EXACT16", "0") == "1"
+        self.algo = ALGO[os.environ.get("TANDEM_ALLREDUCE", "auto")]
+        # clock calibration for traces: device event time -> host perf_counter
+        self._t0_event = torch.cuda.Event(enable_timing=True)
+        self._t0_event.record(self.stream)
+        self._t0_event.synchronize()
+        self._t0_host = time.perf_counter()
+
+    # ------------------------------------------------------------------ heap
+    def _add_segment(self, nbytes):
+        """Collective: every rank allocates a segment and maps everyone else's."""
+        mine = ctypes.c_void_p()
+        check_rc(self.lib.tb_malloc(ctypes.byref(mine), nbytes), f"cudaMalloc of a {nbytes >> 20} MiB symmetric segment")
+        self._owned.append(mine.value)
+        handle = (ctypes.c_ubyte * 64)()
+        check_rc(self.lib.tb_ipc_export(mine, handle), "cudaIpcGetMemHandle")
+        table = torch.zeros(self.n, 64, dtype=torch.uint8)
+        table[self.rank] = torch.frombuffer(bytearray(handle), dtype=torch.uint8)
+        self.g._native("handles", lambda: self.g._engine.all_gather(table.data_ptr(), table.numel(), 8, [64] * self.n),
+                       None, 0, False, (table,))
+        bases = []
+        for q in range(self.n):
+            if q == self.rank:
+                bases.append(mine.value)
+                continue
+            raw = (ctypes.c_ubyte * 64)(*table[q].tolist())
+            out = ctypes.c_void_p()
+            check_rc(self.lib.tb_ipc_open(raw, ctypes.byref(out)), f"cudaIpcOpenMemHandle of rank {q}'s segment")
+            self._opened.append(out.value)
+            bases.append(out.value)
+        self.heap.add_segment(nbytes, bases)
+
+    def _take(self, nbytes):
+        where = self.heap.take(nbytes)
+        if where is None:
+            self._add_segment(max(self.segment_bytes, (nbytes + ALIGN - 1) // ALIGN * ALIGN))
+            where = self.heap.take(nbytes)
+        return where
+
+    def alloc(self, numel, dtype, zero=True):
+        esz = torch.empty(0, dtype=dtype).element_size()
+        seg, off = self._take(numel * esz)
+        t = tensor_at(self.heap.segments[seg][1][self.rank] + off, numel, dtype, self.device)
+        if zero:
+            t.zero_()
+        return t
+
+    def free(self, t):
+        where = self.heap.locate(self.rank, t.data_ptr(), 1)
+        if where is not None and where in self.heap.used:
+            self.heap.give(*where)
+
+    def _peers_of(self, t):
+        """Peer addresses of a tensor that lives in the heap, else None."""
+        nbytes = max(t.numel() * t.element_size(), 1)
+        where = self.heap.locate(self.rank, t.data_ptr(), nbytes)
+        return None if where is None else self.heap.peers(*where)
+
+    # ------------------------------------------------------------------ launching
+    def _begin(self, name, tensors):
+        """Orders the communication stream after the caller's stream; returns timing start or None."""
+        cur = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        self.stream.wait_event(ready)
+        for t in tensors:
+            if t is not None and t.is_cuda and self._peers_of(t) is None:
+                t.record_stream(self.stream)
+        if self.g.tracing:
+            start = torch.cuda.Event(enable_timing=True)
+            start.record(self.stream)
+            return start
+        return None
+
+    def _end(self, name, start, result, nbytes, async_op):
+        from ..comm import _StreamWork
+
+        done = torch.cuda.Event(enable_timing=start is not None)
+        done.record(self.stream)
+        work = _StreamWork(name, self.g, done, result, nbytes, start)
+        if async_op:
+            return work
+        return work.wait()
+
+    def _next_scratch(self):
+        self._half ^= 1
+        return self.heap.peers(*self._scratch[self._half])
+
+    def check(self):
+        if self._status[0] != 0:
+            code, rank, peer, epoch, block = (int(self._status[k]) for k in range(5))
+            raise self._error(f"GPU collective gave up after {self.device_timeout:.1f}s: rank {rank} block {block} "
+                              f"never saw rank {peer}'s signal for barrier {epoch} (code {code})")
+
+    def resolve_spans(self, pending, out):
+        for name, start, end, nbytes in pending:
+            end.synchronize()
+            t0 = self._t0_host + self._t0_event.elapsed_time(start) / 1e3
+            t1 = self._t0_host + self._t0_event.elapsed_time(end) / 1e3
+            out.append((name, t0, t1, nbytes))
+
+    def quiesce(self):
+        self.stream.synchronize()
+        self.check()
+
+    # ------------------------------------------------------------------ collectives
+    def all_reduce(self, flat, average, result, nbytes, async_op, algo=None):
+        start = self._begin("all_reduce", [flat])
+        code = self._codes[flat.dtype]
+        algo = self.algo if algo is None else ALGO[algo]
+        s = self.stream.cuda_stream
+        peers = self._peers_of(flat)
+        if flat.numel():
+            if peers is not None:
+                check_rc(self.lib.tb_all_reduce(self.comm, _ptr_array(peers), None, None, flat.numel(), code, int(average),
+                                                int(self.exact16), algo, s), "all_reduce")
+            else:
+                esz = flat.element_size()
+                step = self.scratch_half // esz
+                for lo in range(0, flat.numel(), step):
+                    piece = flat[lo:lo + step]
+                    local = _ptr_array([piece.data_ptr()])
+                    check_rc(self.lib.tb_all_reduce(self.comm, _ptr_array(self._next_scratch()), local, local, piece.numel(),
+                                                    code, int(average), int(self.exact16), algo, s), "all_reduce")
+        return self._end("all_reduce", start, result, nbytes, async_op)
+
+    def reduce_scatter(self, flat, sizes, average, result, nbytes, async_op, accumulate_into=None, adam=None):
+        """Chunk r of `flat` summed over ranks into rank r's `flat` (in place).
+        accumulate_into: a tensor shaped like the chunk that also receives `+= chunk`.
+        adam: AdamArgs for a fused AdamW step with the chunk as the gradient."""
+        start = self._begin("reduce_scatter", [flat, accumulate_into])
+        code = self._codes[flat.dtype]
+        offs = split_offsets(flat.numel(), self.n, sizes)
+        s = self.stream.cuda_stream
+        peers = self._peers_of(flat)
+        acc = _ptr_array([accumulate_into.data_ptr()]) if accumulate_into is not None and accumulate_into.numel() else None
+        adam_p = ctypes.pointer(adam) if adam is not None and offs[self.rank + 1] > offs[self.rank] else None
+        if flat.numel():
+            if peers is not None:
+                check_rc(self.lib.tb_reduce_scatter(self.comm, _ptr_array(peers), None, flat.numel(), _ll_array(offs), code,
+                                                    int(average), int(self.exact16), acc, adam_p, s), "reduce_scatter")
+            else:
+                if flat.numel() * flat.element_size() > self.scratch_half:
+                    raise self._error("reduce_scatter of an unregistered tensor larger than the scratch area: "
+                                      "allocate it with Group.empty() or raise TANDEM_SCRATCH_BYTES")
+                scratch = self._next_scratch()
+                check_rc(self.lib.tb_reduce_scatter(self.comm, _ptr_array(scratch), _ptr_array([flat.data_ptr()]),
+                                                    flat.numel(), _ll_array(offs), code, int(average), int(self.exact16),
+                                                    acc, adam_p, s), "reduce_scatter")
+                lo, hi = offs[self.rank], offs[self.rank + 1]
+                if hi > lo:  # the reduced chunk sits in the scratch: bring it home
+                    esz = flat.element_size()
+                    check_rc(self.lib.tb_memcpy_async(flat.data_ptr() + lo * esz, scratch[self.rank] + lo * esz,
+                                                      (hi - lo) * esz, s), "memcpy")
+        return self._end("reduce_scatter", start, result, nbytes, async_op)
+
+    def _pull(self, srcs, dst, src_off, dst_off, lens, stage, sync):
+        check_rc(self.lib.tb_gather_pull(self.comm, _ptr_array(srcs), _ptr_array([dst]), _ll_array(src_off), _ll_array(dst_off),
+                                         _ll_array(lens), _ptr_array([stage]) if stage is not None else None, int(sync),
+                                         self.stream.cuda_stream), "gather")
+
+    def all_gather(self, flat, sizes, result, nbytes, async_op):
+        start = self._begin("all_gather", [flat])
+        esz = flat.element_size()
+        offs = [o * esz for o in split_offsets(flat.numel(), self.n, sizes)]
+        lens = [offs[q + 1] - offs[q] for q in range(self.n)]
+        peers = self._peers_of(flat)
+        if flat.numel() and self.n > 1:
+            if peers is not None:
+                self._pull(peers, flat.data_ptr(), offs[:-1], offs[:-1], lens, None, True)
+            else:
+                step = self.scratch_half
+                for lo in range(0, max(lens), step):  # piece k of every rank's chunk per launch
+                    plen = [max(0, min(l - lo, step)) for l in lens]
+                    mine = flat.data_ptr() + offs[self.rank] + lo if plen[self.rank] else None
+                    self._pull(self._next_scratch(), flat.data_ptr(), [0] * self.n, [offs[q] + lo for q in range(self.n)],
+                               plen, mine, True)
+        return self._end("all_gather", start, result, nbytes, async_op)
+
+    def gather_shards(self, full, shard, sizes, async_op=True):
+        """full[off_q : off_q + sizes[q]] = rank q's `shard`, for every q, with no
+        synchronisation: `shard` is a heap tensor allocated identically on every rank
+        whose contents only change between barriers (parameter shards between
+        optimizer steps)."""
+        start = self._begin("all_gather", [full])
+        esz = full.element_size()
+        offs = [o * esz for o in split_offsets(full.numel(), self.n, sizes)]
+        lens = [offs[q + 1] - offs[q] for q in range(self.n)]
+        peers = self._peers_of(shard)
+        if peers is None:
+            raise self._error("gather_shards needs a shard allocated with Group.empty()")
+        self._pull(peers, full.data_ptr(), [0] * self.n, offs[:-1], lens, None, False)
+        return self._end("all_gather", start, full, full.numel() * esz, async_op)
+
+    def broadcast(self, flat, root, result, nbytes, async_op):
+        start = self._begin("broadcast", [flat])
+        total = flat.numel() * flat.element_size()
+        peers = self._peers_of(flat)
+        if total and self.n > 1:
+            if peers is not None:
+                lens = [total if q == root else 0 for q in range(self.n)]
+                self._pull(peers, flat.data_ptr(), [0] * self.n, [0] * self.n, lens, None, True)
+            else:
+                step = self.scratch_half
+                for lo in range(0, total, step):
+                    plen = min(step, total - lo)
+                    lens = [plen if q == root else 0 for q in range(self.n)]
+                    stage = flat.data_ptr() + lo if self.rank == root else None
+                    self._pull(self._next_scratch(), flat.data_ptr(), [0] * self.n, [lo] * self.n, lens, stage, True)
+        return self._end("broadcast", start, result, nbytes, async_op)
+
+    def device_barrier(self):
+        """A barrier on the communication stream (ranks meet on the device, the host does not block)."""
+        start = self._begin("barrier", [])
+        check_rc(self.lib.tb_barrier(self.comm, self.stream.cuda_stream), "barrier")
+        return self._end("barrier", start, None, 0, False)
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        self.g._native("barrier", self.g._engine.barrier, None, 0, False)  # nobody is still reading our memory
+        for p in self._opened:
+            self.lib.tb_ipc_close(p)
+        self._opened = []
+        self.g._native("barrier", self.g._engine.barrier, None, 0, False)  # everyone has unmapped
+        for p in self._owned:
+            self.lib.tb_free(p)
+        self._owned = []
+        self.lib.tb_free(self._epoch)
+        self.lib.tb_status_free(self._status_host)
+        self.lib.tb_comm_destroy(self.comm)
+        self.comm = None
+
+
+class EmulatedRanks:
+    """All ranks of a group on ONE GPU, driven by one process: every collective is
+    a single cooperative launch whose blockIdx.y is the rank, so blocks that wait
+    on one another are resident together.  For testing the kernels' multi-rank
+    logic where only one GPU is available; not a transport."""
+
+    def __init__(self, n, device="cuda:0", timeout_s=2.0, max_blocks=16):
+        self.lib = cuda_lib()
+        self.n = n
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self._flags = [torch.zeros(FLAG_BYTES // 4, dtype=torch.int32, device=self.device) for _ in range(n)]
+        self._epochs = [torch.zeros(MAX_BLOCKS, dtype=torch.int32, device=self.device) for _ in range(n)]
+        host, dev = ctypes.c_void_p(), ctypes.c_void_p()
+        check_rc(self.lib.tb_status_alloc(ctypes.byref(host), ctypes.byref(dev), 64), "cudaHostAlloc")
+        self._status_host = host
+        self.status = (ctypes.c_uint32 * 16).from_address(host.value)
+        self.comm = self.lib.tb_comm_create(n, 0, 1, _ptr_array([t.data_ptr() for t in self._flags]),
+                                            _ptr_array([t.data_ptr() for t in self._epochs]), dev, timeout_s, max_blocks)
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def all_reduce(self, bufs, average=False, exact=False, algo="auto", staged=None):
+        """bufs: one symmetric buffer per rank.  staged: per-rank private tensors
+        to reduce through them (in place) instead."""
+        code = {torch.float32: 0, torch.float64: 1, torch.bfloat16: 2, torch.float16: 3, torch.int64: 4, torch.int32: 5}[bufs[0].dtype]
+        numel = (staged or bufs)[0].numel()
+        loc = _ptr_array([t.data_ptr() for t in staged]) if staged else None
+        check_rc(self.lib.tb_all_reduce(self.comm, _ptr_array([b.data_ptr() for b in bufs]), loc, loc, numel, code,
+                                        int(average), int(exact), ALGO[algo], self._stream()), "all_reduce")
+
+    def reduce_scatter(self, bufs, sizes=None, average=False, exact=False, accumulate_into=None, adam=None, staged=None):
+        code = {torch.float32: 0, torch.float64: 1, torch.bfloat16: 2, torch.float16: 3, torch.int64: 4, torch.int32: 5}[bufs[0].dtype]
+        numel = (staged or bufs)[0].numel()
+        offs = split_offsets(numel, self.n, sizes)
+        acc = _ptr_array([t.data_ptr() for t in accumulate_into]) if accumulate_into else None
+        ad = (AdamArgs * self.n)(*adam) if adam else None
+        loc = _ptr_array([t.data_ptr() for t in staged]) if staged else None
+        check_rc(self.lib.tb_reduce_scatter(self.comm, _ptr_array([b.data_ptr() for b in bufs]), loc, numel, _ll_array(offs),
+                                            code, int(average), int(exact), acc, ad, self._stream()), "reduce_scatter")
+        return offs
+
+    def gather(self, srcs, dsts, src_off, dst_off, lens, stage=None, sync=True):
+        st = _ptr_array([t.data_ptr() if t is not None else None for t in stage]) if stage else None
+        check_rc(self.lib.tb_gather_pull(self.comm, _ptr_array([t.data_ptr() for t in srcs]), _ptr_array([t.data_ptr() for t in dsts]),
+                                         _ll_array(src_off), _ll_array(dst_off), _ll_array(lens), st, int(sync),
+                                         self._stream()), "gather")
+
+    def barrier(self):
+        check_rc(self.lib.tb_barrier(self.comm, self._stream()), "barrier")
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        self.lib.tb_comm_destroy(self.comm)
+        self.lib.tb_status_free(self._status_host)

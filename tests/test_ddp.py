@@ -161,3 +161,33 @@ def unused(g):
 
 def test_unused_parameters_are_reported():
     assert launch(unused, 2) == [True, True]
+
+
+def bucket_adamw_rank(g):
+    from tandem_b200.ddp import BucketAdamW
+
+    torch.manual_seed(0)
+    m1, m2 = GPT(CFG), GPT(CFG)
+    m2.load_state_dict(m1.state_dict())
+    d1 = DDP(m1, g, rebuild=False)
+    o1 = BucketAdamW(d1, lr=3e-3, weight_decay=0.1)
+    d2 = DDP(m2, g)
+    o2 = torch.optim.AdamW(m2.parameters(), lr=3e-3, weight_decay=0.1, foreach=False)
+    text = synthetic(20_000)
+    for step in range(4):
+        x, y = text.batch(step, BATCH, CFG.seq, rank=g.rank, world=g.size)
+        l1 = d1(x, y)
+        l1.backward()
+        o1.step()
+        o1.zero_grad()
+        l2 = d2(x, y)
+        l2.backward()
+        o2.step()
+        o2.zero_grad()
+        assert l1.item() == l2.item()
+    return torch.equal(torch.cat([p.detach().reshape(-1) for p in m1.parameters()]),
+                       torch.cat([p.detach().reshape(-1) for p in m2.parameters()]))
+
+
+def test_bucket_adamw_equals_per_parameter_adamw():
+    assert launch(bucket_adamw_rank, 2) == [True, True]
