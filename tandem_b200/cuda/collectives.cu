@@ -451,16 +451,17 @@ static int elem_size(int dtype) {
   }
 }
 
+// Averaging multiplies each operand by float(1/n) before the sum.  That is what
+// ATen's CUDA `div_(n)` does (a host scalar divisor becomes a reciprocal multiply),
+// so results equal a `flat.div_(n)` followed by ordered adds on the GPU; for a
+// power-of-two group it also equals true division.
 static void scale_mode(int n, int average, int* smode, float* sval) {
   if (!average || n == 1) {
     *smode = SCALE_NONE;
     *sval = 1.f;
-  } else if ((n & (n - 1)) == 0) {
+  } else {
     *smode = SCALE_MUL;
     *sval = 1.f / (float)n;
-  } else {
-    *smode = SCALE_DIV;
-    *sval = (float)n;
   }
 }
 

@@ -1,0 +1,513 @@
+// bf16 GEMM on the 5th-generation tensor cores: D[M,N] = A . B (+ epilogue), fp32 accumulation in TMEM.
+//
+// Structure (one persistent CTA per SM, 192 threads, no cluster, no TMA multicast):
+//   warp 0      TMA producer: cp.async.bulk.tensor.2d loads A and B tiles (128B swizzle) into a
+//               4-stage shared-memory ring, signalling `full[s]` by transaction bytes.
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma.cta_group::1.kind::f16
+//               (128 x BN x 16 per instruction, 4 per stage), releases stages with
+//               tcgen05.commit -> `empty[s]`, and hands a finished accumulator to the epilogue
+//               with tcgen05.commit -> `acc_full[b]`.  TMEM holds two accumulators (2 x BN
+//               columns), so the next tile's MMAs overlap this tile's epilogue.
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, then bias / GELU /
+//               residual / dGELU / accumulate in registers and 16-byte stores.
+//
+// Operand layouts.  Each operand is either K-major (the reduction dimension is contiguous in
+// global memory) or MN-major (the other dimension is).  That covers all three GEMMs of a linear
+// layer without transposing anything in memory:
+//   forward   Y[M,N]  = X[M,K] . W[N,K]^T          A K-major,  B K-major
+//   dX        dX[M,K] = dY[M,N] . W[N,K]            A K-major,  B MN-major   (reduction over N)
+//   dW        dW[N,K] = dY[M,N]^T . X[M,K]          A MN-major, B MN-major   (reduction over M)
+// MN-major tiles are loaded as 64-element-wide (128-byte) column strips so the same 128B
+// swizzle applies; the shared-memory descriptors carry the strip stride (LBO) and the 8-row
+// group stride (SBO).
+//
+// Every mbarrier wait is bounded; a wait that runs out sets a host-visible error word and the CTA
+// winds down (frees its TMEM, returns).  The reference has no GEMM of its own: its Linear layers
+// call cuBLAS through torch (tandem/model.py:36-37,53-54,75).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT_CYCLES_SHIFT = 32;  // ~2 s at 2 GHz: (1 << 32) cycles
+
+enum EpilogueFlags {
+  EPI_BIAS = 1,        // + bias[col]
+  EPI_GELU = 2,        // out = gelu(v); with aux_out: also write v (pre-activation) there
+  EPI_RESIDUAL = 4,    // + aux_in[row, col]
+  EPI_DGELU = 8,       // out = v * gelu'(aux_in[row, col])
+  EPI_ACCUMULATE = 16, // out += v  (gradient accumulation)
+  EPI_OUT_F32 = 32,    // out is fp32 (else bf16)
+};
+
+struct GemmArgs {
+  int M, N, K;
+  int ldc;            // leading dimension of out / aux (elements)
+  int flags;
+  void* out;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux_in;   // residual or pre-activation, [M, ldc]
+  __nv_bfloat16* aux_out;        // pre-activation out for EPI_GELU, [M, ldc]
+  int* error;                    // host-mapped; set to 1 when a wait runs out
+};
+
+// ------------------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false (and raises the error word) if the phase does not complete.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > (1ll << WAIT_LIMIT_CYCLES_SHIFT)) {
+      *error = 1;
+      __threadfence_system();
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                   smem_u32(dst)),
+               "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The mbarrier gets one arrival once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets
+// (each >> 4), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(sbo_bytes >> 4) << 32;
+  d |= 1ull << 46;  // version
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16 with bf16 inputs and an fp32 accumulator.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool a_mn, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float gelu_exact(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f)); }
+
+__device__ __forceinline__ float gelu_grad(float x) {
+  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752440f));
+  const float pdf = 0.39894228040143267794f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+
+// ------------------------------------------------------------------------------------------ kernel
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  using L = SmemLayout<BN>;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (g.K + BK - 1) / BK;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: a power of two
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&empty[s], phase ^ 1, g.error))) break;
+          uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + L::A_BYTES;
+          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(a_dst, &map_a, &full[s], k0, m0);  // box {64 k, 128 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &map_a, &full[s], m0 + j * 64, k0);  // box {64 mn, 64 k}
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, &map_b, &full[s], k0, n0);  // box {64 k, BN rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &map_b, &full[s], n0 + j * 64, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BM, BN, A_MN, B_MN);
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const uint32_t buf = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!(ok = mbar_wait(&acc_empty[buf], acc_phase ^ 1, g.error))) break;  // the epilogue has drained this accumulator
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&full[s], phase, g.error))) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+          // K-major: rows of 128 B, 8-row groups 1024 B apart; one K=16 step is 32 B along the row.
+          // MN-major: 64-wide strips 8192 B apart (LBO), 8 k-rows 1024 B apart (SBO); one K=16 step is 16 rows = 2048 B.
+          const uint64_t a_desc = A_MN ? smem_desc(a_addr, 8192, 1024) : smem_desc(a_addr, 16, 1024);
+          const uint64_t b_desc = B_MN ? smem_desc(b_addr, 8192, 1024) : smem_desc(b_addr, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t a_k = a_desc + (uint64_t)((A_MN ? 2048 : 32) * k >> 4);
+            const uint64_t b_k = b_desc + (uint64_t)((B_MN ? 2048 : 32) * k >> 4);
+            mma_bf16(d_tmem, a_k, b_k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+        }
+        if (ok) mma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    uint32_t local_tile = 0;
+    bool ok = true;
+    const bool out_f32 = g.flags & EPI_OUT_F32;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const uint32_t buf = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      ok = mbar_wait(&acc_full[buf], acc_phase, g.error);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t raw[32];
+        tmem_ld32(taddr + c * 32, raw);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < g.M && col0 < g.N) {
+          const size_t base = (size_t)row * g.ldc + col0;
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {  // 8 columns at a time
+            const int col = col0 + v8 * 8;
+            if (col >= g.N) break;
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(raw[v8 * 8 + j]);
+            if (g.flags & EPI_BIAS) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col + j < g.N) x[j] += __bfloat162float(g.bias[col + j]);
+            }
+            const bool full8 = col + 8 <= g.ldc;  // the padded row has room for a whole vector
+            if (g.flags & (EPI_RESIDUAL | EPI_DGELU)) {
+              __nv_bfloat16 aux[8];
+              if (full8) {
+                *reinterpret_cast<uint4*>(aux) = *reinterpret_cast<const uint4*>(g.aux_in + base + v8 * 8);
+              } else {
+                for (int j = 0; j < 8; ++j) aux[j] = col + j < g.N ? g.aux_in[base + v8 * 8 + j] : __float2bfloat16(0.f);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float a = __bfloat162float(aux[j]);
+                x[j] = (g.flags & EPI_RESIDUAL) ? x[j] + a : x[j] * gelu_grad(a);
+              }
+            }
+            if (g.flags & EPI_GELU) {
+              if (g.aux_out != nullptr) {
+                __nv_bfloat16 pre[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pre[j] = __float2bfloat16_rn(x[j]);
+                if (full8) {
+                  *reinterpret_cast<uint4*>(g.aux_out + base + v8 * 8) = *reinterpret_cast<const uint4*>(pre);
+                } else {
+                  for (int j = 0; j < 8; ++j)
+                    if (col + j < g.N) g.aux_out[base + v8 * 8 + j] = pre[j];
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
+            }
+            if (out_f32) {
+              float* o = reinterpret_cast<float*>(g.out) + base + v8 * 8;
+              if (full8) {
+                float4 lo = make_float4(x[0], x[1], x[2], x[3]), hi = make_float4(x[4], x[5], x[6], x[7]);
+                if (g.flags & EPI_ACCUMULATE) {
+                  const float4 a = *reinterpret_cast<const float4*>(o), b = *reinterpret_cast<const float4*>(o + 4);
+                  lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+                  hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+                }
+                *reinterpret_cast<float4*>(o) = lo;
+                *reinterpret_cast<float4*>(o + 4) = hi;
+              } else {
+                for (int j = 0; j < 8; ++j)
+                  if (col + j < g.N) o[j] = (g.flags & EPI_ACCUMULATE) ? o[j] + x[j] : x[j];
+              }
+            } else {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + base + v8 * 8;
+              __nv_bfloat16 y[8];
+              if (g.flags & EPI_ACCUMULATE) {
+                if (full8) {
+                  *reinterpret_cast<uint4*>(y) = *reinterpret_cast<const uint4*>(o);
+                } else {
+                  for (int j = 0; j < 8; ++j) y[j] = col + j < g.N ? o[j] : __float2bfloat16(0.f);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] += __bfloat162float(y[j]);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) y[j] = __float2bfloat16_rn(x[j]);
+              if (full8) {
+                *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(y);
+              } else {
+                for (int j = 0; j < 8; ++j)
+                  if (col + j < g.N) o[j] = y[j];
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  }
+  return fn;
+}
+
+// A 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows of `row_stride` elements.
+int make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long row_stride, int box_inner, int box_outer) {
+  EncodeTiled enc = encoder();
+  if (enc == nullptr) return -10;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+int* g_error_host = nullptr;
+int* g_error_dev = nullptr;
+int g_sm_count = 0;
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int max_ctas, cudaStream_t stream) {
+  auto kernel = k_gemm<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  int ctas = tiles < g_sm_count ? tiles : g_sm_count;
+  if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
+  kernel<<<ctas, GEMM_THREADS, SmemLayout<BN>::TOTAL, stream>>>(ma, mb, g);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" void tb_note_launch(int n);
+
+extern "C" {
+
+// 0 while every GEMM wait so far has completed; 1 after one ran out.
+int tb_gemm_error() { return g_error_host != nullptr ? *g_error_host : 0; }
+
+// D[M,N] = op(A) . op(B) with bf16 operands, then the epilogue selected by `flags` (EpilogueFlags).
+//   a_mn == 0: A is [M, K] with leading dimension lda (K contiguous); a_mn == 1: A is [K, M], lda (M contiguous).
+//   b_mn == 0: B is [N, K] with leading dimension ldb (K contiguous); b_mn == 1: B is [K, N], ldb (N contiguous).
+// Leading dimensions must be multiples of 8 elements and base pointers 16-byte aligned (TMA).
+int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
+                 int flags, const void* bias, const void* aux_in, void* aux_out, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (((uintptr_t)A | (uintptr_t)B) & 15)) return -12;
+  if (g_error_host == nullptr) {
+    if (cudaHostAlloc((void**)&g_error_host, 64, cudaHostAllocMapped) != cudaSuccess) return -13;
+    *g_error_host = 0;
+    if (cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0) != cudaSuccess) return -13;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int BN = N > 128 ? 256 : 128;
+  CUtensorMap ma, mb;
+  int rc;
+  if (!a_mn) rc = make_map(&ma, A, K, M, lda, 64, BM);
+  else rc = make_map(&ma, A, M, K, lda, 64, 64);
+  if (rc) return rc;
+  if (!b_mn) rc = make_map(&mb, B, K, N, ldb, 64, BN);
+  else rc = make_map(&mb, B, N, K, ldb, 64, 64);
+  if (rc) return rc;
+  GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev};
+  tb_note_launch(1);
+#define GO(BN_, AM, BM_) return launch_gemm<BN_, AM, BM_>(ma, mb, g, max_ctas, stream)
+  if (BN == 256) {
+    if (!a_mn && !b_mn) GO(256, false, false);
+    if (!a_mn && b_mn) GO(256, false, true);
+    if (a_mn && b_mn) GO(256, true, true);
+    GO(256, true, false);
+  }
+  if (!a_mn && !b_mn) GO(128, false, false);
+  if (!a_mn && b_mn) GO(128, false, true);
+  if (a_mn && b_mn) GO(128, true, true);
+  GO(128, true, false);
+#undef GO
+}
+
+}  // extern "C"

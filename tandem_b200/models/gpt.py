@@ -85,9 +85,8 @@ class Block(nn.Module):
         if self.kernels == "b200" and x.is_cuda:
             ops = _b200()
             x = self.attn(ops.layer_norm(x, self.ln1.weight, self.ln1.bias, self.ln1.eps), residual=x)
-            h = ops.linear(ops.layer_norm(x, self.ln2.weight, self.ln2.bias, self.ln2.eps), self.fc.weight, self.fc.bias,
-                           gelu=True)
-            return ops.linear(h, self.out.weight, self.out.bias, residual=x)
+            return ops.mlp(ops.layer_norm(x, self.ln2.weight, self.ln2.bias, self.ln2.eps), self.fc.weight, self.fc.bias,
+                           self.out.weight, self.out.bias, residual=x)
         x = x + self.attn(self.ln1(x))
         return x + self.out(F.gelu(self.fc(self.ln2(x))))
 

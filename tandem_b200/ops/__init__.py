@@ -35,6 +35,12 @@ def linear(x, weight, bias=None, gelu=False, residual=None):
     return f(x, weight, bias, gelu, residual)
 
 
+def mlp(x, w1, b1, w2, b2, residual):
+    from .gemm import mlp as f
+
+    return f(x, w1, b1, w2, b2, residual)
+
+
 def layer_norm(x, weight, bias, eps=1e-5):
     from .norm import layer_norm as f
 

@@ -1,0 +1,152 @@
+"""Linear layers on the tcgen05 GEMM (tandem_b200/cuda/gemm.cu).
+
+`linear` and `mlp` are autograd functions whose forward and both backward
+products (dX, dW) run on the same kernel with different operand layouts, and
+whose element-wise work rides in the GEMM epilogues: bias add, exact GELU
+(with the pre-activation saved for backward), the residual add that follows
+the projection, and GELU's derivative applied to the incoming gradient.
+The reference computes these with nn.Linear / F.gelu / `+` (tandem/model.py:36-58)."""
+
+import torch
+
+from ._lib import check_rc, empty_padded, lib, need_bf16, pad8, stream
+
+BIAS, GELU, RESIDUAL, DGELU, ACCUMULATE, OUT_F32 = 1, 2, 4, 8, 16, 32
+
+
+def _rows(t):
+    """(2-D view, leading dimension) of a tensor whose last dim is contiguous and rows evenly strided."""
+    t2 = t.reshape(-1, t.shape[-1]) if t.dim() != 2 else t
+    if t2.stride(1) != 1 or (t2.shape[0] > 1 and t2.stride(0) % 8) or t2.data_ptr() % 16:
+        t2 = _repack(t2)
+    return t2, (t2.stride(0) if t2.shape[0] > 1 else pad8(t2.shape[1]))
+
+
+def _repack(t2):
+    out = empty_padded(t2.shape[0], t2.shape[1], t2.dtype, t2.device)
+    out.copy_(t2)
+    return out
+
+
+def gemm(a, b, M, N, K, lda, ldb, a_mn, b_mn, flags=0, bias=None, aux_in=None, aux_out=None, out=None, out_dtype=torch.bfloat16):
+    """out[M, N] = op(a) . op(b) (+ epilogue).  Returns a [M, N] view with a 16-byte-aligned row stride."""
+    if out is None:
+        out = empty_padded(M, N, out_dtype, a.device)
+    ldc = out.stride(0) if M > 1 else pad8(N)
+    if aux_in is not None and (aux_in.stride(0) if M > 1 else ldc) != ldc:
+        raise ValueError("aux_in must share the output's row stride")
+    if out.dtype == torch.float32:
+        flags |= OUT_F32
+    check_rc(lib().tb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), flags,
+                                bias.data_ptr() if bias is not None else None,
+                                aux_in.data_ptr() if aux_in is not None else None,
+                                aux_out.data_ptr() if aux_out is not None else None, 0, stream(a)), "gemm")
+    return out
+
+
+def _forward(x2, ldx, w, bias, flags, aux_in=None, aux_out=None):
+    M, K = x2.shape
+    N = w.shape[0]
+    if bias is not None:
+        flags |= BIAS
+    return gemm(x2, w, M, N, K, ldx, w.stride(0), False, False, flags, bias, aux_in, aux_out)
+
+
+def _grad_input(dy2, ldy, w, flags=0, aux_in=None):
+    """dX[M, K] = dY[M, N] . W[N, K]   (reduction over N; W read as an MN-major operand)"""
+    M, N = dy2.shape
+    K = w.shape[1]
+    return gemm(dy2, w, M, K, N, ldy, w.stride(0), False, True, flags, None, aux_in)
+
+
+def _grad_weight(dy2, ldy, x2, ldx, dtype):
+    """dW[N, K] = dY[M, N]^T . X[M, K]   (reduction over the M tokens; both operands MN-major)"""
+    M, N = dy2.shape
+    K = x2.shape[1]
+    return gemm(dy2, x2, N, K, M, ldy, ldx, True, True, 0, out_dtype=dtype).contiguous()
+
+
+def _grad_bias(dy2, ldy):
+    M, N = dy2.shape
+    out = torch.empty(N, dtype=torch.bfloat16, device=dy2.device)
+    scratch = torch.empty(32 * N, dtype=torch.float32, device=dy2.device)
+    check_rc(lib().tb_col_sum(dy2.data_ptr(), M, N, ldy, out.data_ptr(), scratch.data_ptr(), stream(dy2)), "col_sum")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        need_bf16(x, w, bias, residual)
+        x2, ldx = _rows(x)
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(-1, residual.shape[-1])
+            if pad8(w.shape[0]) != w.shape[0] or not res2.is_contiguous():
+                raise ValueError("a fused residual needs a contiguous tensor whose width is a multiple of 8")
+        y = _forward(x2, ldx, w, bias, RESIDUAL if res2 is not None else 0, res2)
+        ctx.save_for_backward(x2, w)
+        ctx.ldx, ctx.has_bias, ctx.has_res = ldx, bias is not None, residual is not None
+        ctx.in_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0]) if y.is_contiguous() else y.unflatten(0, x.shape[:-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2, ldy = _rows(dy)
+        dx = dw = db = dres = None
+        if ctx.needs_input_grad[0]:
+            dx = _grad_input(dy2, ldy, w)
+            dx = dx.view(ctx.in_shape) if dx.is_contiguous() else dx.unflatten(0, ctx.in_shape[:-1])
+        if ctx.needs_input_grad[1]:
+            dw = _grad_weight(dy2, ldy, x2, ctx.ldx, w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = _grad_bias(dy2, ldy)
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = dy
+        return dx, dw, db, dres
+
+
+class _MLP(torch.autograd.Function):
+    """out = residual + W2 . gelu(W1 . x + b1) + b2, with both element-wise stages in GEMM epilogues."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, residual):
+        need_bf16(x, w1, b1, w2, b2, residual)
+        x2, ldx = _rows(x)
+        M = x2.shape[0]
+        pre = empty_padded(M, w1.shape[0], torch.bfloat16, x.device)
+        h = _forward(x2, ldx, w1, b1, GELU, None, pre)
+        res2 = residual.reshape(-1, residual.shape[-1])
+        y = _forward(h, h.stride(0), w2, b2, RESIDUAL, res2)
+        ctx.save_for_backward(x2, w1, w2, pre, h)
+        ctx.ldx, ctx.in_shape = ldx, x.shape
+        return y.view(*x.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w1, w2, pre, h = ctx.saved_tensors
+        dy2, ldy = _rows(dy)
+        dw2 = _grad_weight(dy2, ldy, h, h.stride(0), w2.dtype)
+        db2 = _grad_bias(dy2, ldy)
+        dpre = _grad_input(dy2, ldy, w2, DGELU, pre)  # (dY . W2) * gelu'(pre)
+        ldp = dpre.stride(0)
+        dw1 = _grad_weight(dpre, ldp, x2, ctx.ldx, w1.dtype)
+        db1 = _grad_bias(dpre, ldp)
+        dx = _grad_input(dpre, ldp, w1).view(ctx.in_shape)
+        return dx, dw1, db1, dw2, db2, dy
+
+
+def linear(x, weight, bias=None, gelu=False, residual=None):
+    if gelu:
+        raise ValueError("use ops.mlp for the GELU MLP (its backward fuses GELU's derivative into a GEMM epilogue)")
+    return _Linear.apply(x, weight, bias, residual)
+
+
+def mlp(x, w1, b1, w2, b2, residual):
+    return _MLP.apply(x, w1, b1, w2, b2, residual)
+
+
+def gemm_error():
+    """True once any GEMM gave up on a wait (results since then are invalid)."""
+    return bool(lib().tb_gemm_error())

@@ -22,7 +22,7 @@ def expected_fold(xs, average, sizes=None, exact_dtype=None):
     def prep(t):
         t = t.float()
         if average:
-            t = t * (1.0 / n) if n & (n - 1) == 0 else t / n
+            t = t * (1.0 / n)  # ATen's CUDA div_ by a host scalar multiplies by the reciprocal
         return t.to(exact_dtype).float() if exact_dtype else t
 
     out = torch.empty(numel, dtype=torch.float32, device=xs[0].device)

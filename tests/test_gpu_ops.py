@@ -1,0 +1,193 @@
+"""Numerics of the sm_100a compute kernels against plain PyTorch fp32 references
+computed from the same bf16 inputs.  Tolerances are those of one bf16 rounding of
+the output (2^-8 relative) plus fp32 accumulation-order noise."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, want, rtol=1.6e-2, atol=1e-2):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    tol = atol * want.abs().max().clamp_min(1e-6) + rtol * want.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (|want| max {want.abs().max().item():.4g})"
+
+
+def rnd(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+@pytest.fixture(autouse=True)
+def no_gemm_timeouts():
+    yield
+    from tandem_b200.ops.gemm import gemm_error
+
+    torch.cuda.synchronize()
+    assert not gemm_error(), "a GEMM wait ran out"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (256, 384, 768), (1024, 2304, 768), (512, 65, 768),
+                                   (384, 768, 3072), (130, 72, 200)])
+def test_gemm_three_layouts(M, N, K):
+    from tandem_b200.ops._lib import empty_padded
+    from tandem_b200.ops.gemm import gemm
+
+    def padded(rows, cols):
+        t = empty_padded(rows, cols, torch.bfloat16, "cuda")
+        t.copy_(rnd(rows, cols, scale=0.5))
+        return t
+
+    a, b = padded(M, K), padded(N, K)  # forward: A K-major, B K-major
+    out = gemm(a, b, M, N, K, a.stride(0), b.stride(0), False, False)
+    close(out, a.float() @ b.float().t())
+    bt = padded(K, N)  # dX-style: B is [K, N] with N contiguous
+    out = gemm(a, bt, M, N, K, a.stride(0), bt.stride(0), False, True)
+    close(out, a.float() @ bt.float())
+    at = padded(K, M)  # dW-style: both MN-major
+    out = gemm(at, bt, M, N, K, at.stride(0), bt.stride(0), True, True)
+    close(out, at.float().t() @ bt.float())
+    out32 = gemm(at, bt, M, N, K, at.stride(0), bt.stride(0), True, True, out_dtype=torch.float32)
+    close(out32, at.float().t() @ bt.float(), rtol=2e-3, atol=2e-3)
+
+
+def test_gemm_epilogues():
+    from tandem_b200.ops import gemm as G
+
+    M, N, K = 256, 512, 384
+    a, w, bias, res = rnd(M, K, scale=0.5), rnd(N, K, scale=0.5), rnd(N), rnd(M, N)
+    ref = a.float() @ w.float().t() + bias.float()
+    close(G.gemm(a, w, M, N, K, K, K, False, False, G.BIAS, bias), ref)
+    close(G.gemm(a, w, M, N, K, K, K, False, False, G.BIAS | G.RESIDUAL, bias, res), ref + res.float())
+    pre = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    act = G.gemm(a, w, M, N, K, K, K, False, False, G.BIAS | G.GELU, bias, None, pre)
+    close(pre, ref)
+    close(act, torch.nn.functional.gelu(ref))
+    x = pre.float().requires_grad_()
+    torch.nn.functional.gelu(x).sum().backward()
+    close(G.gemm(a, w, M, N, K, K, K, False, False, G.DGELU, None, pre), (a.float() @ w.float().t()) * x.grad)
+    acc = torch.ones(M, N, dtype=torch.float32, device="cuda")
+    G.gemm(a, w, M, N, K, K, K, False, False, G.ACCUMULATE, out=acc)
+    close(acc, a.float() @ w.float().t() + 1, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("N", [768, 65])
+def test_linear_autograd_matches_fp32(N):
+    from tandem_b200 import ops
+
+    B, T, K = 4, 96, 256
+    x, w, b = rnd(B, T, K).requires_grad_(), rnd(N, K, scale=0.1).requires_grad_(), rnd(N).requires_grad_()
+    res = rnd(B, T, N).requires_grad_() if N % 8 == 0 else None
+    y = ops.linear(x, w, b, residual=res)
+    dy = rnd(B, T, N)
+    y.backward(dy)
+    xf, wf, bf = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yf = torch.nn.functional.linear(xf, wf, bf)
+    if res is not None:
+        rf = res.detach().float().requires_grad_()
+        yf = yf + rf
+    yf.backward(dy.float())
+    close(y, yf)
+    close(x.grad, xf.grad)
+    close(w.grad, wf.grad)
+    close(b.grad, bf.grad)
+    if res is not None:
+        close(res.grad, rf.grad)
+
+
+def test_mlp_autograd_matches_fp32():
+    from tandem_b200 import ops
+
+    B, T, D = 2, 128, 256
+    x = rnd(B, T, D).requires_grad_()
+    w1, b1 = rnd(4 * D, D, scale=0.05).requires_grad_(), rnd(4 * D, scale=0.1).requires_grad_()
+    w2, b2 = rnd(D, 4 * D, scale=0.05).requires_grad_(), rnd(D, scale=0.1).requires_grad_()
+    res = rnd(B, T, D).requires_grad_()
+    y = ops.mlp(x, w1, b1, w2, b2, res)
+    dy = rnd(B, T, D)
+    y.backward(dy)
+    f = [t.detach().float().requires_grad_() for t in (x, w1, b1, w2, b2, res)]
+    F = torch.nn.functional
+    yf = f[5] + F.linear(F.gelu(F.linear(f[0], f[1], f[2])), f[3], f[4])
+    yf.backward(dy.float())
+    close(y, yf)
+    for got, want in zip((x, w1, b1, w2, b2, res), f):
+        close(got.grad, want.grad, rtol=3e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("D", [256, 768, 2048])
+def test_layer_norm_matches_fp32(D):
+    from tandem_b200 import ops
+
+    x, w, b = rnd(3, 100, D, scale=2).requires_grad_(), rnd(D).requires_grad_(), rnd(D).requires_grad_()
+    y = ops.layer_norm(x, w, b, 1e-5)
+    dy = rnd(3, 100, D)
+    y.backward(dy)
+    xf, wf, bf = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yf = torch.nn.functional.layer_norm(xf, (D,), wf, bf, 1e-5)
+    yf.backward(dy.float())
+    close(y, yf)
+    close(x.grad, xf.grad)
+    close(w.grad, wf.grad)
+    close(b.grad, bf.grad)
+
+
+@pytest.mark.parametrize("V", [65, 50304])
+def test_cross_entropy_matches_fp32(V):
+    from tandem_b200 import ops
+    from tandem_b200.ops._lib import empty_padded
+
+    rows = 300
+    logits = empty_padded(rows, V, torch.bfloat16, "cuda")
+    logits.copy_(rnd(rows, V, scale=3))
+    ref_in = logits.detach().float().clone().requires_grad_()
+    targets = torch.randint(0, V, (rows,), device="cuda")
+    leaf = logits.detach().requires_grad_()
+    loss = ops.cross_entropy(leaf, targets)
+    want = torch.nn.functional.cross_entropy(ref_in, targets)
+    (loss * 0.5).backward()
+    (want * 0.5).backward()
+    assert abs(loss.item() - want.item()) < 1e-4 * max(1.0, abs(want.item()))
+    close(leaf.grad, ref_in.grad, rtol=2e-2, atol=1e-3)
+
+
+def test_embedding_matches_fp32():
+    from tandem_b200 import ops
+
+    V, S, D, B, T = 65, 128, 256, 4, 128
+    tok, pos = rnd(V, D).requires_grad_(), rnd(S, D).requires_grad_()
+    idx = torch.randint(0, V, (B, T), device="cuda")
+    y = ops.embedding(idx, tok, pos)
+    dy = rnd(B, T, D)
+    y.backward(dy)
+    tf, pf = tok.detach().float().requires_grad_(), pos.detach().float().requires_grad_()
+    yf = tf[idx] + pf[torch.arange(T, device="cuda")]
+    yf.backward(dy.float())
+    close(y, yf)
+    close(tok.grad, tf.grad)
+    close(pos.grad, pf.grad)
+
+
+def test_gpt_on_b200_kernels_tracks_torch_path():
+    """Same weights, same batch: loss and gradients of the kernel path stay within bf16 noise of the torch path."""
+    from tandem_b200.model import GPT, Config
+
+    torch.manual_seed(0)
+    cfg_t = Config(vocab=65, seq=128, layers=2, heads=4, dim=256, kernels="torch")
+    cfg_k = Config(vocab=65, seq=128, layers=2, heads=4, dim=256, kernels="b200")
+    ref = GPT(cfg_t).cuda()
+    ker = GPT(cfg_k).cuda().bfloat16()
+    ker.load_state_dict({k: v.bfloat16() for k, v in ref.state_dict().items()})
+    ref.load_state_dict({k: v.float() for k, v in ker.state_dict().items()})  # identical (bf16-representable) weights
+    x = torch.randint(0, 65, (4, 128), device="cuda")
+    y = torch.randint(0, 65, (4, 128), device="cuda")
+    lk = ker(x, y)
+    lk.backward()
+    lr = ref(x, y)
+    lr.backward()
+    assert abs(lk.item() - lr.item()) < 2e-2, (lk.item(), lr.item())
+    for (name, pk), (_, pr) in zip(ker.named_parameters(), ref.named_parameters()):
+        g, w = pk.grad.float(), pr.grad
+        denom = w.norm().clamp_min(1e-6)
+        assert ((g - w).norm() / denom).item() < 6e-2, (name, ((g - w).norm() / denom).item())
