@@ -295,10 +295,20 @@ class Group:
         return self._native("all_reduce", lambda: self._engine.all_reduce(flat.data_ptr(), flat.numel(), code, op == "avg"),
                             t, nbytes, async_op, (flat,))
 
-    def reduce_scatter(self, t, sizes=None, op="sum", async_op=False):
+    @property
+    def fused(self):
+        """True when collectives run as GPU kernels that accept fused epilogues
+        (reduce_scatter's accumulate_into= / adam=) and sync-free shard gathers."""
+        return self._sym is not None
+
+    def reduce_scatter(self, t, sizes=None, op="sum", async_op=False, accumulate_into=None, adam=None):
         """Sums `t` across ranks; rank r's chunk (chunk r of torch.tensor_split,
         or of `sizes`) ends reduced in place and is returned as a view.  The
-        other chunks' contents afterwards are unspecified."""
+        other chunks' contents afterwards are unspecified.
+        GPU kernels only (`group.fused`): accumulate_into, a tensor shaped like
+        the chunk, also receives `+= chunk` inside the kernel; adam, a
+        parallel.symm.AdamArgs, applies a fused AdamW step with the chunk as
+        the gradient."""
         if op not in ("sum", "avg"):
             raise CommError(f"unknown op {op}")
         flat = self._flat(t)
@@ -310,7 +320,10 @@ class Group:
             raise CommError("avg needs a floating-point tensor")
         if not self._on_host(flat):
             if self._sym is not None:
-                return self._sym.reduce_scatter(flat, sizes, op == "avg", mine, nbytes, async_op)
+                return self._sym.reduce_scatter(flat, sizes, op == "avg", mine, nbytes, async_op, accumulate_into, adam)
+        if accumulate_into is not None or adam is not None:
+            raise CommError("fused reduce_scatter epilogues need GPU ranks with transport='device'")
+        if not self._on_host(flat):
             return self._staged("reduce_scatter", flat,
                                 lambda h: self._engine.reduce_scatter(h.data_ptr(), h.numel(), code, szs, op == "avg"),
                                 lambda: mine, nbytes, async_op)

@@ -429,8 +429,9 @@ class SymmetricComm:
                     self._pull(self._next_scratch(), flat.data_ptr(), [0] * self.n, [lo] * self.n, lens, stage, True)
         return self._end("broadcast", start, result, nbytes, async_op)
 
-    def device_barrier(self):
-        """A barrier on the communication stream (ranks meet on the device, the host does not block)."""
+    def device_barrier(self, after_current=False):
+        """A barrier on the communication stream (ranks meet on the device, the host does not block).
+        The caller's stream waits for it either way; it also waits for the caller's earlier work."""
         start = self._begin("barrier", [])
         check_rc(self.lib.tb_barrier(self.comm, self.stream.cuda_stream), "barrier")
         return self._end("barrier", start, None, 0, False)

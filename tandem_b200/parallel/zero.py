@@ -68,6 +68,7 @@ class _Range:
         self.ready = 0
         self.work = None
         self.staging = None
+        self.fused_acc = False
 
 
 def _flatten_into(buf, layout):
@@ -155,8 +156,15 @@ class ZeRO(torch.nn.Module):
             if self.stage == 1:
                 nxt.work = self.g.all_reduce(self.grad[nxt.a:nxt.b], op="avg", async_op=True)
             else:
-                nxt.work = self.g.reduce_scatter(nxt.staging, self.flat.bucket_sizes(nxt.a, nxt.b), op="avg",
-                                                 async_op=True)
+                sizes = self.flat.bucket_sizes(nxt.a, nxt.b)
+                if self.g.fused and nxt.staging.is_cuda and sizes[self.g.rank]:
+                    at = max(nxt.a, self.flat.lo) - self.flat.lo
+                    nxt.work = self.g.reduce_scatter(nxt.staging, sizes, op="avg", async_op=True,
+                                                     accumulate_into=self.grad_shard[at:at + sizes[self.g.rank]])
+                    nxt.fused_acc = True
+                else:
+                    nxt.work = self.g.reduce_scatter(nxt.staging, sizes, op="avg", async_op=True)
+                    nxt.fused_acc = False
             self._next += 1
 
     def _finish_backward(self):
@@ -165,7 +173,7 @@ class ZeRO(torch.nn.Module):
         for r in self.buckets:
             if r.work is not None:
                 mine = r.work.wait()
-                if self.stage == 2 and mine.numel():
+                if self.stage == 2 and mine.numel() and not r.fused_acc:
                     at = max(r.a, self.flat.lo) - self.flat.lo
                     self.grad_shard[at:at + mine.numel()].add_(mine)
             if self.stage == 2 and r.staging is not None:
@@ -204,6 +212,7 @@ class _Unit:
         self.ready = 0
         self.rs = None  # reduce-scatter in flight
         self.staging = None
+        self.fused_acc = False
 
 
 class FSDP(torch.nn.Module):
@@ -231,7 +240,8 @@ class FSDP(torch.nn.Module):
                 _flatten_into(u.full, u.flat)
                 group.broadcast(u.full, root=0)
                 _point_into(u.full, u.flat)
-                u.shard = group.empty(u.flat.hi - u.flat.lo, u.full.dtype, u.full.device, zero=False)
+                # every rank allocates the largest shard's size, so heap offsets stay identical across ranks
+                u.shard = group.empty(max(u.flat.sizes), u.full.dtype, u.full.device)[:u.flat.hi - u.flat.lo]
                 u.shard.copy_(u.full[u.flat.lo:u.flat.hi])
             for p in ps:
                 self.unit_of[p] = u
@@ -246,6 +256,8 @@ class FSDP(torch.nn.Module):
             raise ValueError("every parameter must belong to one of model.units()")
         self._queued = False
         self.max_live = 0
+        if group.fused and self.units[0].shard.is_cuda:
+            group._sym.device_barrier()  # every rank's shards are in place before anyone pulls them
 
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
@@ -257,8 +269,13 @@ class FSDP(torch.nn.Module):
         u.full.untyped_storage().resize_(u.nbytes)
         self.live += 1
         self.max_live = max(self.max_live, self.live)
-        u.full[u.flat.lo:u.flat.hi].copy_(u.shard)
-        u.pending = self.g.all_gather(u.full, u.flat.sizes, async_op=True)
+        if self.g.fused and u.full.is_cuda:
+            # Shards only change inside step(), which is fenced by barriers on both
+            # sides, so peers' shards can be pulled with no handshake at all.
+            u.pending = self.g._sym.gather_shards(u.full, u.shard, u.flat.sizes)
+        else:
+            u.full[u.flat.lo:u.flat.hi].copy_(u.shard)
+            u.pending = self.g.all_gather(u.full, u.flat.sizes, async_op=True)
 
     def _gather(self, u):
         self._start_gather(u)
@@ -315,7 +332,12 @@ class FSDP(torch.nn.Module):
         if u.ready == len(u.flat.params):
             # Backward through the unit is over: drop its parameters, ship its gradients.
             self._free(u)
-            u.rs = self.g.reduce_scatter(u.staging, u.flat.sizes, op="avg", async_op=True)
+            if self.g.fused and u.staging.is_cuda:  # the shard accumulation rides in the kernel's epilogue
+                u.rs = self.g.reduce_scatter(u.staging, u.flat.sizes, op="avg", async_op=True, accumulate_into=u.grad_shard)
+                u.fused_acc = True
+            else:
+                u.rs = self.g.reduce_scatter(u.staging, u.flat.sizes, op="avg", async_op=True)
+                u.fused_acc = False
 
     def _finish_backward(self):
         self._queued = False
@@ -325,7 +347,7 @@ class FSDP(torch.nn.Module):
                 incomplete = True
             if u.rs is not None:
                 mine = u.rs.wait()
-                if mine.numel():
+                if mine.numel() and not u.fused_acc:
                     u.grad_shard.add_(mine)
             if u.staging is not None:
                 self.g.release(u.staging)
@@ -337,8 +359,13 @@ class FSDP(torch.nn.Module):
 
     @torch.no_grad()
     def step(self):
+        fence = self.g.fused and self.units[0].shard.is_cuda
+        if fence:
+            self.g._sym.device_barrier()  # every rank has finished pulling the old shards
         for u in self.units:
             self.opt.update(u.index, u.shard, u.grad_shard)
+        if fence:
+            self.g._sym.device_barrier(after_current=True)  # the new shards are complete before anyone pulls them
 
     def zero_grad(self):
         for u in self.units:

@@ -1,0 +1,234 @@
+"""Multi-GPU checks (need at least 2 GPUs): the collectives over real NVLink peer
+memory against locally computed values, NCCL point-to-point, and GPU training with
+DDP / ZeRO-1/2 / FSDP / pipeline against torch DDP (NCCL) and single-process runs.
+Integer-valued data make sums exact; training runs use deterministic torch kernels."""
+
+import os
+import tempfile
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+
+
+def data(rank, n, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed * 1000 + rank)
+    hi = 30 if dtype in (torch.bfloat16, torch.float16) else 100
+    return torch.randint(-hi, hi, (n,), generator=g).to(dtype)
+
+
+def gpu_collectives(g):
+    r, w, dev = g.rank, g.size, g.device
+    for dtype in (torch.float32, torch.bfloat16, torch.float64, torch.int64):
+        for n in (0, 1, 5, 1000, 4099, 300_001):
+            want = sum(data(q, n, dtype).double() for q in range(w))
+            for registered in (False, True):
+                x = g.empty(n, dtype) if registered else torch.empty(n, dtype=dtype, device=dev)
+                x.copy_(data(r, n, dtype))
+                g.all_reduce(x)
+                assert torch.equal(x.double().cpu(), want), ("all_reduce", dtype, n, registered)
+                if registered:
+                    g.release(x)
+            sizes = [n // w] * w
+            sizes[-1] += n - sum(sizes)
+            sizes = sizes[1:] + sizes[:1]
+            lo = sum(sizes[:r])
+            x = data(r, n, dtype).to(dev)
+            mine = g.reduce_scatter(x, sizes)
+            assert torch.equal(mine.double().cpu(), want[lo:lo + sizes[r]]), ("reduce_scatter", dtype, n)
+            full = want.to(dtype)
+            x = torch.full((n,), -7, dtype=dtype)
+            x[lo:lo + sizes[r]] = full[lo:lo + sizes[r]]
+            x = x.to(dev)
+            g.all_gather(x, sizes)
+            assert torch.equal(x.cpu(), full), ("all_gather", dtype, n)
+            x = data(r, n, dtype, seed=1).to(dev)
+            g.broadcast(x, root=w - 1)
+            assert torch.equal(x.cpu(), data(w - 1, n, dtype, seed=1)), ("broadcast", dtype, n)
+    x = data(r, 4097, torch.float32).to(dev)
+    works = [g.all_reduce(x, op="avg", async_op=True)]
+    works[0].wait()
+    want = sum(data(q, 4097, torch.float32).double() for q in range(w)) / w
+    assert torch.allclose(x.double().cpu(), want, rtol=0, atol=1e-5)
+    # point to point over NCCL
+    other = (r + 1) % w
+    src = (r - 1) % w
+    a = torch.arange(10_000, dtype=torch.float32, device=dev) * (r + 1)
+    b = torch.empty_like(a)
+    g.sendrecv(a, other, b, src)
+    assert torch.equal(b.cpu(), torch.arange(10_000, dtype=torch.float32) * (src + 1))
+    g.check()
+    return r
+
+
+@needs2
+def test_collectives_on_two_gpus():
+    from tandem_b200 import launch
+
+    assert launch(gpu_collectives, 2, device="cuda") == [0, 1]
+
+
+@needs4
+def test_collectives_on_four_gpus():
+    from tandem_b200 import launch
+
+    assert launch(gpu_collectives, 4, device="cuda") == [0, 1, 2, 3]
+
+
+# ------------------------------------------------------------------ training equality
+def _setup_deterministic():
+    os.environ["CUBLAS_WORKSPACE_CONFIG"] = ":4096:8"
+    torch.use_deterministic_algorithms(True)
+    torch.backends.cuda.enable_flash_sdp(False)
+    torch.backends.cuda.enable_mem_efficient_sdp(False)
+    torch.backends.cuda.matmul.allow_tf32 = False
+
+
+def _cfg():
+    from tandem_b200.model import Config
+
+    return Config(seq=64, layers=2, heads=2, dim=64)
+
+
+STEPS, BATCH = 5, 8
+
+
+def ours_rank(g, strategy):
+    from tandem_b200.data import synthetic
+    from tandem_b200.ddp import DDP
+    from tandem_b200.model import GPT
+    from tandem_b200.optim import ShardedAdamW
+    from tandem_b200.pipeline import Pipeline
+    from tandem_b200.zero import FSDP, ZeRO
+
+    _setup_deterministic()
+    torch.manual_seed(0)
+    cfg = _cfg()
+    text = synthetic(20_000)
+    model = GPT(cfg).to(g.device)
+    pipe = None
+    if strategy == "ddp":
+        wrapped = DDP(model, g, bucket_bytes=64 << 10)
+        opt = torch.optim.AdamW(model.parameters(), lr=3e-3, weight_decay=0.1, foreach=False)
+    elif strategy in ("zero1", "zero2"):
+        wrapped = ZeRO(model, g, int(strategy[-1]), ShardedAdamW(lr=3e-3, weight_decay=0.1, fused=False), 64 << 10)
+    elif strategy == "zero3":
+        wrapped = FSDP(model, g, ShardedAdamW(lr=3e-3, weight_decay=0.1, fused=False))
+    else:
+        pipe = Pipeline(model, g, 4, strategy)
+        opt = torch.optim.AdamW(pipe.parameters(), lr=3e-3, weight_decay=0.1, foreach=False)
+    losses = []
+    for step in range(STEPS):
+        if pipe is not None:
+            x, y = text.batch(step, BATCH, cfg.seq, device=g.device)
+            loss = pipe.train_step(x, y)
+            opt.step()
+            opt.zero_grad()
+        else:
+            x, y = text.batch(step, BATCH, cfg.seq, rank=g.rank, world=g.size, device=g.device)
+            loss = wrapped(x, y)
+            loss.backward()
+            if strategy == "ddp":
+                opt.step()
+                opt.zero_grad()
+            else:
+                wrapped.step()
+                wrapped.zero_grad()
+        losses.append(None if loss is None else loss.item())
+    if strategy == "zero3":
+        w = wrapped.full_parameters().float().cpu()
+    elif pipe is not None:
+        w = torch.cat([p.detach().reshape(-1) for p in pipe.parameters()]).cpu()
+    else:
+        w = torch.cat([p.detach().reshape(-1) for p in model.parameters()]).cpu()
+    g.check()
+    return losses, w
+
+
+def torch_ddp_rank(rank, world, init, out):
+    import torch.distributed as dist
+    from torch.nn.parallel import DistributedDataParallel
+
+    from tandem_b200.data import synthetic
+    from tandem_b200.model import GPT
+
+    torch.cuda.set_device(rank)
+    _setup_deterministic()
+    dist.init_process_group("nccl", init_method=f"file://{init}", rank=rank, world_size=world)
+    torch.manual_seed(0)
+    cfg = _cfg()
+    text = synthetic(20_000)
+    model = GPT(cfg).cuda()
+    ddp = DistributedDataParallel(model, device_ids=[rank])
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3, weight_decay=0.1, foreach=False)
+    losses = []
+    for step in range(STEPS):
+        x, y = text.batch(step, BATCH, cfg.seq, rank=rank, world=world, device="cuda")
+        loss = ddp(x, y)
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.item())
+    torch.save((losses, torch.cat([p.detach().reshape(-1) for p in model.parameters()]).cpu()), f"{out}.{rank}")
+    dist.destroy_process_group()
+
+
+@pytest.fixture(scope="module")
+def torch_ddp_2gpu():
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(torch_ddp_rank, args=(2, os.path.join(d, "init"), os.path.join(d, "out")), nprocs=2)
+        return [torch.load(os.path.join(d, f"out.{r}")) for r in range(2)]
+
+
+@needs2
+@pytest.mark.parametrize("strategy", ["ddp", "zero1", "zero2", "zero3"])
+def test_gpu_training_bit_identical_to_torch_ddp_nccl(strategy, torch_ddp_2gpu):
+    from tandem_b200 import launch
+
+    ours = launch(ours_rank, 2, strategy, device="cuda")
+    for r in range(2):
+        assert ours[r][0] == torch_ddp_2gpu[r][0], (strategy, r, ours[r][0], torch_ddp_2gpu[r][0])
+        assert torch.equal(ours[r][1], torch_ddp_2gpu[r][1]), (strategy, r, (ours[r][1] - torch_ddp_2gpu[r][1]).abs().max())
+
+
+def single_accumulate():
+    from tandem_b200.data import synthetic
+    from tandem_b200.model import GPT, loss_fn
+
+    _setup_deterministic()
+    torch.manual_seed(0)
+    cfg = _cfg()
+    text = synthetic(20_000)
+    model = GPT(cfg).cuda()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3, weight_decay=0.1, foreach=False)
+    losses = []
+    for step in range(STEPS):
+        x, y = text.batch(step, BATCH, cfg.seq, device="cuda")
+        total = 0
+        for xb, yb in zip(x.chunk(4), y.chunk(4)):
+            loss = loss_fn(model(xb), yb) / 4
+            loss.backward()
+            total = total + loss.detach()
+        losses.append(total.item())
+        opt.step()
+        opt.zero_grad()
+    return losses, [torch.cat([p.detach().reshape(-1) for p in u.parameters()]).cpu() for u in model.units()]
+
+
+@needs2
+@pytest.mark.parametrize("schedule", ["gpipe", "1f1b"])
+def test_gpu_pipeline_matches_single_process_accumulation(schedule):
+    from tandem_b200 import launch
+    from tandem_b200.pipeline import split_units
+
+    ours = launch(ours_rank, 2, schedule, device="cuda")
+    ref_losses, ref_units = single_accumulate()
+    for r, (lo, hi) in enumerate(split_units(len(ref_units), 2)):
+        assert torch.equal(ours[r][1], torch.cat(ref_units[lo:hi])), f"stage {r} weights differ"
+    assert ours[-1][0] == ref_losses
