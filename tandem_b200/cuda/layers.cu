@@ -6,6 +6,9 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
+
+#include "noalloc.h"
 
 extern "C" void tb_note_launch(int n);
 
@@ -392,3 +395,43 @@ int tb_embed_bwd(const long long* idx, const void* dy, float* dtok32, void* dtok
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------ no-allocation variant
+// See noalloc.h.  The scratch lives in this file so that both host and device code here can
+// name it; host code must not pass the name itself to a kernel (on the host it is only a
+// stand-in for the symbol), so the device address is looked up once per device.
+static __device__ __align__(256) float g_colsum_scratch[32 * TB_COLSUM_NOALLOC_MAX_N];
+static float* g_colsum_scratch_addr[64] = {nullptr};
+static char g_noalloc_error[160] = "";
+
+extern "C" const char* tb_noalloc_last_error() { return g_noalloc_error; }
+
+extern "C" int tb_col_sum_noalloc(const void* x_bf16, int M, int N, int ld, void* out_bf16, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (N > TB_COLSUM_NOALLOC_MAX_N) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "tb_col_sum_noalloc: N = %d exceeds the built-in scratch (max %d columns)",
+             N, TB_COLSUM_NOALLOC_MAX_N);
+    return TB_NOALLOC_TOO_WIDE;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "tb_col_sum_noalloc: no usable current device");
+    return TB_NOALLOC_SETUP_FAILED;
+  }
+  if (g_colsum_scratch_addr[dev] == nullptr) {  // first call on this device: resolve the symbol here, with it current
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_colsum_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_noalloc_error, sizeof(g_noalloc_error), "tb_col_sum_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return TB_NOALLOC_SETUP_FAILED;
+    }
+    g_colsum_scratch_addr[dev] = p;
+  }
+  float* scratch = g_colsum_scratch_addr[dev];
+  const int slices = M >= 2048 ? 32 : (M >= 256 ? 8 : 1);
+  dim3 grid((N + 31) / 32, slices);
+  tb_note_launch(2);
+  k_col_sum<<<grid, 1024, 0, stream>>>((const __nv_bfloat16*)x_bf16, M, N, ld, scratch);
+  k_reduce_partials<<<(N + 255) / 256, 256, 0, stream>>>(scratch, slices, N, (__nv_bfloat16*)out_bf16, nullptr, N);
+  return (int)cudaGetLastError();
+}
