@@ -212,6 +212,14 @@ def run_ours(args):
         finish()
         return loss
 
+    per_rank = GLOBAL_BATCH // world
+    graphed = args.graph and args.strategy == "ddp"
+    if graphed:
+        from tandem_b200.parallel.graph import GraphedStep
+
+        ex = torch.zeros(per_rank, MODEL["seq"], dtype=torch.long, device=dev)
+        step_fn = GraphedStep(wrapped, opt, ex, ex.clone(), autocast=None if pure_bf16 else torch.bfloat16)
+
     def reduce_max(v):
         if world == 1:
             return v
@@ -220,19 +228,22 @@ def run_ours(args):
         g.all_reduce(gathered)  # CPU tensor: host control plane
         return float(gathered.max())
 
-    per_rank = GLOBAL_BATCH // world
     batches = token_batches(8, per_rank, rank, world, MODEL["vocab"], MODEL["seq"])
     sampler = ClockSampler(dev.index)
     if rank == 0:
         sampler.start()
-    dev_ms, e2e_ms, h2d, d2h, launches, last = timed_loops(
-        step_fn, batches, args.steps, args.warmup, dev, g.barrier, reduce_max,
-        lambda reset: lib.tb_launch_count(1 if reset else 0))
+    lib.tb_launch_count(1)
+    step_fn(batches[0][0].to(dev), batches[0][1].to(dev))  # one eager-or-replayed step to count our kernels per step
+    per_step = lib.tb_launch_count(1)
+    if graphed:
+        per_step = step_fn.launches_per_step
+    dev_ms, e2e_ms, h2d, d2h, launches, last = timed_loops(step_fn, batches, args.steps, args.warmup, dev, g.barrier, reduce_max)
+    launches = per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     g.close()
     if rank == 0:
         print(json.dumps(result_line(args, "ours", args.strategy, dev_ms, e2e_ms, h2d, d2h, int(launches), clocks, "bf16",
-                                     {"kernels": kernels, "final_loss": last})), flush=True)
+                                     {"kernels": kernels, "final_loss": last, "cuda_graph": bool(graphed)})), flush=True)
 
 
 # ---------------------------------------------------------------------------------------------- torch DDP (context)
@@ -369,6 +380,7 @@ def main():
     ap.add_argument("--strategy", default="ddp", choices=["ddp", "zero1", "zero2", "zero3"])
     ap.add_argument("--kernels", default=os.environ.get("TANDEM_BENCH_KERNELS", "b200"), choices=["torch", "b200"])
     ap.add_argument("--ref-backend", default="python", choices=["python", "cpp"])
+    ap.add_argument("--graph", type=int, default=1, help="replay the ddp step as a CUDA graph (ours, ddp only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -1,0 +1,118 @@
+"""Collective sweep: this library's GPU kernels against NCCL (torch.distributed),
+all_reduce / reduce_scatter / all_gather / broadcast, fp32 and bf16, 1 KB - 1 GB.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P -m tandem_b200.bench_collectives [--max-bytes 1073741824] [--out rows.jsonl]
+
+Buffers are allocated once per size (ours: Group.empty(), i.e. symmetric memory, the
+way DDP buckets and ZeRO buffers are; NCCL: ordinary tensors).  Every number is
+device time from CUDA events around `iters` back-to-back calls, after warm-up, max
+over ranks.  For messages smaller than the L2 an L2-sized buffer is overwritten
+between timed batches.  Bus bandwidth: algorithm bandwidth x 2(n-1)/n for
+all-reduce, x (n-1)/n for reduce-scatter / all-gather, x 1 for broadcast (the
+reference reports algorithm bandwidth: bench/run.py:347-348).
+"""
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def timed(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if flush is not None:
+        flush.zero_()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min-bytes", type=int, default=1 << 10)
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--ops", default="all_reduce,reduce_scatter,all_gather,broadcast")
+    ap.add_argument("--dtypes", default="float32,bfloat16")
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ.setdefault("TANDEM_SYMM_BYTES", str(max(args.max_bytes + (128 << 20), 1 << 30)))
+    from tandem_b200 import Group
+
+    g = Group.from_env(device="cuda")
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+    n = world
+    rows = []
+    sizes = []
+    b = args.min_bytes
+    while b <= args.max_bytes:
+        sizes.append(b)
+        b *= 4
+    for dname in args.dtypes.split(","):
+        dtype = getattr(torch, dname)
+        esz = torch.empty(0, dtype=dtype).element_size()
+        for nbytes in sizes:
+            numel = nbytes // esz
+            iters = 200 if nbytes <= (1 << 20) else (50 if nbytes <= (64 << 20) else 10)
+            mine = g.empty(numel, dtype)
+            mine.normal_()
+            theirs = torch.randn(numel, device="cuda").to(dtype)
+            chunk = torch.empty(numel // n, device="cuda", dtype=dtype)
+            fl = flush if nbytes < (128 << 20) else None
+            for op in args.ops.split(","):
+                if op == "all_reduce":
+                    ours = lambda: g.all_reduce(mine, op="avg")
+                    nccl = lambda: dist.all_reduce(theirs, op=dist.ReduceOp.AVG)
+                    factor = 2 * (n - 1) / n
+                elif op == "reduce_scatter":
+                    if numel % n:
+                        continue
+                    ours = lambda: g.reduce_scatter(mine)
+                    nccl = lambda: dist.reduce_scatter_tensor(chunk, theirs)
+                    factor = (n - 1) / n
+                elif op == "all_gather":
+                    if numel % n:
+                        continue
+                    ours = lambda: g.all_gather(mine)
+                    nccl = lambda: dist.all_gather_into_tensor(theirs, chunk)
+                    factor = (n - 1) / n
+                else:
+                    ours = lambda: g.broadcast(mine, root=0)
+                    nccl = lambda: dist.broadcast(theirs, 0)
+                    factor = 1.0
+                t_ours = timed(ours, iters, 5, fl)
+                t_nccl = timed(nccl, iters, 5, fl)
+                row = {"op": op, "dtype": dname, "bytes": nbytes, "ranks": n, "ours_us": round(t_ours * 1e3, 2),
+                       "nccl_us": round(t_nccl * 1e3, 2), "ours_bus_GBps": round(nbytes / t_ours / 1e6 * factor, 1),
+                       "nccl_bus_GBps": round(nbytes / t_nccl / 1e6 * factor, 1), "ratio": round(t_nccl / t_ours, 3)}
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+            g.release(mine)
+            del theirs, chunk
+    g.check()
+    if rank == 0 and args.out:
+        with open(args.out, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+    g.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

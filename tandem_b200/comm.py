@@ -179,7 +179,8 @@ class Group:
             elif size == 1:
                 job = uuid.uuid4().hex[:12]
             else:
-                job = "env" + os.environ.get("MASTER_PORT", "0") + "-" + os.environ.get("TORCHELASTIC_RUN_ID", "0")
+                # the launcher process (torchrun's agent) is the same parent for every rank of one run
+                job = f"env{os.environ.get('MASTER_PORT', '0')}-{os.getppid()}"
         return cls(rank, size, device, job=job, **kw)
 
     # ------------------------------------------------------------------ plumbing

@@ -37,6 +37,42 @@ k_adamw(float* __restrict__ param, const G* __restrict__ grad, float* __restrict
   }
 }
 
+// Same update with the step-dependent scalars read from device memory, so the launch can sit in a
+// CUDA graph and still see a new bias correction on every replay.
+template <typename G>
+__global__ void __launch_bounds__(256)
+k_adamw_dev(float* __restrict__ param, const G* __restrict__ grad, float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
+            __nv_bfloat16* __restrict__ shadow, long long n, const AdamScalars* __restrict__ scalars) {
+  const AdamScalars s = *scalars;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float g = grad_of<G>(grad[i]);
+    float p = param[i], m = exp_avg[i], v = exp_avg_sq[i];
+    adam_update(p, m, v, g, s);
+    param[i] = p;
+    exp_avg[i] = m;
+    exp_avg_sq[i] = v;
+    if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(p);
+  }
+}
+
+// One thread: step += 1, then the scalars of that step, in double precision as the host would.
+__global__ void k_adam_prepare(double* step, double lr, double beta1, double beta2, double eps, double wd, AdamScalars* out) {
+  const double t = *step + 1.0;
+  *step = t;
+  const double bc1 = 1.0 - pow(beta1, t), bc2 = 1.0 - pow(beta2, t);
+  AdamScalars s;
+  s.decay = (float)(1.0 - lr * wd);
+  s.w1 = (float)(1.0 - beta1);
+  s.b2 = (float)beta2;
+  s.w2 = (float)(1.0 - beta2);
+  s.inv_bias2_sqrt = 1.0f / (float)sqrt(bc2);
+  s.eps = (float)eps;
+  s.neg_step = (float)(-(lr / bc1));
+  s.do_decay = wd != 0.0;
+  *out = s;
+}
+
 // ---------------------------------------------------------------- multi-tensor copy
 #define TB_COPY_MAX 48
 struct CopyTable {
@@ -80,6 +116,30 @@ int tb_adamw(void* param, const void* grad, int grad_is_bf16, void* exp_avg, voi
   else
     k_adamw<float><<<blocks, 256, 0, stream>>>((float*)param, (const float*)grad, (float*)exp_avg, (float*)exp_avg_sq,
                                                 (__nv_bfloat16*)shadow_bf16, n, s, grad_scale);
+  return (int)cudaGetLastError();
+}
+
+// Advances the device-resident step counter (a double) and writes that step's AdamScalars (32 bytes) to `scalars`.
+int tb_adam_prepare(void* step_counter, double lr, double beta1, double beta2, double eps, double wd, void* scalars,
+                    cudaStream_t stream) {
+  tb_note_launch(1);
+  k_adam_prepare<<<1, 1, 0, stream>>>((double*)step_counter, lr, beta1, beta2, eps, wd, (AdamScalars*)scalars);
+  return (int)cudaGetLastError();
+}
+
+// tb_adamw with the scalars taken from device memory (written by tb_adam_prepare).
+int tb_adamw_dev(void* param, const void* grad, int grad_is_bf16, void* exp_avg, void* exp_avg_sq, void* shadow_bf16, long long n,
+                 const void* scalars, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  long long want = (n + 256 * 4 - 1) / (256 * 4);
+  int blocks = (int)(want > 148 * 8 ? 148 * 8 : want);
+  tb_note_launch(1);
+  if (grad_is_bf16)
+    k_adamw_dev<__nv_bfloat16><<<blocks, 256, 0, stream>>>((float*)param, (const __nv_bfloat16*)grad, (float*)exp_avg,
+                                                            (float*)exp_avg_sq, (__nv_bfloat16*)shadow_bf16, n, (const AdamScalars*)scalars);
+  else
+    k_adamw_dev<float><<<blocks, 256, 0, stream>>>((float*)param, (const float*)grad, (float*)exp_avg, (float*)exp_avg_sq,
+                                                    (__nv_bfloat16*)shadow_bf16, n, (const AdamScalars*)scalars);
   return (int)cudaGetLastError();
 }
 

@@ -1,15 +1,16 @@
 // bf16 GEMM on the 5th-generation tensor cores: D[M,N] = A . B (+ epilogue), fp32 accumulation in TMEM.
 //
-// Structure (one persistent CTA per SM, 192 threads, no cluster, no TMA multicast):
+// Structure (one persistent CTA per SM, 320 threads, no cluster, no TMA multicast):
 //   warp 0      TMA producer: cp.async.bulk.tensor.2d loads A and B tiles (128B swizzle) into a
-//               4-stage shared-memory ring, signalling `full[s]` by transaction bytes.
+//               3- to 6-stage shared-memory ring, signalling `full[s]` by transaction bytes.
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma.cta_group::1.kind::f16
 //               (128 x BN x 16 per instruction, 4 per stage), releases stages with
 //               tcgen05.commit -> `empty[s]`, and hands a finished accumulator to the epilogue
 //               with tcgen05.commit -> `acc_full[b]`.  TMEM holds two accumulators (2 x BN
 //               columns), so the next tile's MMAs overlap this tile's epilogue.
-//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, then bias / GELU /
-//               residual / dGELU / accumulate in registers and 16-byte stores.
+//   warps 2-9   epilogue: tcgen05.ld 32 lanes x 32 columns at a time (the next load in flight while
+//               one chunk is processed), then bias / GELU / residual / dGELU / accumulate in
+//               registers and 16-byte stores.
 //
 // Operand layouts.  Each operand is either K-major (the reduction dimension is contiguous in
 // global memory) or MN-major (the other dimension is).  That covers all three GEMMs of a linear
@@ -32,10 +33,9 @@
 
 namespace {
 
-constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
-constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_BUDGET = 192 * 1024;   // operand ring
+constexpr int EPI_STAGING = 8 * 4096;     // per epilogue warp: a 32-row x 128-byte block for coalescing its stores
 constexpr uint32_t WAIT_LIMIT_CYCLES_SHIFT = 32;  // ~2 s at 2 GHz: (1 << 32) cycles
 
 enum EpilogueFlags {
@@ -45,6 +45,9 @@ enum EpilogueFlags {
   EPI_DGELU = 8,       // out = v * gelu'(aux_in[row, col])
   EPI_ACCUMULATE = 16, // out += v  (gradient accumulation)
   EPI_OUT_F32 = 32,    // out is fp32 (else bf16)
+  EPI_DISCARD = 64,    // measurement aid: drain the accumulator but compute and store nothing
+  EPI_NO_STORE = 128,  // measurement aid: everything except the final global stores
+  EPI_LOAD_ONLY = 256, // measurement aid: read the accumulator from TMEM and do nothing with it
 };
 
 struct GemmArgs {
@@ -180,21 +183,251 @@ __device__ __forceinline__ float gelu_grad(float x) {
 }
 
 // ------------------------------------------------------------------------------------------ kernel
-template <int BN>
+// One 32-column chunk of one accumulator row: the general path (tile edges, padded rows, any flags).
+__device__ __forceinline__ void epilogue_chunk_generic(const uint32_t (&raw)[32], int row, int col0, const GemmArgs& g, bool out_f32) {
+  if (row < g.M && col0 < g.N) {
+    const size_t base = (size_t)row * g.ldc + col0;
+#pragma unroll
+    for (int v8 = 0; v8 < 4; ++v8) {  // 8 columns at a time
+      const int col = col0 + v8 * 8;
+      if (col >= g.N) break;
+      float x[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(raw[v8 * 8 + j]);
+      if (g.flags & EPI_BIAS) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col + j < g.N) x[j] += __bfloat162float(g.bias[col + j]);
+      }
+      const bool full8 = col + 8 <= g.ldc;  // the padded row has room for a whole vector
+      if (g.flags & (EPI_RESIDUAL | EPI_DGELU)) {
+        __nv_bfloat16 aux[8];
+        if (full8) {
+          *reinterpret_cast<uint4*>(aux) = *reinterpret_cast<const uint4*>(g.aux_in + base + v8 * 8);
+        } else {
+          for (int j = 0; j < 8; ++j) aux[j] = col + j < g.N ? g.aux_in[base + v8 * 8 + j] : __float2bfloat16(0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float a = __bfloat162float(aux[j]);
+          x[j] = (g.flags & EPI_RESIDUAL) ? x[j] + a : x[j] * gelu_grad(a);
+        }
+      }
+      if (g.flags & EPI_GELU) {
+        if (g.aux_out != nullptr) {
+          __nv_bfloat16 pre[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) pre[j] = __float2bfloat16_rn(x[j]);
+          if (full8) {
+            *reinterpret_cast<uint4*>(g.aux_out + base + v8 * 8) = *reinterpret_cast<const uint4*>(pre);
+          } else {
+            for (int j = 0; j < 8; ++j)
+              if (col + j < g.N) g.aux_out[base + v8 * 8 + j] = pre[j];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
+      }
+      if (out_f32) {
+        float* o = reinterpret_cast<float*>(g.out) + base + v8 * 8;
+        if (full8) {
+          float4 lo = make_float4(x[0], x[1], x[2], x[3]), hi = make_float4(x[4], x[5], x[6], x[7]);
+          if (g.flags & EPI_ACCUMULATE) {
+            const float4 a = *reinterpret_cast<const float4*>(o), b = *reinterpret_cast<const float4*>(o + 4);
+            lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+            hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+          }
+          *reinterpret_cast<float4*>(o) = lo;
+          *reinterpret_cast<float4*>(o + 4) = hi;
+        } else {
+          for (int j = 0; j < 8; ++j)
+            if (col + j < g.N) o[j] = (g.flags & EPI_ACCUMULATE) ? o[j] + x[j] : x[j];
+        }
+      } else {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + base + v8 * 8;
+        __nv_bfloat16 y[8];
+        if (g.flags & EPI_ACCUMULATE) {
+          if (full8) {
+            *reinterpret_cast<uint4*>(y) = *reinterpret_cast<const uint4*>(o);
+          } else {
+            for (int j = 0; j < 8; ++j) y[j] = col + j < g.N ? o[j] : __float2bfloat16(0.f);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] += __bfloat162float(y[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = __float2bfloat16_rn(x[j]);
+        if (full8) {
+          *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(y);
+        } else {
+          for (int j = 0; j < 8; ++j)
+            if (col + j < g.N) o[j] = y[j];
+        }
+      }
+    }
+  }
+}
+
+// The same for a chunk that lies wholly inside the matrix with 16-byte-aligned rows: no per-element
+// bounds checks, bias fetched as four 16-byte vectors.
+__device__ __forceinline__ void epilogue_chunk_interior(const uint32_t (&raw)[32], int row, int col0, const GemmArgs& g, bool out_f32,
+                                                        bool bias_vec) {
+  const size_t base = (size_t)row * g.ldc + col0;
+#pragma unroll
+  for (int v8 = 0; v8 < 4; ++v8) {
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(raw[v8 * 8 + j]);
+    if (g.flags & EPI_BIAS) {
+      __nv_bfloat16 bv[8];
+      if (bias_vec) {
+        *reinterpret_cast<uint4*>(bv) = __ldg(reinterpret_cast<const uint4*>(g.bias + col0 + v8 * 8));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bv[j] = g.bias[col0 + v8 * 8 + j];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] += __bfloat162float(bv[j]);
+    }
+    if (g.flags & (EPI_RESIDUAL | EPI_DGELU)) {
+      __nv_bfloat16 aux[8];
+      *reinterpret_cast<uint4*>(aux) = *reinterpret_cast<const uint4*>(g.aux_in + base + v8 * 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a = __bfloat162float(aux[j]);
+        x[j] = (g.flags & EPI_RESIDUAL) ? x[j] + a : x[j] * gelu_grad(a);
+      }
+    }
+    if (g.flags & EPI_GELU) {
+      if (g.aux_out != nullptr) {
+        __nv_bfloat162 pre[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pre[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+        *reinterpret_cast<uint4*>(g.aux_out + base + v8 * 8) = *reinterpret_cast<const uint4*>(pre);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
+    }
+    if (out_f32) {
+      float* o = reinterpret_cast<float*>(g.out) + base + v8 * 8;
+      float4 lo = make_float4(x[0], x[1], x[2], x[3]), hi = make_float4(x[4], x[5], x[6], x[7]);
+      if (g.flags & EPI_ACCUMULATE) {
+        const float4 a = *reinterpret_cast<const float4*>(o), b = *reinterpret_cast<const float4*>(o + 4);
+        lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+        hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+      }
+      *reinterpret_cast<float4*>(o) = lo;
+      *reinterpret_cast<float4*>(o + 4) = hi;
+    } else {
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + base + v8 * 8;
+      if (g.flags & EPI_ACCUMULATE) {
+        __nv_bfloat16 y[8];
+        *reinterpret_cast<uint4*>(y) = *reinterpret_cast<const uint4*>(o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] += __bfloat162float(y[j]);
+      }
+      __nv_bfloat162 y2[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) y2[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+      *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(y2);
+    }
+  }
+}
+
+// Writes a warp's 32-row x 64-column bf16 block (lane = row, `v` = that row's 128 bytes as eight
+// 16-byte vectors) to row-major global memory through shared memory, so that each store instruction
+// covers four complete 128-byte lines instead of 32 scattered 16-byte pieces.  The 16-byte slots are
+// XOR-swizzled by row so neither the writes (lane = row) nor the reads (8 lanes per row) conflict.
+__device__ __forceinline__ void store_block_coalesced(uint8_t* stage, const uint4 (&v)[8], __nv_bfloat16* out, size_t ldc,
+                                                      int row0, int rows_valid, int col0, int lane, bool skip) {
+  __syncwarp();
+#pragma unroll
+  for (int sgm = 0; sgm < 8; ++sgm) *reinterpret_cast<uint4*>(stage + lane * 128 + ((sgm ^ (lane & 7)) << 4)) = v[sgm];
+  __syncwarp();
+  const int sgm = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = (lane >> 3) + 4 * i;
+    const uint4 x = *reinterpret_cast<const uint4*>(stage + r * 128 + ((sgm ^ (r & 7)) << 4));
+    if (r < rows_valid && !skip) *reinterpret_cast<uint4*>(out + (size_t)(row0 + r) * ldc + col0 + sgm * 8) = x;
+    if (skip && x.x == 0x7fc0dead) stage[0] = 1;  // keeps the loads alive when stores are skipped
+  }
+}
+
+// Two adjacent 32-column chunks (64 columns) of an interior tile with a bf16 output: element-wise
+// work in registers, then coalesced stores of the result (and of the pre-activation, if kept).
+__device__ __forceinline__ void epilogue_pair_interior(const uint32_t (&ra)[32], const uint32_t (&rb)[32], uint8_t* stage, int row,
+                                                       int row0, int rows_valid, int col0, const GemmArgs& g, bool bias_vec, int lane) {
+  uint4 outv[8], prev[8];
+  const bool keep_pre = (g.flags & EPI_GELU) && g.aux_out != nullptr;
+  const bool row_ok = row < g.M;
+  const size_t base = (size_t)(row_ok ? row : row0) * g.ldc + col0;  // rows past M only feed the staging shuffle
+#pragma unroll
+  for (int v8 = 0; v8 < 8; ++v8) {
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v8 < 4 ? ra[v8 * 8 + j] : rb[(v8 - 4) * 8 + j]);
+    if (g.flags & EPI_BIAS) {
+      __nv_bfloat16 bv[8];
+      if (bias_vec) {
+        *reinterpret_cast<uint4*>(bv) = __ldg(reinterpret_cast<const uint4*>(g.bias + col0 + v8 * 8));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bv[j] = g.bias[col0 + v8 * 8 + j];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] += __bfloat162float(bv[j]);
+    }
+    if (g.flags & (EPI_RESIDUAL | EPI_DGELU | EPI_ACCUMULATE)) {
+      __nv_bfloat16 aux[8];
+      const __nv_bfloat16* src = (g.flags & EPI_ACCUMULATE) && !(g.flags & (EPI_RESIDUAL | EPI_DGELU))
+                                     ? reinterpret_cast<const __nv_bfloat16*>(g.out) : g.aux_in;
+      *reinterpret_cast<uint4*>(aux) = *reinterpret_cast<const uint4*>(src + base + v8 * 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a = __bfloat162float(aux[j]);
+        x[j] = (g.flags & EPI_DGELU) ? x[j] * gelu_grad(a) : x[j] + a;
+      }
+    }
+    if (g.flags & EPI_GELU) {
+      __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&prev[v8]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pp[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
+    }
+    __nv_bfloat162* oo = reinterpret_cast<__nv_bfloat162*>(&outv[v8]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oo[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+  }
+  const bool skip = g.flags & EPI_NO_STORE;
+  store_block_coalesced(stage, outv, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, row0, rows_valid, col0, lane, skip);
+  if (keep_pre) store_block_coalesced(stage, prev, g.aux_out, g.ldc, row0, rows_valid, col0, lane, skip);
+}
+
+// Tile shapes.  BM = 128: one 128-row accumulator per tile, two of them in TMEM so the next tile's
+// MMAs overlap this tile's epilogue.  BM = 256: two 128-row MMAs per k-step share one B tile (a
+// third less operand traffic per flop and twice the work per pipeline stage, which is what hides
+// the load latency); its two accumulators fill TMEM, so only the halves overlap.
+template <int BM, int BN>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES > 8 ? 8 : SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_STAGING + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int THREADS = 64 + 256;  // producer warp, MMA warp, eight epilogue warps
 };
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int BM, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(320, 1)
 k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BM, BN>;
+  constexpr int STAGES = L::STAGES;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * L::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + EPI_STAGING);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -213,7 +446,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], BM == 128 ? 8 : 4);  // one arrival per epilogue warp that drains it
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -242,7 +475,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
           mbar_expect_tx(&full[s], L::STAGE_BYTES);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_2d(a_dst, &map_a, &full[s], k0, m0);  // box {64 k, 128 rows}
+            tma_load_2d(a_dst, &map_a, &full[s], k0, m0);  // box {64 k, BM rows}
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &map_a, &full[s], m0 + j * 64, k0);  // box {64 mn, 64 k}
@@ -259,16 +492,15 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = instr_desc(128, BN, A_MN, B_MN);
+      constexpr int HALVES = BM / 128;
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-        const uint32_t buf = local_tile & 1;
-        const uint32_t acc_phase = (local_tile >> 1) & 1;
-        if (!(ok = mbar_wait(&acc_empty[buf], acc_phase ^ 1, g.error))) break;  // the epilogue has drained this accumulator
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        // BM = 128: accumulators alternate between the two TMEM regions.  BM = 256: region h holds rows [128h, 128h+128).
+        const uint32_t first_buf = HALVES == 1 ? (local_tile & 1) : 0;
+        const uint32_t acc_phase = HALVES == 1 ? ((local_tile >> 1) & 1) : (local_tile & 1);
+        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
           if (!(ok = mbar_wait(&full[s], phase, g.error))) break;
@@ -277,120 +509,85 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
           const uint32_t b_addr = a_addr + L::A_BYTES;
           // K-major: rows of 128 B, 8-row groups 1024 B apart; one K=16 step is 32 B along the row.
           // MN-major: 64-wide strips 8192 B apart (LBO), 8 k-rows 1024 B apart (SBO); one K=16 step is 16 rows = 2048 B.
-          const uint64_t a_desc = A_MN ? smem_desc(a_addr, 8192, 1024) : smem_desc(a_addr, 16, 1024);
           const uint64_t b_desc = B_MN ? smem_desc(b_addr, 8192, 1024) : smem_desc(b_addr, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t a_k = a_desc + (uint64_t)((A_MN ? 2048 : 32) * k >> 4);
-            const uint64_t b_k = b_desc + (uint64_t)((B_MN ? 2048 : 32) * k >> 4);
-            mma_bf16(d_tmem, a_k, b_k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int h = 0; h < HALVES; ++h) {
+            const uint32_t buf = first_buf + h;
+            if (kb == 0) {  // the epilogue has drained this accumulator
+              if (!(ok = mbar_wait(&acc_empty[buf], acc_phase ^ 1, g.error))) break;
+              tc_fence_after();
+            }
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            const uint32_t a_half = a_addr + h * 16384;  // 128 rows x 128 B, or two 64-wide strips
+            const uint64_t a_desc = A_MN ? smem_desc(a_half, 8192, 1024) : smem_desc(a_half, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t a_k = a_desc + (uint64_t)((A_MN ? 2048 : 32) * k >> 4);
+              const uint64_t b_k = b_desc + (uint64_t)((B_MN ? 2048 : 32) * k >> 4);
+              mma_bf16(d_tmem, a_k, b_k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
           }
-          mma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+          if (ok) mma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
         }
-        if (ok) mma_commit(&acc_full[buf]);
+        if (ok) {
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h) mma_commit(&acc_full[first_buf + h]);
+        }
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    // ------------------------------------------------------------------ epilogue (warps 2 and up)
+    // Eight epilogue warps in two groups of four (one warp per TMEM lane quarter in each group).
+    // BM = 128: both groups drain the same accumulator, each taking half of its columns.
+    // BM = 256: group h drains the accumulator of rows [128h, 128h + 128).
+    const int quarter = warp & 3;        // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    const int group = (warp - 2) >> 2;
+    const int half = BM == 128 ? 0 : group;
     uint32_t local_tile = 0;
     bool ok = true;
     const bool out_f32 = g.flags & EPI_OUT_F32;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-      const uint32_t buf = local_tile & 1;
-      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      const uint32_t buf = BM == 128 ? (local_tile & 1) : half;
+      const uint32_t acc_phase = BM == 128 ? ((local_tile >> 1) & 1) : (local_tile & 1);
       ok = mbar_wait(&acc_full[buf], acc_phase, g.error);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
+      const int row = m0 + half * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      // Chunks of 32 columns, the TMEM load of the next one in flight while this one is processed.
+      const bool interior_rows = row < g.M && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0;
+      const bool bias_vec = (g.flags & EPI_BIAS) && (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0;
+      constexpr int CHUNKS = BN / 32;
+      const int c_begin = BM == 128 ? group * (CHUNKS / 2) : 0;
+      const int c_end = BM == 128 ? c_begin + CHUNKS / 2 : CHUNKS;
+      if (!(g.flags & EPI_DISCARD)) {
+        uint32_t ra[32], rb[32];
+        uint8_t* stage = staging + (warp - 2) * 4096;
+        const int row0 = m0 + half * 128 + quarter * 32;           // first row of this warp's block
+        const int rows_valid = g.M - row0 < 32 ? g.M - row0 : 32;   // may be <= 0 on the last tile row
+        // bf16 outputs whose rows are 16-byte aligned go through the coalescing path; accumulate-with-aux combinations
+        // and fp32 outputs take the direct path.
+        const bool pair_ok = !out_f32 && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && rows_valid > 0 &&
+                             !((g.flags & EPI_ACCUMULATE) && (g.flags & (EPI_RESIDUAL | EPI_DGELU)));
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(taddr + c * 32, raw);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < g.M && col0 < g.N) {
-          const size_t base = (size_t)row * g.ldc + col0;
-#pragma unroll
-          for (int v8 = 0; v8 < 4; ++v8) {  // 8 columns at a time
-            const int col = col0 + v8 * 8;
-            if (col >= g.N) break;
-            float x[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(raw[v8 * 8 + j]);
-            if (g.flags & EPI_BIAS) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (col + j < g.N) x[j] += __bfloat162float(g.bias[col + j]);
-            }
-            const bool full8 = col + 8 <= g.ldc;  // the padded row has room for a whole vector
-            if (g.flags & (EPI_RESIDUAL | EPI_DGELU)) {
-              __nv_bfloat16 aux[8];
-              if (full8) {
-                *reinterpret_cast<uint4*>(aux) = *reinterpret_cast<const uint4*>(g.aux_in + base + v8 * 8);
-              } else {
-                for (int j = 0; j < 8; ++j) aux[j] = col + j < g.N ? g.aux_in[base + v8 * 8 + j] : __float2bfloat16(0.f);
-              }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float a = __bfloat162float(aux[j]);
-                x[j] = (g.flags & EPI_RESIDUAL) ? x[j] + a : x[j] * gelu_grad(a);
-              }
-            }
-            if (g.flags & EPI_GELU) {
-              if (g.aux_out != nullptr) {
-                __nv_bfloat16 pre[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) pre[j] = __float2bfloat16_rn(x[j]);
-                if (full8) {
-                  *reinterpret_cast<uint4*>(g.aux_out + base + v8 * 8) = *reinterpret_cast<const uint4*>(pre);
-                } else {
-                  for (int j = 0; j < 8; ++j)
-                    if (col + j < g.N) g.aux_out[base + v8 * 8 + j] = pre[j];
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
-            }
-            if (out_f32) {
-              float* o = reinterpret_cast<float*>(g.out) + base + v8 * 8;
-              if (full8) {
-                float4 lo = make_float4(x[0], x[1], x[2], x[3]), hi = make_float4(x[4], x[5], x[6], x[7]);
-                if (g.flags & EPI_ACCUMULATE) {
-                  const float4 a = *reinterpret_cast<const float4*>(o), b = *reinterpret_cast<const float4*>(o + 4);
-                  lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
-                  hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
-                }
-                *reinterpret_cast<float4*>(o) = lo;
-                *reinterpret_cast<float4*>(o + 4) = hi;
-              } else {
-                for (int j = 0; j < 8; ++j)
-                  if (col + j < g.N) o[j] = (g.flags & EPI_ACCUMULATE) ? o[j] + x[j] : x[j];
-              }
-            } else {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + base + v8 * 8;
-              __nv_bfloat16 y[8];
-              if (g.flags & EPI_ACCUMULATE) {
-                if (full8) {
-                  *reinterpret_cast<uint4*>(y) = *reinterpret_cast<const uint4*>(o);
-                } else {
-                  for (int j = 0; j < 8; ++j) y[j] = col + j < g.N ? o[j] : __float2bfloat16(0.f);
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) x[j] += __bfloat162float(y[j]);
-              }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) y[j] = __float2bfloat16_rn(x[j]);
-              if (full8) {
-                *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(y);
-              } else {
-                for (int j = 0; j < 8; ++j)
-                  if (col + j < g.N) o[j] = y[j];
-              }
-            }
+        for (int c = c_begin; c < c_end; c += 2) {  // c_end - c_begin is even: 2 or 4 or 8 chunks
+          tmem_ld32(taddr + c * 32, ra);
+          tmem_ld32(taddr + (c + 1) * 32, rb);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (g.flags & EPI_LOAD_ONLY) {
+            if (ra[0] == 0x7fc0dead && rb[31] == 0x7fc0dead) stage[0] = 1;  // keeps the loads alive
+            continue;
+          }
+          if (pair_ok && col0 + 64 <= g.N) {
+            epilogue_pair_interior(ra, rb, stage, row, row0, rows_valid, col0, g, bias_vec, lane);
+          } else {
+            if (interior_rows && col0 + 32 <= g.N) epilogue_chunk_interior(ra, row, col0, g, out_f32, bias_vec);
+            else epilogue_chunk_generic(ra, row, col0, g, out_f32);
+            if (interior_rows && col0 + 64 <= g.N) epilogue_chunk_interior(rb, row, col0 + 32, g, out_f32, bias_vec);
+            else epilogue_chunk_generic(rb, row, col0 + 32, g, out_f32);
           }
         }
       }
@@ -426,6 +623,8 @@ EncodeTiled encoder() {
   return fn;
 }
 
+char g_map_error[256] = "";
+
 // A 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows of `row_stride` elements.
 int make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long row_stride, int box_inner, int box_outer) {
   EncodeTiled enc = encoder();
@@ -437,6 +636,9 @@ int make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    snprintf(g_map_error, sizeof(g_map_error), "cuTensorMapEncodeTiled -> %d (ptr %p, dims %lld x %lld, row stride %lld el, box %d x %d)",
+             (int)r, ptr, inner, outer, row_stride, box_inner, box_outer);
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
@@ -444,21 +646,51 @@ int* g_error_host = nullptr;
 int* g_error_dev = nullptr;
 int g_sm_count = 0;
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BM, int BN, bool A_MN, bool B_MN>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int max_ctas, cudaStream_t stream) {
-  auto kernel = k_gemm<BN, A_MN, B_MN>;
+  auto kernel = k_gemm<BM, BN, A_MN, B_MN>;
+  using L = SmemLayout<BM, BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   int ctas = tiles < g_sm_count ? tiles : g_sm_count;
   if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
-  kernel<<<ctas, GEMM_THREADS, SmemLayout<BN>::TOTAL, stream>>>(ma, mb, g);
+  kernel<<<ctas, L::THREADS, L::TOTAL, stream>>>(ma, mb, g);
   return (int)cudaGetLastError();
 }
+
+// Picks the tile shape with the least estimated time: rounds of tiles over the SMs times the relative
+// cost of one tile.  Measured on B200 (tandem_b200/ops/bench_gemm.py --tile): with a short reduction
+// (K <= 1024) the epilogue sets the pace and the double-buffered 128x256 tile wins; with a long one the
+// 256x256 tile wins (a third less operand traffic per flop) unless it leaves most SMs idle, and the
+// weight-gradient shapes (few output tiles, K = tokens) want 128x128 tiles to fill the machine.
+void choose_tile(int M, int N, int K, int sms, int forced, int* bm, int* bn) {
+  struct Shape { int bm, bn; double cost; };  // cost: relative time of one tile at equal K
+  const Shape shapes[3] = {{256, 256, K <= 1024 ? 5.0 : 4.0}, {128, 256, 2.3}, {128, 128, 1.5}};
+  if (forced >= 0 && forced < 3) {
+    *bm = shapes[forced].bm;
+    *bn = shapes[forced].bn;
+    return;
+  }
+  double best = 1e30;
+  for (const Shape& s : shapes) {
+    if (s.bn > 128 && N <= 128) continue;
+    const long long tiles = (long long)((M + s.bm - 1) / s.bm) * ((N + s.bn - 1) / s.bn);
+    const long long rounds = (tiles + sms - 1) / sms;
+    const double t = rounds * s.cost;
+    if (t < best - 1e-9) {
+      best = t;
+      *bm = s.bm;
+      *bn = s.bn;
+    }
+  }
+}
+
+int g_forced_tile = -1;
 
 }  // namespace
 
@@ -485,7 +717,8 @@ int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, i
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  const int BN = N > 128 ? 256 : 128;
+  int BM = 128, BN = 128;
+  choose_tile(M, N, K, g_sm_count, g_forced_tile, &BM, &BN);
   CUtensorMap ma, mb;
   int rc;
   if (!a_mn) rc = make_map(&ma, A, K, M, lda, 64, BM);
@@ -496,18 +729,22 @@ int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, i
   if (rc) return rc;
   GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev};
   tb_note_launch(1);
-#define GO(BN_, AM, BM_) return launch_gemm<BN_, AM, BM_>(ma, mb, g, max_ctas, stream)
-  if (BN == 256) {
-    if (!a_mn && !b_mn) GO(256, false, false);
-    if (!a_mn && b_mn) GO(256, false, true);
-    if (a_mn && b_mn) GO(256, true, true);
-    GO(256, true, false);
-  }
-  if (!a_mn && !b_mn) GO(128, false, false);
-  if (!a_mn && b_mn) GO(128, false, true);
-  if (a_mn && b_mn) GO(128, true, true);
-  GO(128, true, false);
+#define GO(BM_, BN_) \
+  do { \
+    if (!a_mn && !b_mn) return launch_gemm<BM_, BN_, false, false>(ma, mb, g, max_ctas, stream); \
+    if (!a_mn && b_mn) return launch_gemm<BM_, BN_, false, true>(ma, mb, g, max_ctas, stream); \
+    if (a_mn && b_mn) return launch_gemm<BM_, BN_, true, true>(ma, mb, g, max_ctas, stream); \
+    return launch_gemm<BM_, BN_, true, false>(ma, mb, g, max_ctas, stream); \
+  } while (0)
+  if (BM == 256) GO(256, 256);
+  if (BN == 256) GO(128, 256);
+  GO(128, 128);
 #undef GO
 }
+
+// Forces a tile shape for every later call (0: 256x256, 1: 128x256, 2: 128x128; -1: automatic).  For tuning.
+void tb_gemm_force_tile(int which) { g_forced_tile = which; }
+
+const char* tb_gemm_last_error() { return g_map_error; }
 
 }  // extern "C"

@@ -168,15 +168,26 @@ k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__
   }
 }
 
-// out[c] = sum over p of part[p][c] (fixed order), written as bf16.
-__global__ void k_reduce_partials(const float* __restrict__ part, int parts, int width, __nv_bfloat16* __restrict__ out0,
-                                  __nv_bfloat16* __restrict__ out1, int split) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= width) return;
+// out[c] = sum over p of part[p][c], written as bf16.  32 columns x 8 row lanes per block: each lane adds
+// every 8th partial, then the 8 lanes are combined in a fixed order (deterministic).
+__global__ void __launch_bounds__(256)
+k_reduce_partials(const float* __restrict__ part, int parts, int width, __nv_bfloat16* __restrict__ out0,
+                  __nv_bfloat16* __restrict__ out1, int split) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float acc = 0.f;
-  for (int p = 0; p < parts; ++p) acc += part[(size_t)p * width + c];
-  if (c < split) out0[c] = __float2bfloat16_rn(acc);
-  else out1[c - split] = __float2bfloat16_rn(acc);
+  if (c < width)
+    for (int p = ry; p < parts; p += 8) acc += part[(size_t)p * width + c];
+  sh[ry][cx] = acc;
+  __syncthreads();
+  if (ry == 0 && c < width) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sh[k][cx];
+    if (c < split) out0[c] = __float2bfloat16_rn(t);
+    else out1[c - split] = __float2bfloat16_rn(t);
+  }
 }
 
 // ------------------------------------------------------------------------------------ column sums
@@ -345,7 +356,7 @@ int tb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* 
   else if (D <= 256 * 4) LN(4);
   else LN(8);
 #undef LN
-  k_reduce_partials<<<(2 * D + 255) / 256, 256, 0, s>>>(scratch, blocks, 2 * D, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, D);
+  k_reduce_partials<<<(2 * D + 31) / 32, 256, 0, s>>>(scratch, blocks, 2 * D, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, D);
   return (int)cudaGetLastError();
 }
 
@@ -355,7 +366,7 @@ int tb_col_sum(const void* x, int M, int N, int ld, void* out_bf16, float* scrat
   dim3 grid((N + 31) / 32, slices);
   tb_note_launch(2);
   k_col_sum<<<grid, 1024, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, scratch);
-  k_reduce_partials<<<(N + 255) / 256, 256, 0, s>>>(scratch, slices, N, (__nv_bfloat16*)out_bf16, nullptr, N);
+  k_reduce_partials<<<(N + 31) / 32, 256, 0, s>>>(scratch, slices, N, (__nv_bfloat16*)out_bf16, nullptr, N);
   return (int)cudaGetLastError();
 }
 
@@ -432,6 +443,6 @@ extern "C" int tb_col_sum_noalloc(const void* x_bf16, int M, int N, int ld, void
   dim3 grid((N + 31) / 32, slices);
   tb_note_launch(2);
   k_col_sum<<<grid, 1024, 0, stream>>>((const __nv_bfloat16*)x_bf16, M, N, ld, scratch);
-  k_reduce_partials<<<(N + 255) / 256, 256, 0, stream>>>(scratch, slices, N, (__nv_bfloat16*)out_bf16, nullptr, N);
+  k_reduce_partials<<<(N + 31) / 32, 256, 0, stream>>>(scratch, slices, N, (__nv_bfloat16*)out_bf16, nullptr, N);
   return (int)cudaGetLastError();
 }

@@ -14,6 +14,8 @@ def lib():
     vp, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     sig = {
         "tb_gemm_error": ([], i),
+        "tb_gemm_last_error": ([], ctypes.c_char_p),
+        "tb_gemm_force_tile": ([i], None),
         "tb_gemm_bf16": ([vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp, vp, i, vp], i),
         "tb_layernorm_fwd": ([vp, vp, vp, vp, vp, vp, i, i, f, vp], i),
         "tb_layernorm_bwd_blocks": ([i], i),

@@ -40,3 +40,17 @@ def adamw_step(param, grad, exp_avg, exp_avg_sq, scalars, decay, shadow=None, gr
     check_rc(cuda_lib().tb_adamw(param.data_ptr(), grad.contiguous().data_ptr(), int(grad.dtype == torch.bfloat16),
                                  exp_avg.data_ptr(), exp_avg_sq.data_ptr(), shadow.data_ptr() if shadow is not None else None,
                                  param.numel(), sc, int(decay), float(grad_scale), _stream(param)), "adamw")
+
+
+def adam_prepare(step_counter, hyper, scalars):
+    """step_counter (1 double on the device) += 1; `scalars` (8 floats on the device) <- that step's constants."""
+    lr, (b1, b2), eps, wd = hyper
+    check_rc(cuda_lib().tb_adam_prepare(step_counter.data_ptr(), lr, b1, b2, eps, wd, scalars.data_ptr(), _stream(scalars)),
+             "adam_prepare")
+
+
+def adamw_step_dev(param, grad, exp_avg, exp_avg_sq, scalars, shadow=None):
+    """adamw_step with the step's constants read from device memory (safe inside a CUDA graph)."""
+    check_rc(cuda_lib().tb_adamw_dev(param.data_ptr(), grad.data_ptr(), int(grad.dtype == torch.bfloat16), exp_avg.data_ptr(),
+                                     exp_avg_sq.data_ptr(), shadow.data_ptr() if shadow is not None else None, param.numel(),
+                                     scalars.data_ptr(), _stream(param)), "adamw")

@@ -206,6 +206,10 @@ class BucketAdamW:
                 master = flat if first.dtype == torch.float32 else flat.float()
                 self.slots.append({"bucket": b, "flat": flat, "master": master, "m": torch.zeros_like(master),
                                    "v": torch.zeros_like(master)})
+        dev = ddp.params[0].device
+        if dev.type == "cuda":  # step counter and per-step constants live on the device: the step is graph-capturable
+            self._step_dev = torch.zeros(1, dtype=torch.float64, device=dev)
+            self._scalars_dev = torch.zeros(8, dtype=torch.float32, device=dev)
 
     @torch.no_grad()
     def step(self):
@@ -215,11 +219,16 @@ class BucketAdamW:
             raise RuntimeError("the buckets are not final yet: create BucketAdamW after the first backward or use rebuild=False")
         self.step_count += 1.0
         sc = self.rule.scalars(self.step_count)
+        on_gpu = self.slots[0]["bucket"].flat.is_cuda
+        if on_gpu:
+            from ..ops.elementwise import adam_prepare, adamw_step_dev
+
+            adam_prepare(self._step_dev, (self.rule.lr, self.rule.betas, self.rule.eps, self.rule.weight_decay), self._scalars_dev)
         for s in self.slots:
             b = s["bucket"]
             shadow = None if s["master"] is s["flat"] else s["flat"]
-            if b.flat.is_cuda:
-                fused_adamw(s["master"], b.flat, s["m"], s["v"], sc, self.rule.weight_decay != 0, shadow)
+            if on_gpu:
+                adamw_step_dev(s["master"], b.flat, s["m"], s["v"], self._scalars_dev, shadow)
             else:
                 self.rule.state["b"] = [self.step_count - 1.0, s["m"], s["v"]]
                 self.rule.update("b", s["master"], b.flat.float(), shadow)

@@ -83,6 +83,8 @@ def cuda_lib():
         "tb_gather_pull": ([vp, pp, pp, pll, pll, pll, pp, i, vp], i),
         "tb_adamw": ([vp, vp, i, vp, vp, vp, ll, ctypes.POINTER(f), i, f, vp], i),
         "tb_multi_copy": ([pp, pp, pll, i, vp], i),
+        "tb_adam_prepare": ([vp, d, d, d, d, d, vp, vp], i),
+        "tb_adamw_dev": ([vp, vp, i, vp, vp, vp, ll, vp, vp], i),
     }
     for name, (argtypes, restype) in sig.items():
         fn = getattr(lib, name)
@@ -118,7 +120,7 @@ class _Raw:
 
 def tensor_at(ptr, numel, dtype, device):
     """A tensor over memory this library owns (it does not free it)."""
-    nbytes = max(numel * torch.empty(0, dtype=dtype).element_size(), 1)
+    nbytes = max(numel, 1) * torch.empty(0, dtype=dtype).element_size()
     t = torch.as_tensor(_Raw(ptr, nbytes), device=device)
     return t.view(dtype)[:numel]
 
@@ -210,7 +212,7 @@ class SymmetricComm:
         check_rc(self.lib.tb_status_alloc(ctypes.byref(host), ctypes.byref(dev), 64), "cudaHostAlloc")
         self._status_host = host
         self._status = (ctypes.c_uint32 * 16).from_address(host.value)
-        self.device_timeout = float(os.environ.get("TANDEM_DEVICE_TIMEOUT", str(min(group.timeout, 120.0))))
+        self.device_timeout = float(os.environ.get("TANDEM_DEVICE_TIMEOUT", str(min(group.timeout, 30.0))))
         self.max_blocks = int(os.environ.get("TANDEM_COMM_BLOCKS", "32"))
         epochs = [self._epoch.value if q == self.rank else None for q in range(self.n)]
         self.comm = self.lib.tb_comm_create(self.n, self.rank, 0, _ptr_array(flags), _ptr_array(epochs), dev,
@@ -330,7 +332,7 @@ class SymmetricComm:
         algo = self.algo if algo is None else ALGO[algo]
         s = self.stream.cuda_stream
         peers = self._peers_of(flat)
-        if flat.numel():
+        if flat.numel() and self.n > 1:  # a group of one: the buffer already holds its own sum (and mean)
             if peers is not None:
                 check_rc(self.lib.tb_all_reduce(self.comm, _ptr_array(peers), None, None, flat.numel(), code, int(average),
                                                 int(self.exact16), algo, s), "all_reduce")

@@ -1,0 +1,84 @@
+"""Checkpoint / resume: train k steps, save, keep training -> A; in fresh ranks load
+the file and train the same further steps -> B; A and B must be bit-identical, for
+every strategy, and a checkpoint written by one strategy must load into another."""
+
+import os
+import tempfile
+
+import pytest
+import torch
+
+from tandem_b200 import ckpt, launch
+from tandem_b200.data import synthetic
+from tandem_b200.ddp import DDP
+from tandem_b200.model import GPT, Config
+from tandem_b200.optim import ShardedAdamW
+from tandem_b200.zero import FSDP, ZeRO
+
+CFG = Config(seq=32, layers=2, heads=2, dim=32)
+
+
+def build(g, strategy):
+    torch.manual_seed(0)
+    model = GPT(CFG)
+    if strategy == "ddp":
+        w = DDP(model, g, bucket_bytes=32 << 10)
+        opt = torch.optim.AdamW(model.parameters(), lr=3e-3, weight_decay=0.1, foreach=False)
+        return w, opt, lambda: (opt.step(), opt.zero_grad())
+    opt = ShardedAdamW(lr=3e-3, weight_decay=0.1)
+    w = ZeRO(model, g, int(strategy[-1]), opt, 8 << 10) if strategy != "zero3" else FSDP(model, g, opt)
+    return w, opt, lambda: (w.step(), w.zero_grad())
+
+
+def steps(g, w, finish, first, count):
+    text = synthetic(20_000)
+    losses = []
+    for step in range(first, first + count):
+        x, y = text.batch(step, 8, CFG.seq, rank=g.rank, world=g.size)
+        loss = w(x, y)
+        loss.backward()
+        finish()
+        losses.append(loss.item())
+    return losses
+
+
+def weights(w):
+    sd = ckpt.full_state_dict(w)
+    return torch.cat([sd[k].reshape(-1) for k in sorted(sd)])
+
+
+def run_and_save(g, strategy, path):
+    w, opt, finish = build(g, strategy)
+    steps(g, w, finish, 0, 3)
+    ckpt.save(path, w, opt, extra={"next_step": 3})
+    more = steps(g, w, finish, 3, 3)
+    return more, weights(w)
+
+
+def resume(g, strategy, path):
+    w, opt, finish = build(g, strategy)
+    extra = ckpt.load(path, w, opt)
+    more = steps(g, w, finish, extra["next_step"], 3)
+    return more, weights(w)
+
+
+@pytest.mark.parametrize("strategy", ["ddp", "zero1", "zero2", "zero3"])
+def test_resume_is_bit_identical(strategy):
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "ck.pt")
+        a = launch(run_and_save, 2, strategy, path)
+        b = launch(resume, 2, strategy, path)
+        blob = torch.load(path, weights_only=False)
+    assert a[0][0] == b[0][0] and a[1][0] == b[1][0]
+    assert torch.equal(a[0][1], b[0][1])
+    keys = set(blob["model"])
+    assert "module.embed.tok.weight" in keys and "module.blocks.1.attn.qkv.bias" in keys and "module.head.lm.weight" in keys
+
+
+def test_checkpoint_moves_between_strategies():
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "ck.pt")
+        a = launch(run_and_save, 2, "zero2", path)
+        b = launch(resume, 2, "zero3", path)
+    assert a[0][0] == b[0][0]
+    assert torch.equal(a[0][1], b[0][1])
