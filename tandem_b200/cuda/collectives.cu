@@ -121,6 +121,42 @@ __device__ __forceinline__ T fold_one(const PeerPtrs& buf, int n, int c, long lo
   return from_f<T>(acc);
 }
 
+// Vector body shared by the two-shot all-reduce and reduce-scatter: folds `nvec` 16-byte vectors of chunk
+// `rank` starting at byte offset `off0`.  NR is the group size when it is 2, 4 or 8 (loops unroll exactly and
+// eight operand vectors are in flight per thread), 0 otherwise (predicated over TB_MAX_RANKS).
+template <typename T, bool EXACT, int NR, typename Sink>
+__device__ __forceinline__ void fold_vectors(const PeerPtrs& buf, int n_runtime, int rank, long long off0, long long nvec, int smode,
+                                             float sval, long long tid, long long nth, Sink&& sink) {
+  constexpr int U = NR ? 8 / NR : 1;
+  const int n = NR ? NR : n_runtime;
+  const char* ord[TB_MAX_RANKS];  // operands in fold order: ranks rank+1, ..., rank
+  {
+    int q = rank;
+#pragma unroll
+    for (int j = 0; j < TB_MAX_RANKS; ++j) {
+      q = q + 1 >= n ? 0 : q + 1;
+      ord[j] = j < n ? buf.p[q] : nullptr;
+    }
+  }
+  for (long long v = tid; v < nvec; v += nth * U) {
+    uint4 x[U][TB_MAX_RANKS];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long vv = v + u * nth;
+      if (vv < nvec) {
+#pragma unroll
+        for (int j = 0; j < TB_MAX_RANKS; ++j)
+          if (j < n) x[u][j] = ld_vec_peer(ord[j] + off0 + vv * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long vv = v + u * nth;
+      if (vv < nvec) sink(off0 + vv * 16, fold_vec<T, EXACT>(x[u], n, smode, sval));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Local copy helper: dst[i] = scale(src[i]) for i in [0, numel), all blocks of this rank.
 template <typename T>
@@ -151,8 +187,8 @@ __device__ __forceinline__ void local_copy(char* dst, const char* src, long long
 // Two-shot all-reduce, in place on buf[rank] (and therefore on every rank's buf).
 //   [copy local_in -> buf]  barrier  reduce own chunk from all peers, store it to all peers
 //   barrier  [copy buf -> local_out]
-template <typename T, bool EXACT>
-__global__ void __launch_bounds__(TB_COMM_THREADS)
+template <typename T, bool EXACT, int NR>
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
 k_allreduce_twoshot(CommCtx c, PeerPtrs buf, Locals lin, Locals lout, long long numel, int smode, float sval) {
   __shared__ int sh[2];
   if (threadIdx.x == 0) sh[1] = 0;
@@ -176,15 +212,11 @@ k_allreduce_twoshot(CommCtx c, PeerPtrs buf, Locals lin, Locals lout, long long 
     if (head > hi - lo) head = hi - lo;
     long long nvec = (hi - lo - head) / N;
     long long body = lo + head;
-    for (long long v = tid; v < nvec; v += nth) {
-      const long long off = (body + v * N) * sizeof(T);
-      uint4 x[TB_MAX_RANKS];
-      load_ordered(buf, n, rank, off, x);
-      uint4 r = fold_vec<T, EXACT>(x, n, smode, sval);
+    fold_vectors<T, EXACT, NR>(buf, n, rank, body * (long long)sizeof(T), nvec, smode, sval, tid, nth, [&](long long off, const uint4& r) {
 #pragma unroll
       for (int q = 0; q < TB_MAX_RANKS; ++q)
-        if (q < n) st_vec(buf.p[q] + off, r);
-    }
+        if (q < (NR ? NR : n)) st_vec(buf.p[q] + off, r);
+    });
     const long long ntail = (hi - lo) - nvec * N;  // head + tail elements
     for (long long t = tid; t < ntail; t += nth) {
       long long i = t < head ? lo + t : body + nvec * N + (t - head);
@@ -204,7 +236,7 @@ k_allreduce_twoshot(CommCtx c, PeerPtrs buf, Locals lin, Locals lout, long long 
 // two scratch halves: a rank can only be one collective behind its peers.
 #define TB_ONESHOT_UNROLL 4
 template <typename T, bool EXACT>
-__global__ void __launch_bounds__(TB_COMM_THREADS)
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
 k_allreduce_oneshot(CommCtx c, PeerPtrs buf, Locals lin, Locals lout, long long numel, int smode, float sval) {
   __shared__ int sh[2];
   if (threadIdx.x == 0) sh[1] = 0;
@@ -282,8 +314,8 @@ __device__ __forceinline__ void adam_elem(const AdamArgs& a, long long j, float 
   if (a.shadow != nullptr) a.shadow[j] = __float2bfloat16_rn(p);
 }
 
-template <typename T, bool EXACT, int EPI>  // EPI 0: store only, 1: += into acc_out, 2: fused AdamW (T must be float)
-__global__ void __launch_bounds__(TB_COMM_THREADS)
+template <typename T, bool EXACT, int EPI, int NR>  // EPI 0: store only, 1: += into acc_out, 2: fused AdamW (T must be float)
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
 k_reduce_scatter(CommCtx c, PeerPtrs buf, Locals lin, long long numel, Bounds bounds, int smode, float sval, Locals acc,
                  AdamSet adams) {
   __shared__ int sh[2];
@@ -306,13 +338,10 @@ k_reduce_scatter(CommCtx c, PeerPtrs buf, Locals lin, long long numel, Bounds bo
     if (head > hi - lo) head = hi - lo;
     const long long nvec = (hi - lo - head) / N;
     const long long body = lo + head;
-    for (long long v = tid; v < nvec; v += nth) {
-      const long long i0 = body + v * N;
-      uint4 x[TB_MAX_RANKS];
-      load_ordered(buf, n, rank, i0 * sizeof(T), x);
-      uint4 r = fold_vec<T, EXACT>(x, n, smode, sval);
-      st_vec(buf.p[rank] + i0 * sizeof(T), r);
+    fold_vectors<T, EXACT, NR>(buf, n, rank, body * (long long)sizeof(T), nvec, smode, sval, tid, nth, [&](long long off, const uint4& r) {
+      st_vec(buf.p[rank] + off, r);
       if (EPI != 0) {
+        const long long i0 = off / (long long)sizeof(T);
         const T* e = reinterpret_cast<const T*>(&r);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
@@ -320,7 +349,7 @@ k_reduce_scatter(CommCtx c, PeerPtrs buf, Locals lin, long long numel, Bounds bo
           if (EPI == 2) adam_elem(adam, i0 - lo + j, to_f<T>(e[j]));
         }
       }
-    }
+    });
     const long long ntail = (hi - lo) - nvec * N;
     for (long long t = tid; t < ntail; t += nth) {
       long long i = t < head ? lo + t : body + nvec * N + (t - head);
@@ -344,7 +373,7 @@ struct GatherPlan {
   long long len[TB_MAX_RANKS];      // bytes
 };
 
-__global__ void __launch_bounds__(TB_COMM_THREADS)
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
 k_gather_pull(CommCtx c, PeerPtrs src, Locals dsts, GatherPlan plan, Locals stage, int sync) {
   __shared__ int sh[2];
   if (threadIdx.x == 0) sh[1] = 0;
@@ -371,7 +400,15 @@ k_gather_pull(CommCtx c, PeerPtrs src, Locals dsts, GatherPlan plan, Locals stag
       if (len <= 0 || s == d) continue;
       const bool al = (((uintptr_t)s | (uintptr_t)d) & 15) == 0;
       const long long nv = al ? len / 16 : 0;
-      for (long long v = tid; v < nv; v += nth) st_vec(d + v * 16, ld_vec_peer(s + v * 16));
+      for (long long v = tid; v < nv; v += nth * 8) {  // eight independent 16-byte loads in flight per thread
+        uint4 x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (v + u * nth < nv) x[u] = ld_vec_peer(s + (v + u * nth) * 16);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (v + u * nth < nv) st_vec(d + (v + u * nth) * 16, x[u]);
+      }
       for (long long i = nv * 16 + tid; i < len; i += nth) d[i] = *reinterpret_cast<volatile const char*>(s + i);
     }
   }
@@ -387,7 +424,7 @@ __global__ void k_barrier(CommCtx c) {
 
 // Generic element types (double, integers): one-shot over scalars, sum only.
 template <typename T>
-__global__ void __launch_bounds__(TB_COMM_THREADS)
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
 k_allreduce_generic(CommCtx c, PeerPtrs buf, Locals lin, Locals lout, long long numel, int divide, Bounds bounds,
                     int scatter_only) {
   __shared__ int sh[2];
@@ -592,8 +629,15 @@ int tb_all_reduce(TbComm* c, void* const* bufs, void* const* local_in, void* con
     ONE(__half, false);
 #undef ONE
   }
-  int blocks = blocks_for(c, bytes / c->ctx.n, (long long)TB_COMM_THREADS * 16 * 2);
-#define TWO(T, E) return (int)launch(c, k_allreduce_twoshot<T, E>, blocks, stream, c->ctx, buf, in, out, numel, smode, sval)
+  int blocks = blocks_for(c, bytes / c->ctx.n, (long long)TB_COMM_THREADS * 16 * 8);
+  const int nr = c->ctx.n;
+#define TWO(T, E)                                                                                                                    \
+  do {                                                                                                                               \
+    if (nr == 2) return (int)launch(c, k_allreduce_twoshot<T, E, 2>, blocks, stream, c->ctx, buf, in, out, numel, smode, sval);      \
+    if (nr == 4) return (int)launch(c, k_allreduce_twoshot<T, E, 4>, blocks, stream, c->ctx, buf, in, out, numel, smode, sval);      \
+    if (nr == 8) return (int)launch(c, k_allreduce_twoshot<T, E, 8>, blocks, stream, c->ctx, buf, in, out, numel, smode, sval);      \
+    return (int)launch(c, k_allreduce_twoshot<T, E, 0>, blocks, stream, c->ctx, buf, in, out, numel, smode, sval);                   \
+  } while (0)
   if (dtype == TB_F32) TWO(float, false);
   if (dtype == TB_BF16) {
     if (exact) TWO(__nv_bfloat16, true);
@@ -623,7 +667,8 @@ int tb_reduce_scatter(TbComm* c, void* const* bufs, void* const* local_in, long 
   int smode;
   float sval;
   scale_mode(c->ctx.n, average, &smode, &sval);
-  int blocks = blocks_for(c, most * elem_size(dtype), (long long)TB_COMM_THREADS * 16 * 2);
+  int blocks = blocks_for(c, most * elem_size(dtype), (long long)TB_COMM_THREADS * 16 * 8);
+  const int nr = c->ctx.n;
   if (dtype != TB_F32 && dtype != TB_BF16 && dtype != TB_F16) {
     if (acc_out != nullptr || adam != nullptr) return -3;
     Locals none{};
@@ -638,7 +683,13 @@ int tb_reduce_scatter(TbComm* c, void* const* bufs, void* const* local_in, long 
     }
 #undef GEN
   }
-#define RS(T, E, EPI) return (int)launch(c, k_reduce_scatter<T, E, EPI>, blocks, stream, c->ctx, buf, in, numel, bounds, smode, sval, acc, adams)
+#define RS(T, E, EPI)                                                                                                                      \
+  do {                                                                                                                                 \
+    if (nr == 2) return (int)launch(c, k_reduce_scatter<T, E, EPI, 2>, blocks, stream, c->ctx, buf, in, numel, bounds, smode, sval, acc, adams); \
+    if (nr == 4) return (int)launch(c, k_reduce_scatter<T, E, EPI, 4>, blocks, stream, c->ctx, buf, in, numel, bounds, smode, sval, acc, adams); \
+    if (nr == 8) return (int)launch(c, k_reduce_scatter<T, E, EPI, 8>, blocks, stream, c->ctx, buf, in, numel, bounds, smode, sval, acc, adams); \
+    return (int)launch(c, k_reduce_scatter<T, E, EPI, 0>, blocks, stream, c->ctx, buf, in, numel, bounds, smode, sval, acc, adams);    \
+  } while (0)
   if (dtype == TB_F32) {
     if (adam != nullptr) RS(float, false, 2);
     if (acc_out != nullptr) RS(float, false, 1);
@@ -675,7 +726,7 @@ int tb_gather_pull(TbComm* c, void* const* srcs, void* const* dsts, const long l
     plan.len[q] = len[q];
     if (len[q] > most) most = len[q];
   }
-  int blocks = blocks_for(c, most, (long long)TB_COMM_THREADS * 16 * 4);
+  int blocks = blocks_for(c, most, (long long)TB_COMM_THREADS * 16 * 8);
   return (int)launch(c, k_gather_pull, blocks, stream, c->ctx, src, locals(c, dsts), plan, locals(c, stage_in), sync);
 }
 

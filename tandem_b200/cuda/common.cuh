@@ -14,8 +14,14 @@
 
 #define TB_MAX_RANKS 8
 #define TB_MAX_BLOCKS 128
-#define TB_COMM_THREADS 512
+#define TB_COMM_THREADS 128
 
+// Launch shape of the communication kernels: many small blocks.  128 threads at no more than 85 registers
+// each (launch bounds of 6 blocks per SM) let a block share an SM with a resident GEMM CTA (320 threads x
+// 168 registers, ~225 KB of shared memory), so a collective overlaps backward without waiting for whole
+// SMs to drain; latency over NVLink is covered by each thread keeping eight independent 16-byte loads in
+// flight.
+//
 // Everything a communication kernel needs to know about the group.  In a real
 // multi-GPU run gridDim.y == 1 and this GPU is `rank0`.  For single-GPU tests of
 // the multi-rank logic all ranks' buffers live on one device and ONE cooperative

@@ -213,13 +213,25 @@ class SymmetricComm:
         self._status_host = host
         self._status = (ctypes.c_uint32 * 16).from_address(host.value)
         self.device_timeout = float(os.environ.get("TANDEM_DEVICE_TIMEOUT", str(min(group.timeout, 30.0))))
-        self.max_blocks = int(os.environ.get("TANDEM_COMM_BLOCKS", "32"))
+        self.max_blocks = int(os.environ.get("TANDEM_COMM_BLOCKS", "128"))
         epochs = [self._epoch.value if q == self.rank else None for q in range(self.n)]
         self.comm = self.lib.tb_comm_create(self.n, self.rank, 0, _ptr_array(flags), _ptr_array(epochs), dev,
                                             self.device_timeout, self.max_blocks)
+        # A second, independent set of flags and counters for blocking calls, which run in line on the
+        # caller's stream: kernels of the two channels may overlap on the GPU without sharing barrier state.
+        # (All blocking collectives of a rank must come from one stream at a time.)
+        seg2, off2 = self.heap.take(FLAG_BYTES)
+        self._epoch2 = ctypes.c_void_p()
+        check_rc(self.lib.tb_malloc(ctypes.byref(self._epoch2), MAX_BLOCKS * 4), "cudaMalloc")
+        epochs2 = [self._epoch2.value if q == self.rank else None for q in range(self.n)]
+        self.comm_inline = self.lib.tb_comm_create(self.n, self.rank, 0, _ptr_array(self.heap.peers(seg2, off2)),
+                                                   _ptr_array(epochs2), dev, self.device_timeout, self.max_blocks)
+        self._launch_comm = self.comm
         self.scratch_half = int(os.environ.get("TANDEM_SCRATCH_BYTES", str(32 << 20)))
         self._scratch = [self._take(self.scratch_half) for _ in range(2)]
         self._half = 0
+        self._launch_stream = self.stream
+        self._ptr_cache = {}
         self.exact16 = os.environ.get("TANDEM_EXACT16", "0") == "1"
         self.algo = ALGO[os.environ.get("TANDEM_ALLREDUCE", "auto")]
         # clock calibration for traces: device event time -> host perf_counter
@@ -268,26 +280,44 @@ class SymmetricComm:
         return t
 
     def free(self, t):
+        self._ptr_cache.clear()
         where = self.heap.locate(self.rank, t.data_ptr(), 1)
         if where is not None and where in self.heap.used:
             self.heap.give(*where)
 
     def _peers_of(self, t):
         """Peer addresses of a tensor that lives in the heap, else None."""
+        ptr = t.data_ptr()
         nbytes = max(t.numel() * t.element_size(), 1)
-        where = self.heap.locate(self.rank, t.data_ptr(), nbytes)
-        return None if where is None else self.heap.peers(*where)
+        hit = self._ptr_cache.get(ptr)
+        if hit is not None and hit[0] >= nbytes:
+            return hit[1]
+        where = self.heap.locate(self.rank, ptr, nbytes)
+        if where is None:
+            return None
+        peers = self.heap.peers(*where)
+        if len(self._ptr_cache) > 4096:
+            self._ptr_cache.clear()
+        self._ptr_cache[ptr] = (nbytes, peers)
+        return peers
 
     # ------------------------------------------------------------------ launching
-    def _begin(self, name, tensors):
-        """Orders the communication stream after the caller's stream; returns timing start or None."""
+    def _begin(self, name, tensors, async_op=True):
+        """Picks the stream for this collective and orders it after the caller's work.  A blocking
+        call runs on the caller's own stream (no events, no stream hop); an async one on the
+        high-priority communication stream.  Returns the timing start event or None."""
         cur = torch.cuda.current_stream(self.device)
+        registered = all(t is None or self._peers_of(t) is not None for t in tensors[:1])
+        if not async_op and not self.g.tracing and registered:
+            self._launch_stream, self._launch_comm = cur, self.comm_inline
+            return None
+        self._launch_stream, self._launch_comm = self.stream, self.comm
         ready = torch.cuda.Event()
         ready.record(cur)
         self.stream.wait_event(ready)
         for t in tensors:
             if t is not None and t.is_cuda and self._peers_of(t) is None:
-                t.record_stream(self.stream)
+                t.record_stream(self.stream)  # the caching allocator must not recycle it under the kernel
         if self.g.tracing:
             start = torch.cuda.Event(enable_timing=True)
             start.record(self.stream)
@@ -297,6 +327,10 @@ class SymmetricComm:
     def _end(self, name, start, result, nbytes, async_op):
         from ..comm import _StreamWork
 
+        if self._launch_stream is not self.stream:  # ran in line on the caller's stream: already ordered
+            if self._status[0] != 0:
+                self.check()
+            return result
         done = torch.cuda.Event(enable_timing=start is not None)
         done.record(self.stream)
         work = _StreamWork(name, self.g, done, result, nbytes, start)
@@ -327,14 +361,14 @@ class SymmetricComm:
 
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, flat, average, result, nbytes, async_op, algo=None):
-        start = self._begin("all_reduce", [flat])
+        start = self._begin("all_reduce", [flat], async_op)
         code = self._codes[flat.dtype]
         algo = self.algo if algo is None else ALGO[algo]
-        s = self.stream.cuda_stream
+        s = self._launch_stream.cuda_stream
         peers = self._peers_of(flat)
         if flat.numel() and self.n > 1:  # a group of one: the buffer already holds its own sum (and mean)
             if peers is not None:
-                check_rc(self.lib.tb_all_reduce(self.comm, _ptr_array(peers), None, None, flat.numel(), code, int(average),
+                check_rc(self.lib.tb_all_reduce(self._launch_comm, _ptr_array(peers), None, None, flat.numel(), code, int(average),
                                                 int(self.exact16), algo, s), "all_reduce")
             else:
                 esz = flat.element_size()
@@ -342,7 +376,7 @@ class SymmetricComm:
                 for lo in range(0, flat.numel(), step):
                     piece = flat[lo:lo + step]
                     local = _ptr_array([piece.data_ptr()])
-                    check_rc(self.lib.tb_all_reduce(self.comm, _ptr_array(self._next_scratch()), local, local, piece.numel(),
+                    check_rc(self.lib.tb_all_reduce(self._launch_comm, _ptr_array(self._next_scratch()), local, local, piece.numel(),
                                                     code, int(average), int(self.exact16), algo, s), "all_reduce")
         return self._end("all_reduce", start, result, nbytes, async_op)
 
@@ -350,23 +384,23 @@ class SymmetricComm:
         """Chunk r of `flat` summed over ranks into rank r's `flat` (in place).
         accumulate_into: a tensor shaped like the chunk that also receives `+= chunk`.
         adam: AdamArgs for a fused AdamW step with the chunk as the gradient."""
-        start = self._begin("reduce_scatter", [flat, accumulate_into])
+        start = self._begin("reduce_scatter", [flat, accumulate_into], async_op)
         code = self._codes[flat.dtype]
         offs = split_offsets(flat.numel(), self.n, sizes)
-        s = self.stream.cuda_stream
+        s = self._launch_stream.cuda_stream
         peers = self._peers_of(flat)
         acc = _ptr_array([accumulate_into.data_ptr()]) if accumulate_into is not None and accumulate_into.numel() else None
         adam_p = ctypes.pointer(adam) if adam is not None and offs[self.rank + 1] > offs[self.rank] else None
         if flat.numel():
             if peers is not None:
-                check_rc(self.lib.tb_reduce_scatter(self.comm, _ptr_array(peers), None, flat.numel(), _ll_array(offs), code,
+                check_rc(self.lib.tb_reduce_scatter(self._launch_comm, _ptr_array(peers), None, flat.numel(), _ll_array(offs), code,
                                                     int(average), int(self.exact16), acc, adam_p, s), "reduce_scatter")
             else:
                 if flat.numel() * flat.element_size() > self.scratch_half:
                     raise self._error("reduce_scatter of an unregistered tensor larger than the scratch area: "
                                       "allocate it with Group.empty() or raise TANDEM_SCRATCH_BYTES")
                 scratch = self._next_scratch()
-                check_rc(self.lib.tb_reduce_scatter(self.comm, _ptr_array(scratch), _ptr_array([flat.data_ptr()]),
+                check_rc(self.lib.tb_reduce_scatter(self._launch_comm, _ptr_array(scratch), _ptr_array([flat.data_ptr()]),
                                                     flat.numel(), _ll_array(offs), code, int(average), int(self.exact16),
                                                     acc, adam_p, s), "reduce_scatter")
                 lo, hi = offs[self.rank], offs[self.rank + 1]
@@ -377,12 +411,12 @@ class SymmetricComm:
         return self._end("reduce_scatter", start, result, nbytes, async_op)
 
     def _pull(self, srcs, dst, src_off, dst_off, lens, stage, sync):
-        check_rc(self.lib.tb_gather_pull(self.comm, _ptr_array(srcs), _ptr_array([dst]), _ll_array(src_off), _ll_array(dst_off),
+        check_rc(self.lib.tb_gather_pull(self._launch_comm, _ptr_array(srcs), _ptr_array([dst]), _ll_array(src_off), _ll_array(dst_off),
                                          _ll_array(lens), _ptr_array([stage]) if stage is not None else None, int(sync),
-                                         self.stream.cuda_stream), "gather")
+                                         self._launch_stream.cuda_stream), "gather")
 
     def all_gather(self, flat, sizes, result, nbytes, async_op):
-        start = self._begin("all_gather", [flat])
+        start = self._begin("all_gather", [flat], async_op)
         esz = flat.element_size()
         offs = [o * esz for o in split_offsets(flat.numel(), self.n, sizes)]
         lens = [offs[q + 1] - offs[q] for q in range(self.n)]
@@ -404,7 +438,7 @@ class SymmetricComm:
         synchronisation: `shard` is a heap tensor allocated identically on every rank
         whose contents only change between barriers (parameter shards between
         optimizer steps)."""
-        start = self._begin("all_gather", [full])
+        start = self._begin("all_gather", [full], async_op)
         esz = full.element_size()
         offs = [o * esz for o in split_offsets(full.numel(), self.n, sizes)]
         lens = [offs[q + 1] - offs[q] for q in range(self.n)]
@@ -415,7 +449,7 @@ class SymmetricComm:
         return self._end("all_gather", start, full, full.numel() * esz, async_op)
 
     def broadcast(self, flat, root, result, nbytes, async_op):
-        start = self._begin("broadcast", [flat])
+        start = self._begin("broadcast", [flat], async_op)
         total = flat.numel() * flat.element_size()
         peers = self._peers_of(flat)
         if total and self.n > 1:
@@ -434,7 +468,7 @@ class SymmetricComm:
     def device_barrier(self, after_current=False):
         """A barrier on the communication stream (ranks meet on the device, the host does not block).
         The caller's stream waits for it either way; it also waits for the caller's earlier work."""
-        start = self._begin("barrier", [])
+        start = self._begin("barrier", [], True)
         check_rc(self.lib.tb_barrier(self.comm, self.stream.cuda_stream), "barrier")
         return self._end("barrier", start, None, 0, False)
 
@@ -449,6 +483,8 @@ class SymmetricComm:
             self.lib.tb_free(p)
         self._owned = []
         self.lib.tb_free(self._epoch)
+        self.lib.tb_free(self._epoch2)
+        self.lib.tb_comm_destroy(self.comm_inline)
         self.lib.tb_status_free(self._status_host)
         self.lib.tb_comm_destroy(self.comm)
         self.comm = None
