@@ -300,7 +300,7 @@ class Group:
     def fused(self):
         """True when collectives run as GPU kernels that accept fused epilogues
         (reduce_scatter's accumulate_into= / adam=) and sync-free shard gathers."""
-        return self._sym is not None
+        return self._sym is not None and os.environ.get("TANDEM_FUSED", "1") != "0"
 
     def reduce_scatter(self, t, sizes=None, op="sum", async_op=False, accumulate_into=None, adam=None):
         """Sums `t` across ranks; rank r's chunk (chunk r of torch.tensor_split,

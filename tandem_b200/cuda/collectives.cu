@@ -364,9 +364,11 @@ k_reduce_scatter(CommCtx c, PeerPtrs buf, Locals lin, long long numel, Bounds bo
 
 // ---------------------------------------------------------------------------------------------
 // Gather by pulling: dst (local) receives src.p[q][src_off[q] : +len[q]) at dst_off[q] for
-// every q.  With sync != 0 a barrier precedes the reads (the sources were written
+// every q.  sync == 1: a barrier precedes the reads (the sources were written
 // by this step's kernels) and one follows them (the sources may be overwritten next).
-// Parameter shards that only change at optimizer steps are pulled with sync == 0.
+// sync == 2: no handshake, only a system-scope fence before the reads -- for sources that change only
+// between barriers issued elsewhere (parameter shards between optimizer steps); the fence is what makes
+// the loads observe the peers' latest stores.  sync == 0: neither.
 struct GatherPlan {
   long long src_off[TB_MAX_RANKS];  // bytes
   long long dst_off[TB_MAX_RANKS];  // bytes
@@ -390,7 +392,8 @@ k_gather_pull(CommCtx c, PeerPtrs src, Locals dsts, GatherPlan plan, Locals stag
     for (long long v = tid; v < nv; v += nth) st_vec(s + v * 16, ld_vec(stage_in + v * 16));
     for (long long i = nv * 16 + tid; i < stage_bytes; i += nth) s[i] = stage_in[i];
   }
-  if (sync) comm_barrier(c, sh);
+  if (sync == 1) comm_barrier(c, sh);
+  if (sync == 2) __threadfence_system();
   if (!sh[1]) {
     for (int j = 0; j < n; ++j) {
       const int q = (rank + j) % n;  // start at home, then walk the peers: spreads load over the switch
@@ -412,7 +415,7 @@ k_gather_pull(CommCtx c, PeerPtrs src, Locals dsts, GatherPlan plan, Locals stag
       for (long long i = nv * 16 + tid; i < len; i += nth) d[i] = *reinterpret_cast<volatile const char*>(s + i);
     }
   }
-  if (sync) comm_barrier(c, sh);
+  if (sync == 1) comm_barrier(c, sh);
 }
 
 // A barrier and nothing else (one block per rank).
@@ -586,7 +589,10 @@ int tb_barrier(TbComm* c, cudaStream_t stream) {
 
 // bufs[q]: rank q's copy of the symmetric buffer (same offset in every rank's heap).
 // local_in / local_out: optional arrays (one entry; n entries when emulated) of private tensors
-// to stage through the buffer: in -> buf before the reduction, buf -> out after it.
+// to stage through the buffer: in -> buf before the reduction, buf -> out after it.  Only valid
+// for single-block launches: a block synchronises with the peers' block of the same index, not with
+// their whole grid, so with several blocks a peer could read a part of the buffer that another block
+// has not copied in yet.  Multi-block callers stage with separate copies before and after the call.
 int tb_all_reduce(TbComm* c, void* const* bufs, void* const* local_in, void* const* local_out, long long numel, int dtype,
                   int average, int exact, int algo, cudaStream_t stream) {
   if (numel <= 0) return 0;
@@ -715,8 +721,10 @@ int tb_reduce_scatter(TbComm* c, void* const* bufs, void* const* local_in, long 
 
 // Every rank's dst receives, for every rank q, len[q] bytes from srcs[q] + src_off[q] at dst + dst_off[q].
 // stage_in (array like dsts, entries may be null): first copy len[rank] bytes from it to srcs[rank] + src_off[rank].
+// grid_bytes: what the grid is sized for.  Every rank must pass the same value (ranks synchronise block by
+// block, so their grids must match even when their plans differ); 0 means "the largest len[q]".
 int tb_gather_pull(TbComm* c, void* const* srcs, void* const* dsts, const long long* src_off, const long long* dst_off,
-                   const long long* len, void* const* stage_in, int sync, cudaStream_t stream) {
+                   const long long* len, void* const* stage_in, int sync, long long grid_bytes, cudaStream_t stream) {
   PeerPtrs src = peers(c, srcs);
   GatherPlan plan{};
   long long most = 0;
@@ -726,7 +734,7 @@ int tb_gather_pull(TbComm* c, void* const* srcs, void* const* dsts, const long l
     plan.len[q] = len[q];
     if (len[q] > most) most = len[q];
   }
-  int blocks = blocks_for(c, most, (long long)TB_COMM_THREADS * 16 * 8);
+  int blocks = blocks_for(c, grid_bytes > 0 ? grid_bytes : most, (long long)TB_COMM_THREADS * 16 * 8);
   return (int)launch(c, k_gather_pull, blocks, stream, c->ctx, src, locals(c, dsts), plan, locals(c, stage_in), sync);
 }
 

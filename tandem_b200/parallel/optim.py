@@ -11,6 +11,11 @@ roundings in the same order.
 
 state[key] = [step (float), exp_avg, exp_avg_sq]; key is "flat" for ZeRO-1/2 and
 the unit index for FSDP.
+
+Mixed precision: a 16-bit shard is never updated in its own precision.  The
+optimizer keeps an fp32 master copy of the shard (master[key]) and fp32 moments,
+steps those, and writes the shard back as the rounded copy of the master, in the
+same kernel on a GPU.  (The reference trains in fp32 only.)
 """
 
 import torch
@@ -19,12 +24,16 @@ import torch
 class ShardedAdamW:
     def __init__(self, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, fused=None):
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
-        self.fused = fused  # None: fused kernel on CUDA fp32 shards, torch ops elsewhere
+        self.fused = fused  # None: fused kernel on CUDA shards, torch ops elsewhere
         self.state = {}
+        self.master = {}  # key -> fp32 copy of a 16-bit shard
 
     def _state(self, key, param):
         if key not in self.state:
-            self.state[key] = [0.0, torch.zeros_like(param), torch.zeros_like(param)]
+            like = param if param.dtype in (torch.float32, torch.float64) else param.float()
+            self.state[key] = [0.0, torch.zeros_like(like), torch.zeros_like(like)]
+            if like is not param:
+                self.master[key] = like  # param.float() made a fresh fp32 copy
         return self.state[key]
 
     def scalars(self, step):
@@ -43,12 +52,30 @@ class ShardedAdamW:
         step, exp_avg, exp_avg_sq = st
         if param.numel() == 0:
             return
+        master = self.master.get(key)
+        if master is not None:  # 16-bit shard: step the fp32 master, write the shard back rounded
+            if param.is_cuda and param.dtype == torch.bfloat16 and self.fused is not False:
+                from ..ops import fused_adamw
+
+                g = grad if grad.dtype in (torch.bfloat16, torch.float32) else grad.float()
+                fused_adamw(master, g, exp_avg, exp_avg_sq, self.scalars(step), self.weight_decay != 0, param)
+            else:
+                self._torch_update(master, grad.float(), exp_avg, exp_avg_sq, step)
+                param.copy_(master)
+            if shadow is not None:
+                shadow.copy_(param)
+            return
         use_kernel = self.fused if self.fused is not None else (param.is_cuda and param.dtype == torch.float32)
         if use_kernel:
             from ..ops import fused_adamw
 
             fused_adamw(param, grad, exp_avg, exp_avg_sq, self.scalars(step), self.weight_decay != 0, shadow)
             return
+        self._torch_update(param, grad, exp_avg, exp_avg_sq, step)
+        if shadow is not None:
+            shadow.copy_(param)
+
+    def _torch_update(self, param, grad, exp_avg, exp_avg_sq, step):
         decay, w1, b2, w2, bias2_sqrt, eps, neg_step = self.scalars(step)
         if self.weight_decay != 0:
             param.mul_(decay)
@@ -56,8 +83,6 @@ class ShardedAdamW:
         exp_avg_sq.mul_(b2).addcmul_(grad, grad, value=w2)
         denom = (exp_avg_sq.sqrt() / bias2_sqrt).add_(eps)
         param.addcdiv_(exp_avg, denom, value=neg_step)
-        if shadow is not None:
-            shadow.copy_(param)
 
     def state_bytes(self):
         return sum(t.numel() * t.element_size() for _, m, v in self.state.values() for t in (m, v))
@@ -66,7 +91,8 @@ class ShardedAdamW:
     def state_dict(self):
         return {"hyper": {"lr": self.lr, "betas": tuple(self.betas), "eps": self.eps, "weight_decay": self.weight_decay},
                 "state": {k: {"step": s, "exp_avg": m.detach().cpu().clone(), "exp_avg_sq": v.detach().cpu().clone()}
-                          for k, (s, m, v) in self.state.items()}}
+                          for k, (s, m, v) in self.state.items()},
+                "master": {k: t.detach().cpu().clone() for k, t in self.master.items()}}
 
     def load_state_dict(self, sd, device=None):
         h = sd["hyper"]
@@ -75,3 +101,4 @@ class ShardedAdamW:
         for k, e in sd["state"].items():
             dev = device if device is not None else e["exp_avg"].device
             self.state[k] = [float(e["step"]), e["exp_avg"].to(dev).clone(), e["exp_avg_sq"].to(dev).clone()]
+        self.master = {k: t.to(device if device is not None else t.device).clone() for k, t in sd.get("master", {}).items()}

@@ -80,7 +80,7 @@ def cuda_lib():
         "tb_barrier": ([vp, vp], i),
         "tb_all_reduce": ([vp, pp, pp, pp, ll, i, i, i, i, vp], i),
         "tb_reduce_scatter": ([vp, pp, pp, ll, pll, i, i, i, pp, ctypes.POINTER(AdamArgs), vp], i),
-        "tb_gather_pull": ([vp, pp, pp, pll, pll, pll, pp, i, vp], i),
+        "tb_gather_pull": ([vp, pp, pp, pll, pll, pll, pp, i, ll, vp], i),
         "tb_adamw": ([vp, vp, i, vp, vp, vp, ll, ctypes.POINTER(f), i, f, vp], i),
         "tb_multi_copy": ([pp, pp, pll, i, vp], i),
         "tb_adam_prepare": ([vp, d, d, d, d, d, vp, vp], i),
@@ -371,13 +371,19 @@ class SymmetricComm:
                 check_rc(self.lib.tb_all_reduce(self._launch_comm, _ptr_array(peers), None, None, flat.numel(), code, int(average),
                                                 int(self.exact16), algo, s), "all_reduce")
             else:
+                # Not in the heap: copy each piece into this rank's scratch, reduce the scratch in place, copy
+                # it back.  (The copies are separate launches on purpose: a block of the collective may only
+                # assume that the peers' matching block has run, not that their whole grid has.)
                 esz = flat.element_size()
                 step = self.scratch_half // esz
                 for lo in range(0, flat.numel(), step):
                     piece = flat[lo:lo + step]
-                    local = _ptr_array([piece.data_ptr()])
-                    check_rc(self.lib.tb_all_reduce(self._launch_comm, _ptr_array(self._next_scratch()), local, local, piece.numel(),
+                    scratch = self._next_scratch()
+                    pbytes = piece.numel() * esz
+                    check_rc(self.lib.tb_memcpy_async(scratch[self.rank], piece.data_ptr(), pbytes, s), "memcpy")
+                    check_rc(self.lib.tb_all_reduce(self._launch_comm, _ptr_array(scratch), None, None, piece.numel(),
                                                     code, int(average), int(self.exact16), algo, s), "all_reduce")
+                    check_rc(self.lib.tb_memcpy_async(piece.data_ptr(), scratch[self.rank], pbytes, s), "memcpy")
         return self._end("all_reduce", start, result, nbytes, async_op)
 
     def reduce_scatter(self, flat, sizes, average, result, nbytes, async_op, accumulate_into=None, adam=None):
@@ -400,7 +406,8 @@ class SymmetricComm:
                     raise self._error("reduce_scatter of an unregistered tensor larger than the scratch area: "
                                       "allocate it with Group.empty() or raise TANDEM_SCRATCH_BYTES")
                 scratch = self._next_scratch()
-                check_rc(self.lib.tb_reduce_scatter(self._launch_comm, _ptr_array(scratch), _ptr_array([flat.data_ptr()]),
+                check_rc(self.lib.tb_memcpy_async(scratch[self.rank], flat.data_ptr(), flat.numel() * flat.element_size(), s), "memcpy")
+                check_rc(self.lib.tb_reduce_scatter(self._launch_comm, _ptr_array(scratch), None,
                                                     flat.numel(), _ll_array(offs), code, int(average), int(self.exact16),
                                                     acc, adam_p, s), "reduce_scatter")
                 lo, hi = offs[self.rank], offs[self.rank + 1]
@@ -410,10 +417,14 @@ class SymmetricComm:
                                                       (hi - lo) * esz, s), "memcpy")
         return self._end("reduce_scatter", start, result, nbytes, async_op)
 
-    def _pull(self, srcs, dst, src_off, dst_off, lens, stage, sync):
+    def _pull(self, srcs, dst, src_off, dst_off, lens, stage, sync, grid_bytes=0):
+        """stage: address of this rank's piece to publish first (copied to srcs[rank] + src_off[rank] by a
+        separate launch, so that it is complete before any peer's block can pass the barrier)."""
+        s = self._launch_stream.cuda_stream
+        if stage is not None and lens[self.rank] > 0:
+            check_rc(self.lib.tb_memcpy_async(srcs[self.rank] + src_off[self.rank], stage, lens[self.rank], s), "memcpy")
         check_rc(self.lib.tb_gather_pull(self._launch_comm, _ptr_array(srcs), _ptr_array([dst]), _ll_array(src_off), _ll_array(dst_off),
-                                         _ll_array(lens), _ptr_array([stage]) if stage is not None else None, int(sync),
-                                         self._launch_stream.cuda_stream), "gather")
+                                         _ll_array(lens), None, int(sync), grid_bytes, s), "gather")
 
     def all_gather(self, flat, sizes, result, nbytes, async_op):
         start = self._begin("all_gather", [flat], async_op)
@@ -435,9 +446,11 @@ class SymmetricComm:
 
     def gather_shards(self, full, shard, sizes, async_op=True):
         """full[off_q : off_q + sizes[q]] = rank q's `shard`, for every q, with no
-        synchronisation: `shard` is a heap tensor allocated identically on every rank
-        whose contents only change between barriers (parameter shards between
-        optimizer steps)."""
+        handshake between ranks: `shard` is a heap tensor allocated identically on
+        every rank whose contents only change between barriers (parameter shards
+        between optimizer steps).  The kernel still opens with a system-scope fence:
+        measured on B200, without it loads of a peer's memory can return lines from
+        before the peer's last update even though a barrier kernel ran in between."""
         start = self._begin("all_gather", [full], async_op)
         esz = full.element_size()
         offs = [o * esz for o in split_offsets(full.numel(), self.n, sizes)]
@@ -445,7 +458,7 @@ class SymmetricComm:
         peers = self._peers_of(shard)
         if peers is None:
             raise self._error("gather_shards needs a shard allocated with Group.empty()")
-        self._pull(peers, full.data_ptr(), [0] * self.n, offs[:-1], lens, None, False)
+        self._pull(peers, full.data_ptr(), [0] * self.n, offs[:-1], lens, None, 2, max(lens))  # 2: fence, no handshake
         return self._end("all_gather", start, full, full.numel() * esz, async_op)
 
     def broadcast(self, flat, root, result, nbytes, async_op):
@@ -454,15 +467,25 @@ class SymmetricComm:
         peers = self._peers_of(flat)
         if total and self.n > 1:
             if peers is not None:
-                lens = [total if q == root else 0 for q in range(self.n)]
-                self._pull(peers, flat.data_ptr(), [0] * self.n, [0] * self.n, lens, None, True)
+                if total >= (1 << 20) and self.n > 2:
+                    # scatter + all-gather: rank q pulls slice q from the root, then everyone pulls the other
+                    # slices from their new holders, so the root sends each byte once instead of n-1 times.
+                    cut = [(total * q // self.n) // 16 * 16 for q in range(self.n)] + [total]
+                    lens = [cut[self.rank + 1] - cut[self.rank] if q == root else 0 for q in range(self.n)]
+                    widest = max(cut[q + 1] - cut[q] for q in range(self.n))  # the same on every rank: grids must match
+                    self._pull(peers, flat.data_ptr(), [cut[self.rank]] * self.n, [cut[self.rank]] * self.n, lens, None, True, widest)
+                    lens = [0 if self.rank == root or q == self.rank else cut[q + 1] - cut[q] for q in range(self.n)]
+                    self._pull(peers, flat.data_ptr(), cut[:-1], cut[:-1], lens, None, True, widest)
+                else:
+                    lens = [total if q == root else 0 for q in range(self.n)]
+                    self._pull(peers, flat.data_ptr(), [0] * self.n, [0] * self.n, lens, None, True, total)
             else:
                 step = self.scratch_half
                 for lo in range(0, total, step):
                     plen = min(step, total - lo)
                     lens = [plen if q == root else 0 for q in range(self.n)]
                     stage = flat.data_ptr() + lo if self.rank == root else None
-                    self._pull(self._next_scratch(), flat.data_ptr(), [0] * self.n, [lo] * self.n, lens, stage, True)
+                    self._pull(self._next_scratch(), flat.data_ptr(), [0] * self.n, [lo] * self.n, lens, stage, True, plen)
         return self._end("broadcast", start, result, nbytes, async_op)
 
     def device_barrier(self, after_current=False):
@@ -513,30 +536,27 @@ class EmulatedRanks:
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 
-    def all_reduce(self, bufs, average=False, exact=False, algo="auto", staged=None):
-        """bufs: one symmetric buffer per rank.  staged: per-rank private tensors
-        to reduce through them (in place) instead."""
+    def all_reduce(self, bufs, average=False, exact=False, algo="auto"):
+        """bufs: one symmetric buffer per rank, reduced in place."""
         code = {torch.float32: 0, torch.float64: 1, torch.bfloat16: 2, torch.float16: 3, torch.int64: 4, torch.int32: 5}[bufs[0].dtype]
-        numel = (staged or bufs)[0].numel()
-        loc = _ptr_array([t.data_ptr() for t in staged]) if staged else None
-        check_rc(self.lib.tb_all_reduce(self.comm, _ptr_array([b.data_ptr() for b in bufs]), loc, loc, numel, code,
+        numel = bufs[0].numel()
+        check_rc(self.lib.tb_all_reduce(self.comm, _ptr_array([b.data_ptr() for b in bufs]), None, None, numel, code,
                                         int(average), int(exact), ALGO[algo], self._stream()), "all_reduce")
 
-    def reduce_scatter(self, bufs, sizes=None, average=False, exact=False, accumulate_into=None, adam=None, staged=None):
+    def reduce_scatter(self, bufs, sizes=None, average=False, exact=False, accumulate_into=None, adam=None):
         code = {torch.float32: 0, torch.float64: 1, torch.bfloat16: 2, torch.float16: 3, torch.int64: 4, torch.int32: 5}[bufs[0].dtype]
-        numel = (staged or bufs)[0].numel()
+        numel = bufs[0].numel()
         offs = split_offsets(numel, self.n, sizes)
         acc = _ptr_array([t.data_ptr() for t in accumulate_into]) if accumulate_into else None
         ad = (AdamArgs * self.n)(*adam) if adam else None
-        loc = _ptr_array([t.data_ptr() for t in staged]) if staged else None
-        check_rc(self.lib.tb_reduce_scatter(self.comm, _ptr_array([b.data_ptr() for b in bufs]), loc, numel, _ll_array(offs),
+        check_rc(self.lib.tb_reduce_scatter(self.comm, _ptr_array([b.data_ptr() for b in bufs]), None, numel, _ll_array(offs),
                                             code, int(average), int(exact), acc, ad, self._stream()), "reduce_scatter")
         return offs
 
     def gather(self, srcs, dsts, src_off, dst_off, lens, stage=None, sync=True):
         st = _ptr_array([t.data_ptr() if t is not None else None for t in stage]) if stage else None
         check_rc(self.lib.tb_gather_pull(self.comm, _ptr_array([t.data_ptr() for t in srcs]), _ptr_array([t.data_ptr() for t in dsts]),
-                                         _ll_array(src_off), _ll_array(dst_off), _ll_array(lens), st, int(sync),
+                                         _ll_array(src_off), _ll_array(dst_off), _ll_array(lens), st, int(sync), 0,
                                          self._stream()), "gather")
 
     def barrier(self):

@@ -93,22 +93,6 @@ def test_all_reduce_generic_dtypes(emu, n, dtype):
     assert all(torch.equal(b, want) for b in bufs)
 
 
-@pytest.mark.parametrize("n", [2, 4])
-@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
-def test_all_reduce_staged_through_scratch(emu, n, algo):
-    """Private (unregistered) tensors: copy-in, reduction and copy-out in one kernel."""
-    e = emu(n)
-    numel = 30_001
-    xs = [torch.randn(numel + 1, device="cuda")[1:] for _ in range(n)]  # 4-byte aligned only
-    staged = [x.clone() for x in xs]
-    staged = [s[:] for s in staged]
-    scratch = [torch.zeros(numel + 64, device="cuda") for _ in range(n)]
-    e.all_reduce(scratch, average=True, algo=algo, staged=staged)
-    want, _ = expected_fold(xs, True)
-    for r in range(n):
-        assert torch.equal(staged[r], want)
-
-
 @pytest.mark.parametrize("n", [2, 3, 4, 8])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_reduce_scatter_uneven_with_accumulate(emu, n, dtype):
