@@ -191,3 +191,23 @@ def test_gpt_on_b200_kernels_tracks_torch_path():
         g, w = pk.grad.float(), pr.grad
         denom = w.norm().clamp_min(1e-6)
         assert ((g - w).norm() / denom).item() < 6e-2, (name, ((g - w).norm() / denom).item())
+
+
+@pytest.mark.parametrize("B,T,H,hd", [(2, 128, 2, 64), (2, 512, 3, 64), (1, 256, 2, 128)])
+def test_causal_attention_matches_fp32(B, T, H, hd):
+    from tandem_b200 import ops
+    from tandem_b200.ops.attention import attention_error
+
+    d = H * hd
+    qkv = rnd(B, T, 3 * d).requires_grad_()
+    y = ops.causal_attention(qkv, H)
+    dy = rnd(B, T, d)
+    y.backward(dy)
+    ref = qkv.detach().float().requires_grad_()
+    q, k, v = (z.view(B, T, H, hd).transpose(1, 2) for z in ref.split(d, dim=2))
+    yf = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, T, d)
+    yf.backward(dy.float())
+    torch.cuda.synchronize()
+    assert not attention_error(), "an attention wait ran out"
+    close(y, yf, rtol=2e-2, atol=1e-2)
+    close(qkv.grad, ref.grad, rtol=4e-2, atol=2e-2)
