@@ -62,7 +62,51 @@ struct GemmArgs {
   int* error;                    // host-mapped; set to 1 when a wait runs out
 };
 
+// All-gather fused into the GEMM (B operand = a weight whose flat bytes are sharded over the ranks).
+// Two extra warps per CTA pull the weight, chunk by chunk, from the owners' shard memory (plain 16-byte
+// loads over NVLink from peer pointers) into this GPU's buffer and publish one flag per chunk; the TMA
+// producer waits for the flags that cover a tile's weight panel before it loads it -- from local memory,
+// never from the peer, and without multicast.  Transfer and math overlap panel by panel inside ONE
+// kernel, launched cooperatively so that every CTA (hence every chunk's fetcher) is resident.
+struct GatherArgs {
+  const char* shard[8];   // shard[q]: rank q's shard as mapped here; its byte 0 is byte shard_lo[q] of the unit's flat buffer
+  long long shard_lo[8];  // byte ranges of the shards within the unit's flat buffer
+  long long shard_hi[8];
+  char* full;             // this GPU's copy of the unit's flat buffer; the weight occupies [w_off, w_off + w_bytes)
+  long long w_off, w_bytes;
+  uint32_t* ready;        // one word per chunk of the weight; chunk c is complete once ready[c] == epoch
+  uint32_t epoch;
+  int n;                  // ranks
+  int chunk_bytes;
+  int n_start;            // the n-panel this rank visits first (the one its own shard feeds)
+};
+
 using namespace tc;
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait for chunk flags [c_lo, c_hi] to reach `epoch`.
+__device__ __forceinline__ bool wait_chunks(const uint32_t* ready, int c_lo, int c_hi, uint32_t epoch, int* error) {
+  const long long start = clock64();
+  for (int c = c_lo; c <= c_hi; ++c) {
+    while (ld_acquire_gpu(ready + c) != epoch) {
+      if (clock64() - start > (1ll << WAIT_LIMIT_CYCLES_SHIFT)) {
+        *error = 1;
+        __threadfence_system();
+        return false;
+      }
+    }
+  }
+  return true;
+}
 
 __device__ __forceinline__ float gelu_exact(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f)); }
 
@@ -309,9 +353,9 @@ struct SmemLayout {
   static constexpr int THREADS = 64 + 256;  // producer warp, MMA warp, eight epilogue warps
 };
 
-template <int BM, int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(320, 1)
-k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+template <int BM, int BN, bool A_MN, bool B_MN, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? 384 : 320, 1)
+k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g, const GatherArgs ga) {
   extern __shared__ uint8_t smem_raw[];
   using L = SmemLayout<BM, BN>;
   constexpr int STAGES = L::STAGES;
@@ -328,6 +372,14 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (g.K + BK - 1) / BK;
   constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: a power of two
+  // Tile t -> (m0, n0).  m runs fastest, so the CTAs sweep one weight panel at a time; with GATHER the panels
+  // are visited starting from the one this rank's own shard feeds, the order in which the chunks arrive.
+  auto tile_origin = [&](int tile, int* m0, int* n0) {
+    int n_idx = tile / tiles_m;
+    if (GATHER) n_idx = (n_idx + ga.n_start) % tiles_n;
+    *m0 = (tile % tiles_m) * BM;
+    *n0 = n_idx * BN;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -355,7 +407,14 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        int m0, n0;
+        tile_origin(tile, &m0, &n0);
+        if (GATHER) {  // the panel's bytes must have arrived (they are row-contiguous: rows n0 .. n0+BN of [N, K])
+          const long long lo = (long long)n0 * g.K * 2;
+          long long hi = (long long)(n0 + BN < g.N ? n0 + BN : g.N) * g.K * 2;
+          if (!(ok = wait_chunks(ga.ready, (int)(lo / ga.chunk_bytes), (int)((hi - 1) / ga.chunk_bytes), ga.epoch, g.error))) break;
+          asm volatile("fence.proxy.async;" ::: "memory");  // the fetchers' generic-proxy stores, then TMA's async-proxy loads
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
@@ -425,8 +484,44 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
         }
       }
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue (warps 2 and up)
+  } else if (GATHER && warp >= 10) {
+    // ------------------------------------------------------------------ weight fetchers (warps 10, 11)
+    const int ft = threadIdx.x - 320;  // 0..63
+    const int nchunks = (int)((ga.w_bytes + ga.chunk_bytes - 1) / ga.chunk_bytes);
+    const int first = (int)(((long long)ga.n_start * BN * g.K * 2) / ga.chunk_bytes);
+    __threadfence_system();  // observe the owners' latest stores to their shards
+    for (int ci = blockIdx.x; ci < nchunks; ci += gridDim.x) {
+      const int c = (first + ci) % nchunks;
+      const long long c0 = ga.w_off + (long long)c * ga.chunk_bytes;
+      const long long c1 = ga.w_off + ((long long)(c + 1) * ga.chunk_bytes < ga.w_bytes ? (long long)(c + 1) * ga.chunk_bytes : ga.w_bytes);
+      for (int q = 0; q < ga.n; ++q) {
+        const long long lo = c0 > ga.shard_lo[q] ? c0 : ga.shard_lo[q];
+        const long long hi = c1 < ga.shard_hi[q] ? c1 : ga.shard_hi[q];
+        if (lo >= hi) continue;
+        const char* src = ga.shard[q] + (lo - ga.shard_lo[q]);
+        char* dst = ga.full + lo;
+        const long long len = hi - lo;
+        const bool al = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+        const long long nv = al ? len / 16 : 0;
+        for (long long v = ft; v < nv; v += 64 * 4) {  // four independent 16-byte loads in flight per thread
+          uint4 x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v + u * 64 < nv)
+              asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(x[u].x), "=r"(x[u].y), "=r"(x[u].z), "=r"(x[u].w) : "l"(src + (v + u * 64) * 16));
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v + u * 64 < nv) *reinterpret_cast<uint4*>(dst + (v + u * 64) * 16) = x[u];
+        }
+        for (long long i = nv * 16 + ft; i < len; i += 64) dst[i] = *reinterpret_cast<volatile const char*>(src + i);
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 64;" ::: "memory");  // the two fetch warps only
+      if (ft == 0) st_release_gpu(ga.ready + c, ga.epoch);
+    }
+  } else if (warp < 10) {
+    // ------------------------------------------------------------------ epilogue (warps 2 .. 9)
     // Eight epilogue warps in two groups of four (one warp per TMEM lane quarter in each group).
     // BM = 128: both groups drain the same accumulator, each taking half of its columns.
     // BM = 256: group h drains the accumulator of rows [128h, 128h + 128).
@@ -437,7 +532,8 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
     bool ok = true;
     const bool out_f32 = g.flags & EPI_OUT_F32;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      int m0, n0;
+      tile_origin(tile, &m0, &n0);
       const uint32_t buf = BM == 128 ? (local_tile & 1) : half;
       const uint32_t acc_phase = BM == 128 ? ((local_tile >> 1) & 1) : (local_tile & 1);
       ok = mbar_wait(&acc_full[buf], acc_phase, g.error);
@@ -549,7 +645,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   int ctas = tiles < g_sm_count ? tiles : g_sm_count;
   if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
-  kernel<<<ctas, L::THREADS, L::TOTAL, stream>>>(ma, mb, g);
+  kernel<<<ctas, L::THREADS, L::TOTAL, stream>>>(ma, mb, g, GatherArgs{});
   return (int)cudaGetLastError();
 }
 
@@ -630,6 +726,61 @@ int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, i
   if (BN == 256) GO(128, 256);
   GO(128, 128);
 #undef GO
+}
+
+// out[M, N] = A[M, K] . W[N, K]^T (+ epilogue) where W is gathered by the kernel itself: rank q's shard (peer
+// address shards[q]) holds bytes [shard_lo[q], shard_hi[q]) of the unit's flat buffer; W is the byte range
+// [w_off, w_off + N*K*2) of it and is assembled in `full` (this GPU's copy) while the GEMM runs.
+// ready: one zero-initialised word per chunk (ceil(N*K*2 / chunk_bytes)); epoch: a value not used by an earlier
+// call on the same words.  One cooperative launch; returns a CUDA error if the grid cannot be co-resident.
+int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int ldc, int flags, const void* bias, const void* aux_in,
+                     void* aux_out, void* const* shards, const long long* shard_lo, const long long* shard_hi, int n_ranks, void* full,
+                     long long w_off, void* ready, unsigned epoch, int chunk_bytes, int n_start, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (K & 7) || (w_off & 15) || (((uintptr_t)A | (uintptr_t)full) & 15) || n_ranks < 1 || n_ranks > 8) return -12;
+  if (g_error_host == nullptr) {
+    if (cudaHostAlloc((void**)&g_error_host, 64, cudaHostAllocMapped) != cudaSuccess) return -13;
+    *g_error_host = 0;
+    if (cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0) != cudaSuccess) return -13;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  constexpr int BM = 128, BN = 256;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, A, K, M, lda, 64, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, (const char*)full + w_off, K, N, K, 64, BN);
+  if (rc) return rc;
+  GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev};
+  GatherArgs ga{};
+  for (int q = 0; q < n_ranks; ++q) {
+    ga.shard[q] = (const char*)shards[q];
+    ga.shard_lo[q] = shard_lo[q];
+    ga.shard_hi[q] = shard_hi[q];
+  }
+  ga.full = (char*)full;
+  ga.w_off = w_off;
+  ga.w_bytes = (long long)N * K * 2;
+  ga.ready = (uint32_t*)ready;
+  ga.epoch = epoch;
+  ga.n = n_ranks;
+  ga.chunk_bytes = chunk_bytes;
+  const int tiles_n = (N + BN - 1) / BN;
+  ga.n_start = ((n_start % tiles_n) + tiles_n) % tiles_n;
+  auto kernel = k_gemm<BM, BN, false, false, true>;
+  using L = SmemLayout<BM, BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * tiles_n;
+  int ctas = tiles < g_sm_count ? tiles : g_sm_count;
+  void* params[] = {(void*)&ma, (void*)&mb, (void*)&g, (void*)&ga};
+  tb_note_launch(1);
+  return (int)cudaLaunchCooperativeKernel((const void*)kernel, dim3(ctas), dim3(384), params, L::TOTAL, stream);
 }
 
 // Forces a tile shape for every later call (0: 256x256, 1: 128x256, 2: 128x128; -1: automatic).  For tuning.

@@ -154,3 +154,50 @@ def mlp(x, w1, b1, w2, b2, residual):
 def gemm_error():
     """True once any GEMM gave up on a wait (results since then are invalid)."""
     return bool(lib().tb_gemm_error())
+
+
+class GatheredLinear:
+    """y = x . W^T (+ bias) where W is one parameter inside a sharded flat buffer (a ZeRO-3 unit): the
+    all-gather of W is fused into the GEMM.  Extra warps of the GEMM kernel pull W's bytes from the owners'
+    shards (peer pointers into symmetric memory) into `full`, this rank's copy of the flat buffer, and the
+    kernel's TMA producer consumes each weight panel as soon as its chunks have landed.
+
+    shard_ptrs[q]: address (in this process) of rank q's shard; shard q holds flat elements
+    [offsets[q], offsets[q+1]).  w_offset: W's first element in the flat buffer; W is [N, K] row-major.
+    Forward only (the backward of a ZeRO-3 unit re-gathers with the ordinary pull)."""
+
+    CHUNK = 32 << 10
+
+    def __init__(self, shard_ptrs, offsets, rank, full, w_offset, N, K):
+        esz = 2
+        self.ptrs, self.rank, self.full = list(shard_ptrs), rank, full
+        self.lo = [o * esz for o in offsets[:-1]]
+        self.hi = [o * esz for o in offsets[1:]]
+        self.w_off, self.N, self.K = w_offset * esz, N, K
+        if self.w_off % 16 or K % 8:
+            raise ValueError("the gathered weight must start 16-byte aligned in the flat buffer and K must be a multiple of 8")
+        nchunks = (N * K * esz + self.CHUNK - 1) // self.CHUNK
+        self.ready = torch.zeros(nchunks, dtype=torch.int32, device=full.device)
+        self.epoch = 0
+        # visit first the panel fed by this rank's own shard (it arrives without crossing NVLink)
+        own = max(self.lo[rank], self.w_off) - self.w_off
+        own = own if self.lo[rank] < self.w_off + N * K * esz and self.hi[rank] > self.w_off else 0
+        self.n_start = (own // (K * esz)) // 256
+
+    def __call__(self, x, bias=None):
+        import ctypes
+
+        need_bf16(x, bias)
+        x2, ldx = _rows(x)
+        M = x2.shape[0]
+        out = empty_padded(M, self.N, torch.bfloat16, x.device)
+        self.epoch += 1
+        n = len(self.ptrs)
+        ptrs = (ctypes.c_void_p * n)(*self.ptrs)
+        lo = (ctypes.c_longlong * n)(*self.lo)
+        hi = (ctypes.c_longlong * n)(*self.hi)
+        check_rc(lib().tb_gemm_gathered(x2.data_ptr(), out.data_ptr(), M, self.N, self.K, ldx, out.stride(0), BIAS if bias is not None else 0,
+                                        bias.data_ptr() if bias is not None else None, None, None, ptrs, lo, hi, n,
+                                        self.full.data_ptr(), self.w_off, self.ready.data_ptr(), self.epoch, self.CHUNK, self.n_start,
+                                        stream(x)), "gathered gemm")
+        return out.view(*x.shape[:-1], self.N)

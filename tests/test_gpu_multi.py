@@ -232,3 +232,35 @@ def test_gpu_pipeline_matches_single_process_accumulation(schedule):
     for r, (lo, hi) in enumerate(split_units(len(ref_units), 2)):
         assert torch.equal(ours[r][1], torch.cat(ref_units[lo:hi])), f"stage {r} weights differ"
     assert ours[-1][0] == ref_losses
+
+
+def fused_gather_gemm_rank(g):
+    """A weight sharded over the ranks' symmetric memory, gathered by the GEMM kernel itself over NVLink."""
+    from tandem_b200.ops.gemm import GatheredLinear, gemm_error
+    from tandem_b200.parallel.symm import split_offsets
+
+    torch.manual_seed(0)
+    M, N, K, before = 512, 1024, 512, 1536
+    flat = (torch.randn(before + N * K + 77, device=g.device) * 0.2).bfloat16()  # identical on every rank
+    offs = split_offsets(flat.numel(), g.size)
+    shard = g.empty(max(offs[q + 1] - offs[q] for q in range(g.size)), torch.bfloat16)
+    mine = offs[g.rank + 1] - offs[g.rank]
+    shard[:mine].copy_(flat[offs[g.rank]:offs[g.rank + 1]])
+    g._sym.device_barrier()
+    full = torch.zeros_like(flat)
+    x = (torch.randn(M, K, device=g.device) * 0.5).bfloat16()
+    op = GatheredLinear(g._sym._peers_of(shard), offs, g.rank, full, before, N, K)
+    y = op(x)
+    torch.cuda.synchronize()
+    want = x.float() @ flat[before:before + N * K].view(N, K).float().t()
+    ok = bool(((y.float() - want).abs() <= 2e-2 * want.abs() + 1e-2 * want.abs().max()).all())
+    same = torch.equal(full[before:before + N * K], flat[before:before + N * K])
+    g._sym.device_barrier()
+    return ok and same and not gemm_error()
+
+
+@needs2
+def test_fused_gather_gemm_over_peer_memory():
+    from tandem_b200 import launch
+
+    assert launch(fused_gather_gemm_rank, 2, device="cuda") == [True, True]

@@ -211,3 +211,26 @@ def test_causal_attention_matches_fp32(B, T, H, hd):
     assert not attention_error(), "an attention wait ran out"
     close(y, yf, rtol=2e-2, atol=1e-2)
     close(qkv.grad, ref.grad, rtol=4e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("n,rank", [(1, 0), (4, 2), (8, 7)])
+def test_gemm_with_fused_weight_gather(n, rank):
+    """The weight lives in `n` shards of a flat buffer (here all on this GPU, standing in for the peers'
+    symmetric memory); the kernel assembles it in `full` while it multiplies."""
+    from tandem_b200.ops.gemm import GatheredLinear
+    from tandem_b200.parallel.symm import split_offsets
+
+    M, N, K = 1024, 2304, 768
+    before, after = 1536, 1003
+    flat = rnd(before + N * K + after, scale=0.3)
+    offs = split_offsets(flat.numel(), n)
+    shards = [flat[offs[q]:offs[q + 1]].clone() for q in range(n)]
+    full = torch.zeros_like(flat)
+    x, bias = rnd(M, K, scale=0.5), rnd(N)
+    op = GatheredLinear([s.data_ptr() for s in shards], offs, rank, full, before, N, K)
+    w = flat[before:before + N * K].view(N, K)
+    for _ in range(2):  # the second call reuses the flags with a new epoch
+        full.zero_()
+        y = op(x, bias)
+        close(y, x.float() @ w.float().t() + bias.float())
+        assert torch.equal(full[before:before + N * K], flat[before:before + N * K])
