@@ -465,6 +465,11 @@ typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, v
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 int make_map(CUtensorMap* map, const void* ptr, long long cols, long long rows, long long row_stride) {
+  static thread_local bool context_ready = false;  // the driver entry point below needs a current context in this thread
+  if (!context_ready) {
+    cudaFree(nullptr);
+    context_ready = true;
+  }
   static EncodeTiled enc = nullptr;
   if (enc == nullptr) {
     void* p = nullptr;

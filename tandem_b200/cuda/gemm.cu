@@ -613,6 +613,13 @@ char g_map_error[256] = "";
 
 // A 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows of `row_stride` elements.
 int make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long row_stride, int box_inner, int box_outer) {
+  // cuTensorMapEncodeTiled is a driver entry point: it needs this thread to have a current context, which a
+  // thread that has so far only been handed cached allocations (an autograd worker) may not have yet.
+  static thread_local bool context_ready = false;
+  if (!context_ready) {
+    cudaFree(nullptr);
+    context_ready = true;
+  }
   EncodeTiled enc = encoder();
   if (enc == nullptr) return -10;
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
