@@ -183,6 +183,14 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    if world > 1:
+        # torch.distributed is plumbing only: it lets the symmetric heap be bound to an NVSwitch multicast object
+        # (NVLS all-reduce kernels) and carries pipeline point-to-point traffic.  The collectives are this library's.
+        import torch.distributed as dist
+
+        local = int(os.environ.get("LOCAL_RANK", str(rank)))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     g = tandem_b200.Group.from_env(device="cuda")
     dev = g.device
     lib = cuda_lib()
@@ -197,7 +205,7 @@ def run_ours(args):
         opt = BucketAdamW(wrapped, lr=LR, weight_decay=WD)
         finish = lambda: (opt.step(), opt.zero_grad())
     elif args.strategy in ("zero1", "zero2"):
-        wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD))
+        wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD), fused_step=True)
         finish = lambda: (wrapped.step(), wrapped.zero_grad())
     elif args.strategy == "zero3":
         wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD))
@@ -240,10 +248,15 @@ def run_ours(args):
     dev_ms, e2e_ms, h2d, d2h, launches, last = timed_loops(step_fn, batches, args.steps, args.warmup, dev, g.barrier, reduce_max)
     launches = per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
+    nvls = bool(g._sym is not None and g._sym.nvls)
     g.close()
     if rank == 0:
         print(json.dumps(result_line(args, "ours", args.strategy, dev_ms, e2e_ms, h2d, d2h, int(launches), clocks, "bf16",
-                                     {"kernels": kernels, "final_loss": last, "cuda_graph": bool(graphed)})), flush=True)
+                                     {"kernels": kernels, "final_loss": last, "cuda_graph": bool(graphed), "nvls": nvls})), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
 
 
 # ---------------------------------------------------------------------------------------------- torch DDP (context)

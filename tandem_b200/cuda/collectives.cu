@@ -418,6 +418,68 @@ k_gather_pull(CommCtx c, PeerPtrs src, Locals dsts, GatherPlan plan, Locals stag
   if (sync == 1) comm_barrier(c, sh);
 }
 
+// ---------------------------------------------------------------------------------------------
+// NVLS all-reduce: the buffer is also mapped through an NVSwitch multicast address.  Each rank owns a
+// 16-byte-aligned slice; multimem.ld_reduce returns the SUM OVER ALL RANKS of a 16-byte vector (the
+// switch adds the ranks' copies), the mean's factor is applied, and multimem.st writes the result into
+// every rank's copy at once.  Half the NVLink bytes of the two-shot kernel and no per-peer loads; the
+// switch's order of additions is not specified, so results are not tied to the ring order.
+template <typename T>
+__device__ __forceinline__ uint4 multimem_ld_reduce(const char* mc);
+template <>
+__device__ __forceinline__ uint4 multimem_ld_reduce<float>(const char* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_reduce<__nv_bfloat16>(const char* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void multimem_st(char* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
+k_allreduce_nvls(CommCtx c, char* mc, long long nvec, int smode, float sval) {
+  __shared__ int sh[2];
+  if (threadIdx.x == 0) sh[1] = 0;
+  const int n = c.n, rank = comm_rank(c);
+  constexpr int N = VecOf<T>::N;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  comm_barrier(c, sh);
+  if (!sh[1]) {
+    const long long lo = nvec * rank / n, hi = nvec * (rank + 1) / n;  // this rank's slice, in vectors
+    for (long long v = lo + tid; v < hi; v += nth * 4) {
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v + u * nth < hi) x[u] = multimem_ld_reduce<T>(mc + (v + u * nth) * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v + u * nth < hi) {
+          if (smode != SCALE_NONE) {
+            float f[N];
+            unpack<T>(x[u], f);
+#pragma unroll
+            for (int e = 0; e < N; ++e) f[e] = scaled(f[e], smode, sval);
+            x[u] = pack<T>(f);
+          }
+          multimem_st(mc + (v + u * nth) * 16, x[u]);
+        }
+      }
+    }
+  }
+  comm_barrier(c, sh);
+}
+
 // A barrier and nothing else (one block per rank).
 __global__ void k_barrier(CommCtx c) {
   __shared__ int sh[2];
@@ -654,6 +716,22 @@ int tb_all_reduce(TbComm* c, void* const* bufs, void* const* local_in, void* con
 #undef TWO
 }
 
+// In-switch all-reduce of a buffer that every rank has bound to one multicast object: mc is the multicast
+// address of the buffer (the same offset in every rank's copy).  numel * element size must be a multiple of
+// 16 and mc 16-byte aligned; dtype fp32 or bf16.  Not available when emulating ranks on one GPU.
+int tb_all_reduce_nvls(TbComm* c, void* mc, long long numel, int dtype, int average, cudaStream_t stream) {
+  if (numel <= 0) return 0;
+  if (c->emulated || (dtype != TB_F32 && dtype != TB_BF16)) return -4;
+  const long long bytes = numel * elem_size(dtype);
+  if ((bytes & 15) || ((uintptr_t)mc & 15)) return -4;
+  int smode;
+  float sval;
+  scale_mode(c->ctx.n, average, &smode, &sval);
+  int blocks = blocks_for(c, bytes / c->ctx.n, (long long)TB_COMM_THREADS * 16 * 4);
+  if (dtype == TB_F32) return (int)launch(c, k_allreduce_nvls<float>, blocks, stream, c->ctx, (char*)mc, bytes / 16, smode, sval);
+  return (int)launch(c, k_allreduce_nvls<__nv_bfloat16>, blocks, stream, c->ctx, (char*)mc, bytes / 16, smode, sval);
+}
+
 // Folds chunk r = [offs[r], offs[r+1]) of every rank's buffer into rank r's buffer.
 // acc_out (array like local_in; entries may be null): also acc_out[i - lo] += result.
 // adam (array of AdamArgs like local_in, fp32 only): fused AdamW on {param, exp_avg, exp_avg_sq}[i - lo]
@@ -701,6 +779,7 @@ int tb_reduce_scatter(TbComm* c, void* const* bufs, void* const* local_in, long 
     if (acc_out != nullptr) RS(float, false, 1);
     RS(float, false, 0);
   }
+  if (dtype == TB_BF16 && adam != nullptr) RS(__nv_bfloat16, false, 2);  // bf16 gradients into fp32 master weights
   if (adam != nullptr) return -3;
   if (dtype == TB_BF16) {
     if (acc_out != nullptr) {

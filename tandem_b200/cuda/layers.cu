@@ -100,7 +100,7 @@ k_ln_fwd(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ 
 // dx for each row, and per-block partial sums of dw = sum dy*xhat and db = sum dy into
 // part[blockIdx.x][2][D] (fp32).  A second kernel adds the partials in a fixed order.
 template <int MAXV>
-__global__ void __launch_bounds__(256, 2)  // two blocks per SM: caps registers at 128 (a capture showed 171 and 12 % occupancy)
+__global__ void __launch_bounds__(256, MAXV <= 4 ? 2 : 1)  // two blocks per SM where the row fits: a capture showed 171 registers and 12 % occupancy
 k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
          const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
          float* __restrict__ part, int M, int D) {

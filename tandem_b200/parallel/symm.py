@@ -28,7 +28,7 @@ MAX_RANKS = 8
 MAX_BLOCKS = 128
 ALIGN = 256
 FLAG_BYTES = MAX_BLOCKS * MAX_RANKS * 4
-ALGO = {"auto": 0, "oneshot": 1, "twoshot": 2}
+ALGO = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3}
 
 
 class AdamArgs(ctypes.Structure):
@@ -79,6 +79,7 @@ def cuda_lib():
         "tb_comm_set_max_blocks": ([vp, i], None),
         "tb_barrier": ([vp, vp], i),
         "tb_all_reduce": ([vp, pp, pp, pp, ll, i, i, i, i, vp], i),
+        "tb_all_reduce_nvls": ([vp, vp, ll, i, i, vp], i),
         "tb_reduce_scatter": ([vp, pp, pp, ll, pll, i, i, i, pp, ctypes.POINTER(AdamArgs), vp], i),
         "tb_gather_pull": ([vp, pp, pp, pll, pll, pll, pp, i, ll, vp], i),
         "tb_adamw": ([vp, vp, i, vp, vp, vp, ll, ctypes.POINTER(f), i, f, vp], i),
@@ -141,11 +142,13 @@ class Heap:
 
     def __init__(self):
         self.segments = []  # [(bytes, [base pointer per rank])]
+        self.multicast = []  # per segment: NVSwitch multicast address of the segment, or 0
         self.free = []  # [(segment, offset, bytes)], sorted
         self.used = {}  # (segment, offset) -> bytes
 
-    def add_segment(self, nbytes, bases):
+    def add_segment(self, nbytes, bases, multicast=0):
         self.segments.append((nbytes, bases))
+        self.multicast.append(int(multicast or 0))
         self.free.append((len(self.segments) - 1, 0, nbytes))
 
     def take(self, nbytes):
@@ -200,6 +203,8 @@ class SymmetricComm:
         self.stream = torch.cuda.Stream(self.device, priority=group.priority)
         self.segment_bytes = int(os.environ.get("TANDEM_SYMM_BYTES", str(1 << 30)))
         self.heap = Heap()
+        self._torch_segments = []  # segments that came from torch's symmetric-memory allocator (kept alive here)
+        self._nvls_error = None
         self._owned = []  # this rank's cudaMalloc'd segments
         self._opened = []  # peers' segments mapped here
         self._add_segment(max(self.segment_bytes, 4 << 20))
@@ -233,6 +238,10 @@ class SymmetricComm:
         self._launch_stream = self.stream
         self._ptr_cache = {}
         self.exact16 = os.environ.get("TANDEM_EXACT16", "0") == "1"
+        self.nvls_min_bytes = int(os.environ.get("TANDEM_NVLS_MIN_BYTES", str(1 << 20)))
+        # Measured: with 2 ranks the peer-to-peer two-shot kernel is faster than going through the switch's
+        # reduction (530 vs 396 GB/s bus at 256 MB); the switch pays off as the peer count grows.
+        self.nvls_min_ranks = int(os.environ.get("TANDEM_NVLS_MIN_RANKS", "4"))
         self.algo = ALGO[os.environ.get("TANDEM_ALLREDUCE", "auto")]
         # clock calibration for traces: device event time -> host perf_counter
         self._t0_event = torch.cuda.Event(enable_timing=True)
@@ -242,7 +251,12 @@ class SymmetricComm:
 
     # ------------------------------------------------------------------ heap
     def _add_segment(self, nbytes):
-        """Collective: every rank allocates a segment and maps everyone else's."""
+        """Collective: every rank allocates a segment and maps everyone else's.  With a torch.distributed
+        NCCL group in place (and TANDEM_NVLS != 0) the segment comes from torch's symmetric-memory
+        allocator, which also binds it to an NVSwitch multicast object (for the multimem kernels);
+        otherwise it is cudaMalloc'd here and exchanged through CUDA IPC."""
+        if self.n > 1 and os.environ.get("TANDEM_NVLS", "1") != "0" and self._add_segment_multicast(nbytes):
+            return
         mine = ctypes.c_void_p()
         check_rc(self.lib.tb_malloc(ctypes.byref(mine), nbytes), f"cudaMalloc of a {nbytes >> 20} MiB symmetric segment")
         self._owned.append(mine.value)
@@ -263,6 +277,29 @@ class SymmetricComm:
             self._opened.append(out.value)
             bases.append(out.value)
         self.heap.add_segment(nbytes, bases)
+
+    def _add_segment_multicast(self, nbytes):
+        try:
+            import torch.distributed as dist
+
+            if not (dist.is_available() and dist.is_initialized() and dist.get_backend() == "nccl"
+                    and dist.get_world_size() == self.n and dist.get_rank() == self.rank):
+                return False
+            import torch.distributed._symmetric_memory as symm_mem
+
+            t = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            handle = symm_mem.rendezvous(t, dist.group.WORLD)
+            bases = [int(p) for p in handle.buffer_ptrs]
+            mc = int(handle.multicast_ptr or 0)  # 0 when the machine has no NVSwitch multicast
+        except Exception as e:  # no multicast on this machine / torch build: fall back to CUDA IPC
+            self._nvls_error = repr(e)
+            return False
+        t.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier()
+        self._torch_segments.append((t, handle))
+        self.heap.add_segment(nbytes, bases, mc)
+        return True
 
     def _take(self, nbytes):
         where = self.heap.take(nbytes)
@@ -300,6 +337,18 @@ class SymmetricComm:
             self._ptr_cache.clear()
         self._ptr_cache[ptr] = (nbytes, peers)
         return peers
+
+    def _multicast_of(self, t):
+        """NVSwitch multicast address of a heap tensor, or 0."""
+        where = self.heap.locate(self.rank, t.data_ptr(), max(t.numel() * t.element_size(), 1))
+        if where is None or not self.heap.multicast[where[0]]:
+            return 0
+        return self.heap.multicast[where[0]] + where[1]
+
+    @property
+    def nvls(self):
+        """True when the heap is bound to an NVSwitch multicast object (multimem kernels available)."""
+        return any(self.heap.multicast)
 
     # ------------------------------------------------------------------ launching
     def _begin(self, name, tensors, async_op=True):
@@ -367,7 +416,13 @@ class SymmetricComm:
         s = self._launch_stream.cuda_stream
         peers = self._peers_of(flat)
         if flat.numel() and self.n > 1:  # a group of one: the buffer already holds its own sum (and mean)
-            if peers is not None:
+            mc = self._multicast_of(flat) if peers is not None and flat.dtype in (torch.float32, torch.bfloat16) else 0
+            nbytes_ = flat.numel() * flat.element_size()
+            want_nvls = algo == ALGO["nvls"] or (algo == ALGO["auto"] and self.n >= self.nvls_min_ranks and nbytes_ >= self.nvls_min_bytes and not self.exact16
+                                                 and not torch.are_deterministic_algorithms_enabled())
+            if mc and want_nvls and nbytes_ % 16 == 0 and mc % 16 == 0:
+                check_rc(self.lib.tb_all_reduce_nvls(self._launch_comm, mc, flat.numel(), code, int(average), s), "all_reduce (NVLS)")
+            elif peers is not None:
                 check_rc(self.lib.tb_all_reduce(self._launch_comm, _ptr_array(peers), None, None, flat.numel(), code, int(average),
                                                 int(self.exact16), algo, s), "all_reduce")
             else:

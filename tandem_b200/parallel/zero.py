@@ -86,11 +86,16 @@ def _point_into(buf, layout):
 class ZeRO(torch.nn.Module):
     """Stages 1 and 2."""
 
-    def __init__(self, module, group, stage=1, optimizer=None, bucket_bytes=25 << 20):
+    def __init__(self, module, group, stage=1, optimizer=None, bucket_bytes=25 << 20, fused_step=False):
+        """fused_step (stage 2, GPU kernels only): apply the sharded AdamW update inside each bucket's
+        reduce-scatter kernel, on the freshly reduced gradient chunk, instead of in step().  One pass over
+        the gradients instead of three (reduce, accumulate, optimizer); step() then only all-gathers the
+        parameters.  Not compatible with accumulating gradients over several backward passes."""
         super().__init__()
         if stage not in (1, 2):
             raise ValueError("ZeRO handles stages 1 and 2; stage 3 is FSDP")
         self.module, self.g, self.stage = module, group, stage
+        self.fused_step = bool(fused_step) and stage == 2 and group.fused
         self.opt = optimizer or ShardedAdamW()
         params = [p for p in module.parameters() if p.requires_grad]
         dev, dtype = params[0].device, params[0].dtype
@@ -157,7 +162,12 @@ class ZeRO(torch.nn.Module):
                 nxt.work = self.g.all_reduce(self.grad[nxt.a:nxt.b], op="avg", async_op=True)
             else:
                 sizes = self.flat.bucket_sizes(nxt.a, nxt.b)
-                if self.g.fused and nxt.staging.is_cuda and sizes[self.g.rank]:
+                if self.fused_step and nxt.staging.is_cuda and sizes[self.g.rank]:
+                    at = max(nxt.a, self.flat.lo) - self.flat.lo
+                    nxt.work = self.g.reduce_scatter(nxt.staging, sizes, op="avg", async_op=True,
+                                                     adam=self._adam_args(at, sizes[self.g.rank]))
+                    nxt.fused_acc = True
+                elif self.g.fused and nxt.staging.is_cuda and sizes[self.g.rank]:
                     at = max(nxt.a, self.flat.lo) - self.flat.lo
                     nxt.work = self.g.reduce_scatter(nxt.staging, sizes, op="avg", async_op=True,
                                                      accumulate_into=self.grad_shard[at:at + sizes[self.g.rank]])
@@ -184,11 +194,28 @@ class ZeRO(torch.nn.Module):
         if incomplete:
             raise RuntimeError("tandem_b200 ZeRO: every parameter must receive a gradient")
 
+    def _adam_args(self, at, count):
+        """AdamArgs for elements [at, at+count) of this rank's shard, for the step the current backward feeds."""
+        from .symm import AdamArgs
+
+        lo = self.flat.lo
+        shard = self.buf[lo:self.flat.hi]
+        st = self.opt._state("flat", shard)
+        master = self.opt.master.get("flat")
+        step = st[0] + 1.0
+        param = (master if master is not None else shard)[at:at + count]
+        shadow = shard[at:at + count] if master is not None else None
+        return AdamArgs.make(param, st[1][at:at + count], st[2][at:at + count], self.opt.scalars(step),
+                             self.opt.weight_decay != 0, shadow)
+
     @torch.no_grad()
     def step(self):
         lo, hi = self.flat.lo, self.flat.hi
-        grad = self.grad[lo:hi] if self.stage == 1 else self.grad_shard
-        self.opt.update("flat", self.buf[lo:hi], grad)
+        if self.fused_step:
+            self.opt._state("flat", self.buf[lo:hi])[0] += 1.0  # the update itself ran inside the reduce-scatter kernels
+        else:
+            grad = self.grad[lo:hi] if self.stage == 1 else self.grad_shard
+            self.opt.update("flat", self.buf[lo:hi], grad)
         self.g.all_gather(self.buf, self.flat.sizes)
 
     def zero_grad(self):

@@ -264,3 +264,82 @@ def test_fused_gather_gemm_over_peer_memory():
     from tandem_b200 import launch
 
     assert launch(fused_gather_gemm_rank, 2, device="cuda") == [True, True]
+
+
+def nvls_rank(rank, world, init, out):
+    """All-reduce through the NVSwitch multicast mapping (multimem.ld_reduce / multimem.st)."""
+    import torch.distributed as dist
+
+    from tandem_b200 import Group
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"file://{init}", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    g = Group(rank, world, f"cuda:{rank}", job=os.path.basename(init)[-12:])
+    result = {"nvls": g._sym.nvls, "why": g._sym._nvls_error}
+    if g._sym.nvls:
+        ok = True
+        for dtype in (torch.float32, torch.bfloat16):
+            for n in (1 << 20, 300_000 * 8):
+                x = g.empty(n, dtype)
+                x.copy_(data(rank, n, dtype))
+                g._sym.all_reduce(x, False, x, 0, False, algo="nvls")
+                want = sum(data(q, n, dtype).double() for q in range(world))
+                ok = ok and torch.equal(x.double().cpu(), want)
+                x.copy_(data(rank, n, dtype))
+                g.all_reduce(x, op="avg")  # large enough to pick the NVLS kernel by itself
+                ok = ok and torch.allclose(x.double().cpu(), want / world, rtol=1e-2, atol=1e-2)
+                g.release(x)
+        g.check()
+        result["ok"] = ok
+    g.close()
+    dist.destroy_process_group()
+    torch.save(result, f"{out}.{rank}")
+
+
+@needs2
+def test_nvls_multimem_all_reduce():
+    import torch.multiprocessing as mp
+    import uuid
+
+    with tempfile.TemporaryDirectory() as d:
+        init = os.path.join(d, "init" + uuid.uuid4().hex[:12])
+        mp.spawn(nvls_rank, args=(2, init, os.path.join(d, "out")), nprocs=2)
+        res = [torch.load(os.path.join(d, f"out.{r}")) for r in range(2)]
+    if not res[0]["nvls"]:
+        pytest.skip(f"no NVSwitch multicast on this machine: {res[0]['why']}")
+    assert all(r["ok"] for r in res)
+
+
+def zero2_fused_rank(g, fused):
+    from tandem_b200.data import synthetic
+    from tandem_b200.model import GPT
+    from tandem_b200.optim import ShardedAdamW
+    from tandem_b200.zero import ZeRO
+
+    torch.manual_seed(0)
+    cfg = _cfg()
+    text = synthetic(20_000)
+    model = GPT(cfg).to(g.device)
+    z = ZeRO(model, g, 2, ShardedAdamW(lr=3e-3, weight_decay=0.1), 64 << 10, fused_step=fused)
+    losses = []
+    for step in range(STEPS):
+        x, y = text.batch(step, BATCH, cfg.seq, rank=g.rank, world=g.size, device=g.device)
+        loss = z(x, y)
+        loss.backward()
+        z.step()
+        z.zero_grad()
+        losses.append(loss.item())
+    g.check()
+    return losses, torch.cat([p.detach().reshape(-1) for p in model.parameters()]).cpu()
+
+
+@needs2
+def test_zero2_adamw_fused_into_reduce_scatter_matches_unfused():
+    from tandem_b200 import launch
+
+    fused = launch(zero2_fused_rank, 2, True, device="cuda")
+    plain = launch(zero2_fused_rank, 2, False, device="cuda")
+    assert torch.equal(fused[0][1], fused[1][1])  # ranks stay in step
+    for a, b in zip(fused[0][0], plain[0][0]):
+        assert abs(a - b) < 1e-4, (fused[0][0], plain[0][0])
+    assert torch.allclose(fused[0][1], plain[0][1], rtol=1e-5, atol=1e-6), (fused[0][1] - plain[0][1]).abs().max()
