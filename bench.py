@@ -208,7 +208,7 @@ def run_ours(args):
         wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD), fused_step=True)
         finish = lambda: (wrapped.step(), wrapped.zero_grad())
     elif args.strategy == "zero3":
-        wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD))
+        wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD), fuse_gather_gemm=bool(args.fuse))
         finish = lambda: (wrapped.step(), wrapped.zero_grad())
     else:
         raise SystemExit(f"unknown strategy {args.strategy}")
@@ -393,6 +393,7 @@ def main():
     ap.add_argument("--strategy", default="ddp", choices=["ddp", "zero1", "zero2", "zero3"])
     ap.add_argument("--kernels", default=os.environ.get("TANDEM_BENCH_KERNELS", "b200"), choices=["torch", "b200"])
     ap.add_argument("--ref-backend", default="python", choices=["python", "cpp"])
+    ap.add_argument("--fuse", type=int, default=1, help="zero3: gather each block's qkv weight inside its GEMM kernel")
     ap.add_argument("--graph", type=int, default=1, help="replay the ddp step as a CUDA graph (ours, ddp only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

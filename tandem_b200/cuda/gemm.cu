@@ -72,8 +72,9 @@ struct GatherArgs {
   const char* shard[8];   // shard[q]: rank q's shard as mapped here; its byte 0 is byte shard_lo[q] of the unit's flat buffer
   long long shard_lo[8];  // byte ranges of the shards within the unit's flat buffer
   long long shard_hi[8];
-  char* full;             // this GPU's copy of the unit's flat buffer; the weight occupies [w_off, w_off + w_bytes)
-  long long w_off, w_bytes;
+  char* full;             // this GPU's copy of the unit's flat buffer; the weight occupies [w_off, w_off + N*K*2)
+  long long w_off, w_bytes;  // w_bytes: everything fetched = the weight plus tail_bytes
+  long long tail_bytes;   // bytes right behind the weight that are fetched with it (the layer's bias)
   uint32_t* ready;        // one word per chunk of the weight; chunk c is complete once ready[c] == epoch
   uint32_t epoch;
   int n;                  // ranks
@@ -531,6 +532,12 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
     uint32_t local_tile = 0;
     bool ok = true;
     const bool out_f32 = g.flags & EPI_OUT_F32;
+    if (GATHER && (g.flags & EPI_BIAS) && ga.tail_bytes > 0) {
+      // the bias sits right behind the weight in the flat buffer and is fetched with it: wait for its chunks
+      const long long lo = (long long)g.N * g.K * 2, hi = lo + ga.tail_bytes;
+      ok = wait_chunks(ga.ready, (int)(lo / ga.chunk_bytes), (int)((hi - 1) / ga.chunk_bytes), ga.epoch, g.error);
+      ok = __all_sync(0xffffffffu, ok);
+    }
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       int m0, n0;
       tile_origin(tile, &m0, &n0);
@@ -738,11 +745,13 @@ int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, i
 // out[M, N] = A[M, K] . W[N, K]^T (+ epilogue) where W is gathered by the kernel itself: rank q's shard (peer
 // address shards[q]) holds bytes [shard_lo[q], shard_hi[q]) of the unit's flat buffer; W is the byte range
 // [w_off, w_off + N*K*2) of it and is assembled in `full` (this GPU's copy) while the GEMM runs.
-// ready: one zero-initialised word per chunk (ceil(N*K*2 / chunk_bytes)); epoch: a value not used by an earlier
+// tail_bytes: bytes right behind W in the flat buffer to fetch as well (the layer's bias; pass bias = full + w_off +
+// N*K*2 then).  ready: one zero-initialised word per chunk (ceil((N*K*2 + tail_bytes) / chunk_bytes)); epoch: a value not used by an earlier
 // call on the same words.  One cooperative launch; returns a CUDA error if the grid cannot be co-resident.
 int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int ldc, int flags, const void* bias, const void* aux_in,
                      void* aux_out, void* const* shards, const long long* shard_lo, const long long* shard_hi, int n_ranks, void* full,
-                     long long w_off, void* ready, unsigned epoch, int chunk_bytes, int n_start, cudaStream_t stream) {
+                     long long w_off, long long tail_bytes, void* ready, unsigned epoch, int chunk_bytes, int n_start,
+                     cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (K & 7) || (w_off & 15) || (((uintptr_t)A | (uintptr_t)full) & 15) || n_ranks < 1 || n_ranks > 8) return -12;
   if (g_error_host == nullptr) {
@@ -768,7 +777,8 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
   }
   ga.full = (char*)full;
   ga.w_off = w_off;
-  ga.w_bytes = (long long)N * K * 2;
+  ga.w_bytes = (long long)N * K * 2 + tail_bytes;
+  ga.tail_bytes = tail_bytes;
   ga.ready = (uint32_t*)ready;
   ga.epoch = epoch;
   ga.n = n_ranks;

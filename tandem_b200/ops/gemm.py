@@ -78,11 +78,26 @@ def _grad_bias(dy2, ldy):
     return out
 
 
+# Weights whose all-gather the next forward GEMM performs itself: data_ptr of the weight's place in the local flat
+# buffer -> (GatheredLinear, event to wait for afterwards or None).  ZeRO-3 fills it when it starts a unit's gather.
+GATHERED = {}
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, residual):
         need_bf16(x, w, bias, residual)
         x2, ldx = _rows(x)
+        fused = GATHERED.pop(w.data_ptr(), None) if GATHERED and residual is None else None
+        if fused is not None:
+            op, after = fused
+            y = op(x2, None if op.tail else bias)
+            if after is not None:  # the rest of the unit's parameters, pulled meanwhile on the communication stream
+                torch.cuda.current_stream(x.device).wait_event(after)
+            ctx.save_for_backward(x2, w)
+            ctx.ldx, ctx.has_bias, ctx.has_res = ldx, bias is not None, False
+            ctx.in_shape = x.shape
+            return y.view(*x.shape[:-1], w.shape[0])
         res2 = None
         if residual is not None:
             res2 = residual.reshape(-1, residual.shape[-1])
@@ -168,15 +183,18 @@ class GatheredLinear:
 
     CHUNK = 32 << 10
 
-    def __init__(self, shard_ptrs, offsets, rank, full, w_offset, N, K):
+    def __init__(self, shard_ptrs, offsets, rank, full, w_offset, N, K, bias_follows=False):
+        """bias_follows: the layer's bias (N elements) lies right behind W in the flat buffer (the parameter order of
+        nn.Linear) and is fetched and applied by the same kernel."""
         esz = 2
+        self.tail = N * esz if bias_follows else 0
         self.ptrs, self.rank, self.full = list(shard_ptrs), rank, full
         self.lo = [o * esz for o in offsets[:-1]]
         self.hi = [o * esz for o in offsets[1:]]
         self.w_off, self.N, self.K = w_offset * esz, N, K
         if self.w_off % 16 or K % 8:
             raise ValueError("the gathered weight must start 16-byte aligned in the flat buffer and K must be a multiple of 8")
-        nchunks = (N * K * esz + self.CHUNK - 1) // self.CHUNK
+        nchunks = (N * K * esz + self.tail + self.CHUNK - 1) // self.CHUNK
         self.ready = torch.zeros(nchunks, dtype=torch.int32, device=full.device)
         self.epoch = 0
         # visit first the panel fed by this rank's own shard (it arrives without crossing NVLink)
@@ -196,8 +214,11 @@ class GatheredLinear:
         ptrs = (ctypes.c_void_p * n)(*self.ptrs)
         lo = (ctypes.c_longlong * n)(*self.lo)
         hi = (ctypes.c_longlong * n)(*self.hi)
-        check_rc(lib().tb_gemm_gathered(x2.data_ptr(), out.data_ptr(), M, self.N, self.K, ldx, out.stride(0), BIAS if bias is not None else 0,
-                                        bias.data_ptr() if bias is not None else None, None, None, ptrs, lo, hi, n,
-                                        self.full.data_ptr(), self.w_off, self.ready.data_ptr(), self.epoch, self.CHUNK, self.n_start,
-                                        stream(x)), "gathered gemm")
+        if self.tail:
+            bias_ptr = self.full.data_ptr() + self.w_off + self.N * self.K * 2
+        else:
+            bias_ptr = bias.data_ptr() if bias is not None else None
+        check_rc(lib().tb_gemm_gathered(x2.data_ptr(), out.data_ptr(), M, self.N, self.K, ldx, out.stride(0), BIAS if bias_ptr else 0,
+                                        bias_ptr, None, None, ptrs, lo, hi, n, self.full.data_ptr(), self.w_off, self.tail,
+                                        self.ready.data_ptr(), self.epoch, self.CHUNK, self.n_start, stream(x)), "gathered gemm")
         return out.view(*x.shape[:-1], self.N)

@@ -499,7 +499,7 @@ class SymmetricComm:
                                plen, mine, True)
         return self._end("all_gather", start, result, nbytes, async_op)
 
-    def gather_shards(self, full, shard, sizes, async_op=True):
+    def gather_shards(self, full, shard, sizes, async_op=True, lo=None, hi=None):
         """full[off_q : off_q + sizes[q]] = rank q's `shard`, for every q, with no
         handshake between ranks: `shard` is a heap tensor allocated identically on
         every rank whose contents only change between barriers (parameter shards
@@ -513,8 +513,15 @@ class SymmetricComm:
         peers = self._peers_of(shard)
         if peers is None:
             raise self._error("gather_shards needs a shard allocated with Group.empty()")
-        self._pull(peers, full.data_ptr(), [0] * self.n, offs[:-1], lens, None, 2, max(lens))  # 2: fence, no handshake
-        return self._end("all_gather", start, full, full.numel() * esz, async_op)
+        src_off, dst_off = [0] * self.n, offs[:-1]
+        if lo is not None:  # only the elements [lo, hi) of the flat buffer: each rank's shard clipped to that range
+            a, b = lo * esz, hi * esz
+            starts = [max(offs[q], a) for q in range(self.n)]
+            lens = [max(0, min(offs[q + 1], b) - starts[q]) for q in range(self.n)]
+            src_off = [starts[q] - offs[q] if lens[q] else 0 for q in range(self.n)]
+            dst_off = [starts[q] if lens[q] else 0 for q in range(self.n)]
+        self._pull(peers, full.data_ptr(), src_off, dst_off, lens, None, 2, max(max(lens), 1))  # 2: fence, no handshake
+        return self._end("all_gather", start, full, sum(lens), async_op)
 
     def broadcast(self, flat, root, result, nbytes, async_op):
         start = self._begin("broadcast", [flat], async_op)

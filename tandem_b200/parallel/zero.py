@@ -69,6 +69,7 @@ class _Range:
         self.work = None
         self.staging = None
         self.fused_acc = False
+        self.loose = []  # (staging view, gradient) pairs waiting for the bucket's one pack kernel
 
 
 def _flatten_into(buf, layout):
@@ -150,7 +151,10 @@ class ZeRO(torch.nn.Module):
         else:
             if r.staging is None:
                 r.staging = self.g.empty(r.b - r.a, p.dtype, p.device, zero=False)
-            r.staging[a - r.a:b - r.a].copy_(p.grad.reshape(-1))
+            if p.grad.is_cuda:  # packed by one multi-tensor copy when the bucket is complete
+                r.loose.append((r.staging[a - r.a:b - r.a].view_as(p), p.grad))
+            else:
+                r.staging[a - r.a:b - r.a].copy_(p.grad.reshape(-1))
             p.grad = None  # the full-size gradient is not kept
         if not self._queued:
             self._queued = True
@@ -158,6 +162,11 @@ class ZeRO(torch.nn.Module):
         r.ready += 1
         while self._next < len(self.buckets) and self.buckets[self._next].ready == len(self.buckets[self._next].params):
             nxt = self.buckets[self._next]
+            if nxt.loose:
+                from ..ops import pack_into
+
+                pack_into(nxt.staging, nxt.loose)
+                nxt.loose = []
             if self.stage == 1:
                 nxt.work = self.g.all_reduce(self.grad[nxt.a:nxt.b], op="avg", async_op=True)
             else:
@@ -240,14 +249,22 @@ class _Unit:
         self.rs = None  # reduce-scatter in flight
         self.staging = None
         self.fused_acc = False
+        self.loose = []
+        self.fused = None  # plan for gathering the unit's qkv weight inside its GEMM (FSDP(fuse_gather_gemm=True))
+        self.pending_head = None
 
 
 class FSDP(torch.nn.Module):
     """ZeRO stage 3 over model.units() (for the GPT: embedding, each block, head)."""
 
-    def __init__(self, model, group, optimizer=None, prefetch=True):
+    def __init__(self, model, group, optimizer=None, prefetch=True, fuse_gather_gemm=False):
+        """fuse_gather_gemm (GPU kernels, bf16 model): in the forward pass a transformer block's qkv weight and
+        bias are not gathered ahead of time; the qkv GEMM kernel pulls them from the owners' shards itself while
+        it computes (ops.gemm.GatheredLinear), and the rest of the unit arrives on the communication stream
+        meanwhile.  Backward gathers whole units as usual."""
         super().__init__()
         self.module, self.g = model, group
+        self.fuse = bool(fuse_gather_gemm) and group.fused
         self.opt = optimizer or ShardedAdamW()
         self.prefetch = prefetch
         # The embedding's input needs no gradient, so torch warns that its full
@@ -270,6 +287,8 @@ class FSDP(torch.nn.Module):
                 # every rank allocates the largest shard's size, so heap offsets stay identical across ranks
                 u.shard = group.empty(max(u.flat.sizes), u.full.dtype, u.full.device)[:u.flat.hi - u.flat.lo]
                 u.shard.copy_(u.full[u.flat.lo:u.flat.hi])
+            if self.fuse:
+                self._plan_fusion(u, m)
             for p in ps:
                 self.unit_of[p] = u
                 p.register_post_accumulate_grad_hook(self._on_grad)
@@ -289,14 +308,39 @@ class FSDP(torch.nn.Module):
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
 
+    def _plan_fusion(self, u, m):
+        """Marks a unit whose first GEMM can gather its own weight: a block whose qkv weight is bf16, starts
+        16-byte aligned in the unit's flat buffer and is followed directly by its bias."""
+        qkv = getattr(getattr(m, "attn", None), "qkv", None)
+        if qkv is None or qkv.weight.dtype != torch.bfloat16 or not qkv.weight.is_cuda or qkv.bias is None:
+            return
+        w_off = u.flat.offset[qkv.weight]
+        N, K = qkv.weight.shape
+        if w_off % 8 or K % 8 or u.flat.offset[qkv.bias] != w_off + N * K:
+            return
+        u.fused = {"weight": qkv.weight, "w_off": w_off, "end": w_off + N * K + N, "N": N, "K": K, "op": None}
+
     # ---- a unit's full parameters: gather, wait, free
-    def _start_gather(self, u):
+    def _start_gather(self, u, forward=False):
         if u.gathered or u.pending is not None:
             return
         u.full.untyped_storage().resize_(u.nbytes)
         self.live += 1
         self.max_live = max(self.max_live, self.live)
-        if self.g.fused and u.full.is_cuda:
+        if self.fuse and forward and u.fused is not None and torch.is_grad_enabled():
+            from ..ops.gemm import GATHERED, GatheredLinear
+            from .symm import split_offsets
+
+            f = u.fused
+            if f["op"] is None:
+                offs = split_offsets(u.flat.numel, self.g.size, u.flat.sizes)
+                f["op"] = GatheredLinear(self.g._sym._peers_of(u.shard), offs, self.g.rank, u.full, f["w_off"], f["N"], f["K"],
+                                         bias_follows=True)
+            sym = self.g._sym
+            u.pending_head = sym.gather_shards(u.full, u.shard, u.flat.sizes, lo=0, hi=f["w_off"])
+            u.pending = sym.gather_shards(u.full, u.shard, u.flat.sizes, lo=f["end"], hi=u.flat.numel)
+            GATHERED[f["weight"].data_ptr()] = (f["op"], u.pending._event)
+        elif self.g.fused and u.full.is_cuda:
             # Shards only change inside step(), which is fenced by barriers on both
             # sides, so peers' shards can be pulled with no handshake at all.
             u.pending = self.g._sym.gather_shards(u.full, u.shard, u.flat.sizes)
@@ -304,8 +348,15 @@ class FSDP(torch.nn.Module):
             u.full[u.flat.lo:u.flat.hi].copy_(u.shard)
             u.pending = self.g.all_gather(u.full, u.flat.sizes, async_op=True)
 
-    def _gather(self, u):
-        self._start_gather(u)
+    def _gather(self, u, forward=False):
+        self._start_gather(u, forward)
+        if u.pending_head is not None:
+            # fused unit: only what precedes the qkv weight (the first LayerNorm) is awaited here; the qkv GEMM
+            # brings its own weight and makes the stream wait for the rest afterwards
+            u.pending_head.wait()
+            u.pending_head = None
+            u.gathered = True
+            return
         if u.pending is not None:
             u.pending.wait()
             u.pending = None
@@ -323,9 +374,9 @@ class FSDP(torch.nn.Module):
     # ---- hooks
     def _before_forward(self, u):
         def hook(mod, args):
-            self._gather(u)
+            self._gather(u, forward=True)
             if self.prefetch and u.index + 1 < len(self.units):
-                self._start_gather(self.units[u.index + 1])
+                self._start_gather(self.units[u.index + 1], forward=True)
 
         return hook
 
@@ -353,10 +404,18 @@ class FSDP(torch.nn.Module):
         if u.staging is None:
             u.staging = self.g.empty(u.flat.numel, p.dtype, p.device, zero=False)
         a, b = u.flat.span(p)
-        u.staging[a:b].copy_(p.grad.reshape(-1))
+        if p.grad.is_cuda:
+            u.loose.append((u.staging[a:b].view_as(p), p.grad))
+        else:
+            u.staging[a:b].copy_(p.grad.reshape(-1))
         p.grad = None
         u.ready += 1
         if u.ready == len(u.flat.params):
+            if u.loose:
+                from ..ops import pack_into
+
+                pack_into(u.staging, u.loose)
+                u.loose = []
             # Backward through the unit is over: drop its parameters, ship its gradients.
             self._free(u)
             if self.g.fused and u.staging.is_cuda:  # the shard accumulation rides in the kernel's epilogue

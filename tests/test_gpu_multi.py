@@ -266,6 +266,47 @@ def test_fused_gather_gemm_over_peer_memory():
     assert launch(fused_gather_gemm_rank, 2, device="cuda") == [True, True]
 
 
+def fsdp_kernel_rank(g, fuse):
+    """FSDP over the hand-written kernels in bf16; with `fuse` each block's qkv GEMM gathers its own weight."""
+    from tandem_b200.data import synthetic
+    from tandem_b200.model import Config, GPT
+    from tandem_b200.ops.gemm import GATHERED, gemm_error
+    from tandem_b200.optim import ShardedAdamW
+    from tandem_b200.zero import FSDP
+
+    torch.manual_seed(0)
+    cfg = Config(seq=128, layers=3, heads=4, dim=256, kernels="b200")
+    text = synthetic(50_000)
+    model = GPT(cfg).to(g.device).bfloat16()
+    wrapped = FSDP(model, g, ShardedAdamW(lr=1e-3, weight_decay=0.1), fuse_gather_gemm=fuse)
+    fused_units = sum(u.fused is not None for u in wrapped.units)
+    losses = []
+    for step in range(4):
+        x, y = text.batch(step, 16, cfg.seq, rank=g.rank, world=g.size, device=g.device)
+        loss = wrapped(x, y)
+        loss.backward()
+        wrapped.step()
+        wrapped.zero_grad()
+        losses.append(loss.item())
+    w = wrapped.full_parameters().float().cpu()
+    g.check()
+    return losses, w, fused_units, len(GATHERED), gemm_error()
+
+
+@needs2
+def test_fsdp_with_qkv_weight_gathered_inside_the_gemm():
+    from tandem_b200 import launch
+
+    plain = launch(fsdp_kernel_rank, 2, False, device="cuda")
+    fused = launch(fsdp_kernel_rank, 2, True, device="cuda")
+    for r in range(2):
+        assert plain[r][2] == 0 and fused[r][2] == 3  # one fused GEMM per block
+        assert fused[r][3] == 0 and not fused[r][4]  # every registered gather was consumed; no kernel error
+        assert all(l == l and l < 7 for l in fused[r][0])
+        assert fused[r][0] == plain[r][0], (fused[r][0], plain[r][0])
+        assert torch.equal(fused[r][1], plain[r][1]), (fused[r][1] - plain[r][1]).abs().max()
+
+
 def nvls_rank(rank, world, init, out):
     """All-reduce through the NVSwitch multicast mapping (multimem.ld_reduce / multimem.st)."""
     import torch.distributed as dist

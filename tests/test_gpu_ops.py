@@ -221,7 +221,7 @@ def test_gemm_with_fused_weight_gather(n, rank):
     from tandem_b200.parallel.symm import split_offsets
 
     M, N, K = 1024, 2304, 768
-    before, after = 1536, 1003
+    before, after = 1536, 2304 + 1003
     flat = rnd(before + N * K + after, scale=0.3)
     offs = split_offsets(flat.numel(), n)
     shards = [flat[offs[q]:offs[q + 1]].clone() for q in range(n)]
@@ -234,3 +234,11 @@ def test_gemm_with_fused_weight_gather(n, rank):
         y = op(x, bias)
         close(y, x.float() @ w.float().t() + bias.float())
         assert torch.equal(full[before:before + N * K], flat[before:before + N * K])
+    # the bias sits right behind the weight in the flat buffer and is fetched with it
+    op2 = GatheredLinear([s.data_ptr() for s in shards], offs, rank, full, before, N, K, bias_follows=True)
+    b2 = flat[before + N * K:before + N * K + N]
+    for _ in range(2):
+        full.zero_()
+        y = op2(x, None)
+        close(y, x.float() @ w.float().t() + b2.float())
+        assert torch.equal(full[before:before + N * K + N], flat[before:before + N * K + N])
