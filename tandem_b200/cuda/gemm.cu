@@ -1,6 +1,9 @@
 // bf16 GEMM on the 5th-generation tensor cores: D[M,N] = A . B (+ epilogue), fp32 accumulation in TMEM.
 //
-// Structure (one persistent CTA per SM, 320 threads, no cluster, no TMA multicast):
+// Two kernels share the epilogue code: k_gemm (below: one persistent CTA per SM) and k_gemm_pair (further down: CTA
+// pairs driving tcgen05.mma.cta_group::2).  Neither uses TMA multicast.  Outputs in bf16 leave through TMA stores.
+//
+// Structure of k_gemm (one persistent CTA per SM, 320 threads, no cluster):
 //   warp 0      TMA producer: cp.async.bulk.tensor.2d loads A and B tiles (128B swizzle) into a
 //               3- to 6-stage shared-memory ring, signalling `full[s]` by transaction bytes.
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma.cta_group::1.kind::f16
@@ -8,9 +11,10 @@
 //               tcgen05.commit -> `empty[s]`, and hands a finished accumulator to the epilogue
 //               with tcgen05.commit -> `acc_full[b]`.  TMEM holds two accumulators (2 x BN
 //               columns), so the next tile's MMAs overlap this tile's epilogue.
-//   warps 2-9   epilogue: tcgen05.ld 32 lanes x 32 columns at a time (the next load in flight while
-//               one chunk is processed), then bias / GELU / residual / dGELU / accumulate in
-//               registers and 16-byte stores.
+//   warps 2-9   epilogue: tcgen05.ld 32 lanes x 64 columns at a time, then bias / GELU / residual /
+//               dGELU / accumulate in registers; a bf16 block is staged in shared memory (128-byte
+//               swizzle) and written by one cp.async.bulk.tensor store, fp32 outputs by 16-byte stores.
+// Tile shapes: 256x256, 128x256, 128x192, 128x128 (choose_tile); split-K for outputs with very few tiles.
 //
 // Operand layouts.  Each operand is either K-major (the reduction dimension is contiguous in
 // global memory) or MN-major (the other dimension is).  That covers all three GEMMs of a linear
@@ -30,6 +34,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "tcgen05.cuh"
 
@@ -60,6 +65,13 @@ struct GemmArgs {
   const __nv_bfloat16* aux_in;   // residual or pre-activation, [M, ldc]
   __nv_bfloat16* aux_out;        // pre-activation out for EPI_GELU, [M, ldc]
   int* error;                    // host-mapped; set to 1 when a wait runs out
+  int tma_store;                 // map_out (and map_pre) are valid: bf16 output blocks leave through TMA stores
+  // Split-K (splits > 1): the reduction range is cut into `splits` parts, each (tile, part) is one work item, and part
+  // p stores its fp32 partial tile to partials + p * partial_stride (same [M, ldc] layout as out) with no epilogue;
+  // tb_splitk_reduce() then sums the parts in a fixed order and applies the output conversion.
+  int splits;
+  float* partials;
+  long long partial_stride;
 };
 
 // All-gather fused into the GEMM (B operand = a weight whose flat bytes are sharded over the ranks).
@@ -119,7 +131,8 @@ __device__ __forceinline__ float gelu_grad(float x) {
 
 // ------------------------------------------------------------------------------------------ kernel
 // One 32-column chunk of one accumulator row: the general path (tile edges, padded rows, any flags).
-__device__ __forceinline__ void epilogue_chunk_generic(const uint32_t (&raw)[32], int row, int col0, const GemmArgs& g, bool out_f32) {
+__device__ __forceinline__ void epilogue_chunk_generic(const uint32_t (&raw)[32], int row, int col0, const GemmArgs& g, void* out,
+                                                       bool out_f32) {
   if (row < g.M && col0 < g.N) {
     const size_t base = (size_t)row * g.ldc + col0;
 #pragma unroll
@@ -164,7 +177,7 @@ __device__ __forceinline__ void epilogue_chunk_generic(const uint32_t (&raw)[32]
         for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
       }
       if (out_f32) {
-        float* o = reinterpret_cast<float*>(g.out) + base + v8 * 8;
+        float* o = reinterpret_cast<float*>(out) + base + v8 * 8;
         if (full8) {
           float4 lo = make_float4(x[0], x[1], x[2], x[3]), hi = make_float4(x[4], x[5], x[6], x[7]);
           if (g.flags & EPI_ACCUMULATE) {
@@ -179,7 +192,7 @@ __device__ __forceinline__ void epilogue_chunk_generic(const uint32_t (&raw)[32]
             if (col + j < g.N) o[j] = (g.flags & EPI_ACCUMULATE) ? o[j] + x[j] : x[j];
         }
       } else {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + base + v8 * 8;
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + base + v8 * 8;
         __nv_bfloat16 y[8];
         if (g.flags & EPI_ACCUMULATE) {
           if (full8) {
@@ -205,8 +218,8 @@ __device__ __forceinline__ void epilogue_chunk_generic(const uint32_t (&raw)[32]
 
 // The same for a chunk that lies wholly inside the matrix with 16-byte-aligned rows: no per-element
 // bounds checks, bias fetched as four 16-byte vectors.
-__device__ __forceinline__ void epilogue_chunk_interior(const uint32_t (&raw)[32], int row, int col0, const GemmArgs& g, bool out_f32,
-                                                        bool bias_vec) {
+__device__ __forceinline__ void epilogue_chunk_interior(const uint32_t (&raw)[32], int row, int col0, const GemmArgs& g, void* out,
+                                                        bool out_f32, bool bias_vec) {
   const size_t base = (size_t)row * g.ldc + col0;
 #pragma unroll
   for (int v8 = 0; v8 < 4; ++v8) {
@@ -244,7 +257,7 @@ __device__ __forceinline__ void epilogue_chunk_interior(const uint32_t (&raw)[32
       for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
     }
     if (out_f32) {
-      float* o = reinterpret_cast<float*>(g.out) + base + v8 * 8;
+      float* o = reinterpret_cast<float*>(out) + base + v8 * 8;
       float4 lo = make_float4(x[0], x[1], x[2], x[3]), hi = make_float4(x[4], x[5], x[6], x[7]);
       if (g.flags & EPI_ACCUMULATE) {
         const float4 a = *reinterpret_cast<const float4*>(o), b = *reinterpret_cast<const float4*>(o + 4);
@@ -254,7 +267,7 @@ __device__ __forceinline__ void epilogue_chunk_interior(const uint32_t (&raw)[32
       *reinterpret_cast<float4*>(o) = lo;
       *reinterpret_cast<float4*>(o + 4) = hi;
     } else {
-      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + base + v8 * 8;
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + base + v8 * 8;
       if (g.flags & EPI_ACCUMULATE) {
         __nv_bfloat16 y[8];
         *reinterpret_cast<uint4*>(y) = *reinterpret_cast<const uint4*>(o);
@@ -269,12 +282,32 @@ __device__ __forceinline__ void epilogue_chunk_interior(const uint32_t (&raw)[32
   }
 }
 
-// Writes a warp's 32-row x 64-column bf16 block (lane = row, `v` = that row's 128 bytes as eight
-// 16-byte vectors) to row-major global memory through shared memory, so that each store instruction
-// covers four complete 128-byte lines instead of 32 scattered 16-byte pieces.  The 16-byte slots are
-// XOR-swizzled by row so neither the writes (lane = row) nor the reads (8 lanes per row) conflict.
-__device__ __forceinline__ void store_block_coalesced(uint8_t* stage, const uint4 (&v)[8], __nv_bfloat16* out, size_t ldc,
-                                                      int row0, int rows_valid, int col0, int lane, bool skip) {
+// Writes a warp's 32-row x 64-column bf16 block (lane = row, `v` = that row's 128 bytes as eight 16-byte
+// vectors) to row-major global memory through a 4 KB shared-memory block.  The 16-byte slots are
+// XOR-swizzled by row, which is both conflict-free for the writes (lane = row) and the 128-byte swizzle
+// of a TMA tile.
+//   map != nullptr: one cp.async.bulk.tensor store of the block {64 columns, 32 rows} at (col0, row0); the
+//     tensor map clips rows >= M and columns >= N.  Shared memory carries the bytes once in and once out, and
+//     the stores never pass through the load/store unit, whose global stores (measured on B200) slow the
+//     MMA/TMA traffic of the main loop several times more than their size would suggest.
+//   map == nullptr: the warp reads the block back and stores complete 128-byte lines itself.
+__device__ __forceinline__ void store_block(uint8_t* stage, const uint4 (&v)[8], const CUtensorMap* map, __nv_bfloat16* out, size_t ldc,
+                                            int row0, int rows_valid, int col0, int lane, bool skip) {
+  if (map != nullptr) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous store has read the block
+    __syncwarp();
+#pragma unroll
+    for (int sgm = 0; sgm < 8; ++sgm) *reinterpret_cast<uint4*>(stage + lane * 128 + ((sgm ^ (lane & 7)) << 4)) = v[sgm];
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, then the async proxy's read
+    __syncwarp();
+    if (lane == 0 && !skip) {
+      asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_u32(stage)),
+                   "r"(col0), "r"(row0)
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    return;
+  }
   __syncwarp();
 #pragma unroll
   for (int sgm = 0; sgm < 8; ++sgm) *reinterpret_cast<uint4*>(stage + lane * 128 + ((sgm ^ (lane & 7)) << 4)) = v[sgm];
@@ -289,10 +322,17 @@ __device__ __forceinline__ void store_block_coalesced(uint8_t* stage, const uint
   }
 }
 
+// Before an epilogue warp leaves: its bulk stores have completed.
+__device__ __forceinline__ void drain_stores(int lane) {
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  __syncwarp();
+}
+
 // Two adjacent 32-column chunks (64 columns) of an interior tile with a bf16 output: element-wise
 // work in registers, then coalesced stores of the result (and of the pre-activation, if kept).
 __device__ __forceinline__ void epilogue_pair_interior(const uint32_t (&ra)[32], const uint32_t (&rb)[32], uint8_t* stage, int row,
-                                                       int row0, int rows_valid, int col0, const GemmArgs& g, bool bias_vec, int lane) {
+                                                       int row0, int rows_valid, int col0, const GemmArgs& g, void* out, bool bias_vec,
+                                                       int lane, const CUtensorMap* map_out, const CUtensorMap* map_pre) {
   uint4 outv[8], prev[8];
   const bool keep_pre = (g.flags & EPI_GELU) && g.aux_out != nullptr;
   const bool row_ok = row < g.M;
@@ -316,7 +356,7 @@ __device__ __forceinline__ void epilogue_pair_interior(const uint32_t (&ra)[32],
     if (g.flags & (EPI_RESIDUAL | EPI_DGELU | EPI_ACCUMULATE)) {
       __nv_bfloat16 aux[8];
       const __nv_bfloat16* src = (g.flags & EPI_ACCUMULATE) && !(g.flags & (EPI_RESIDUAL | EPI_DGELU))
-                                     ? reinterpret_cast<const __nv_bfloat16*>(g.out) : g.aux_in;
+                                     ? reinterpret_cast<const __nv_bfloat16*>(out) : g.aux_in;
       *reinterpret_cast<uint4*>(aux) = *reinterpret_cast<const uint4*>(src + base + v8 * 8);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -336,8 +376,8 @@ __device__ __forceinline__ void epilogue_pair_interior(const uint32_t (&ra)[32],
     for (int j = 0; j < 4; ++j) oo[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
   }
   const bool skip = g.flags & EPI_NO_STORE;
-  store_block_coalesced(stage, outv, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, row0, rows_valid, col0, lane, skip);
-  if (keep_pre) store_block_coalesced(stage, prev, g.aux_out, g.ldc, row0, rows_valid, col0, lane, skip);
+  store_block(stage, outv, map_out, reinterpret_cast<__nv_bfloat16*>(out), g.ldc, row0, rows_valid, col0, lane, skip);
+  if (keep_pre) store_block(stage, prev, map_pre, g.aux_out, g.ldc, row0, rows_valid, col0, lane, skip);
 }
 
 // Tile shapes.  BM = 128: one 128-row accumulator per tile, two of them in TMEM so the next tile's
@@ -356,7 +396,10 @@ struct SmemLayout {
 
 template <int BM, int BN, bool A_MN, bool B_MN, bool GATHER = false>
 __global__ void __launch_bounds__(GATHER ? 384 : 320, 1)
-k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g, const GatherArgs ga) {
+k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_out,
+       const __grid_constant__ CUtensorMap map_pre, const GemmArgs g, const GatherArgs ga) {
+  const CUtensorMap* out_map = g.tma_store ? &map_out : nullptr;
+  const CUtensorMap* pre_map = g.tma_store ? &map_pre : nullptr;
   extern __shared__ uint8_t smem_raw[];
   using L = SmemLayout<BM, BN>;
   constexpr int STAGES = L::STAGES;
@@ -370,12 +413,21 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int k_blocks = (g.K + BK - 1) / BK;
-  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: a power of two
+  const int splits = g.splits > 1 ? g.splits : 1;
+  const int num_tiles = tiles_m * tiles_n * splits;  // work items: item -> output tile (item % tiles), k-part (item / tiles)
+  const int k_blocks_all = (g.K + BK - 1) / BK;
+  const int k_per = (k_blocks_all + splits - 1) / splits;
+  auto k_range = [&](int item, int* kb0, int* kb1) {
+    const int part = item / (tiles_m * tiles_n);
+    *kb0 = part * k_per;
+    *kb1 = (part + 1) * k_per < k_blocks_all ? (part + 1) * k_per : k_blocks_all;
+  };
+  constexpr uint32_t ACC_COLS = BN == 192 ? 256 : BN;  // column stride between the two accumulators
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;         // 256 or 512: a power of two
   // Tile t -> (m0, n0).  m runs fastest, so the CTAs sweep one weight panel at a time; with GATHER the panels
   // are visited starting from the one this rank's own shard feeds, the order in which the chunks arrive.
-  auto tile_origin = [&](int tile, int* m0, int* n0) {
+  auto tile_origin = [&](int item, int* m0, int* n0) {
+    const int tile = item % (tiles_m * tiles_n);
     int n_idx = tile / tiles_m;
     if (GATHER) n_idx = (n_idx + ga.n_start) % tiles_n;
     *m0 = (tile % tiles_m) * BM;
@@ -416,7 +468,9 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
           if (!(ok = wait_chunks(ga.ready, (int)(lo / ga.chunk_bytes), (int)((hi - 1) / ga.chunk_bytes), ga.epoch, g.error))) break;
           asm volatile("fence.proxy.async;" ::: "memory");  // the fetchers' generic-proxy stores, then TMA's async-proxy loads
         }
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        int kb0, kb1;
+        k_range(tile, &kb0, &kb1);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
           if (!(ok = mbar_wait(&empty[s], phase ^ 1, g.error))) break;
@@ -450,7 +504,9 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
         // BM = 128: accumulators alternate between the two TMEM regions.  BM = 256: region h holds rows [128h, 128h+128).
         const uint32_t first_buf = HALVES == 1 ? (local_tile & 1) : 0;
         const uint32_t acc_phase = HALVES == 1 ? ((local_tile >> 1) & 1) : (local_tile & 1);
-        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+        int kb0, kb1;
+        k_range(tile, &kb0, &kb1);
+        for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
           if (!(ok = mbar_wait(&full[s], phase, g.error))) break;
@@ -463,18 +519,18 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
 #pragma unroll
           for (int h = 0; h < HALVES; ++h) {
             const uint32_t buf = first_buf + h;
-            if (kb == 0) {  // the epilogue has drained this accumulator
+            if (kb == kb0) {  // the epilogue has drained this accumulator
               if (!(ok = mbar_wait(&acc_empty[buf], acc_phase ^ 1, g.error))) break;
               tc_fence_after();
             }
-            const uint32_t d_tmem = tmem_base + buf * BN;
+            const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
             const uint32_t a_half = a_addr + h * 16384;  // 128 rows x 128 B, or two 64-wide strips
             const uint64_t a_desc = A_MN ? smem_desc(a_half, 8192, 1024) : smem_desc(a_half, 16, 1024);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               const uint64_t a_k = a_desc + (uint64_t)((A_MN ? 2048 : 32) * k >> 4);
               const uint64_t b_k = b_desc + (uint64_t)((B_MN ? 2048 : 32) * k >> 4);
-              mma_bf16(d_tmem, a_k, b_k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              mma_bf16(d_tmem, a_k, b_k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
             }
           }
           if (ok) mma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
@@ -531,7 +587,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
     const int half = BM == 128 ? 0 : group;
     uint32_t local_tile = 0;
     bool ok = true;
-    const bool out_f32 = g.flags & EPI_OUT_F32;
+    const bool out_f32 = g.flags & EPI_OUT_F32;  // split-K: the host passes "store the fp32 partial tile" as the flags
     if (GATHER && (g.flags & EPI_BIAS) && ga.tail_bytes > 0) {
       // the bias sits right behind the weight in the flat buffer and is fetched with it: wait for its chunks
       const long long lo = (long long)g.N * g.K * 2, hi = lo + ga.tail_bytes;
@@ -541,20 +597,22 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       int m0, n0;
       tile_origin(tile, &m0, &n0);
+      void* out = splits > 1 ? (void*)(g.partials + (long long)(tile / (tiles_m * tiles_n)) * g.partial_stride) : g.out;
       const uint32_t buf = BM == 128 ? (local_tile & 1) : half;
       const uint32_t acc_phase = BM == 128 ? ((local_tile >> 1) & 1) : (local_tile & 1);
-      ok = mbar_wait(&acc_full[buf], acc_phase, g.error);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(&acc_full[buf], acc_phase, g.error);
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + half * 128 + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS;
       // Chunks of 32 columns, the TMEM load of the next one in flight while this one is processed.
-      const bool interior_rows = row < g.M && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0;
+      const bool interior_rows = row < g.M && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
       const bool bias_vec = (g.flags & EPI_BIAS) && (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0;
       constexpr int CHUNKS = BN / 32;
-      const int c_begin = BM == 128 ? group * (CHUNKS / 2) : 0;
-      const int c_end = BM == 128 ? c_begin + CHUNKS / 2 : CHUNKS;
+      // BM = 128: the two warp groups split the columns (BN = 192: four chunks and two, so each takes whole pairs)
+      const int c_split = BN == 192 ? 4 : CHUNKS / 2;
+      const int c_begin = BM == 128 ? group * c_split : 0;
+      const int c_end = BM == 128 ? (group == 0 ? c_split : CHUNKS) : CHUNKS;
       if (!(g.flags & EPI_DISCARD)) {
         uint32_t ra[32], rb[32];
         uint8_t* stage = staging + (warp - 2) * 4096;
@@ -562,7 +620,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
         const int rows_valid = g.M - row0 < 32 ? g.M - row0 : 32;   // may be <= 0 on the last tile row
         // bf16 outputs whose rows are 16-byte aligned go through the coalescing path; accumulate-with-aux combinations
         // and fp32 outputs take the direct path.
-        const bool pair_ok = !out_f32 && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && rows_valid > 0 &&
+        const bool pair_ok = !out_f32 && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && rows_valid > 0 &&
                              !((g.flags & EPI_ACCUMULATE) && (g.flags & (EPI_RESIDUAL | EPI_DGELU)));
 #pragma unroll 1
         for (int c = c_begin; c < c_end; c += 2) {  // c_end - c_begin is even: 2 or 4 or 8 chunks
@@ -575,12 +633,12 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
             continue;
           }
           if (pair_ok && col0 + 64 <= g.N) {
-            epilogue_pair_interior(ra, rb, stage, row, row0, rows_valid, col0, g, bias_vec, lane);
+            epilogue_pair_interior(ra, rb, stage, row, row0, rows_valid, col0, g, out, bias_vec, lane, out_map, pre_map);
           } else {
-            if (interior_rows && col0 + 32 <= g.N) epilogue_chunk_interior(ra, row, col0, g, out_f32, bias_vec);
-            else epilogue_chunk_generic(ra, row, col0, g, out_f32);
-            if (interior_rows && col0 + 64 <= g.N) epilogue_chunk_interior(rb, row, col0 + 32, g, out_f32, bias_vec);
-            else epilogue_chunk_generic(rb, row, col0 + 32, g, out_f32);
+            if (interior_rows && col0 + 32 <= g.N) epilogue_chunk_interior(ra, row, col0, g, out, out_f32, bias_vec);
+            else epilogue_chunk_generic(ra, row, col0, g, out, out_f32);
+            if (interior_rows && col0 + 64 <= g.N) epilogue_chunk_interior(rb, row, col0 + 32, g, out, out_f32, bias_vec);
+            else epilogue_chunk_generic(rb, row, col0 + 32, g, out, out_f32);
           }
         }
       }
@@ -588,6 +646,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    drain_stores(lane);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -596,6 +655,231 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------ CTA-pair kernel
+// The same GEMM with tcgen05.mma.cta_group::2: two CTAs of a cluster, on neighbouring SMs, compute one
+// 256 x BN tile together.  Each CTA loads its own 128 rows of A and HALF of the B tile (BN/2 rows), and the
+// leader's MMA instructions read B from both CTAs' shared memory, so per flop each SM moves a third less
+// operand data through TMA and reads a third less of it from shared memory than the 128 x 256 single-CTA
+// tile -- the resource that bounds the single-CTA kernel.  Roles per CTA are the same as above (warp 0 TMA
+// producer, warp 1 MMA issuer in the leader only, warps 2-9 epilogue of this CTA's 128 accumulator rows).
+//   full[s]       leader's barrier: one arrive.expect_tx by the leader's producer + the bytes of BOTH CTAs' loads
+//   empty[s]      each CTA's own barrier, signalled in both by one multicast tcgen05.commit
+//   acc_full[b]   each CTA's own barrier, signalled in both by one multicast tcgen05.commit
+//   acc_empty[b]  leader's barrier: 16 arrivals, one per epilogue warp of either CTA
+// No TMA load uses multicast: each CTA reads its own tiles from global memory.
+template <int BN>
+struct PairLayout {
+  static constexpr int A_BYTES = 128 * BK * 2;       // this CTA's 128 rows of the 256-row A tile
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;  // this CTA's half of the B tile
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES > 8 ? 8 : SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_STAGING + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int THREADS = 64 + 256;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+k_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_out,
+            const __grid_constant__ CUtensorMap map_pre, const GemmArgs g) {
+  const CUtensorMap* out_map = g.tma_store ? &map_out : nullptr;
+  const CUtensorMap* pre_map = g.tma_store ? &map_pre : nullptr;
+  extern __shared__ uint8_t smem_raw[];
+  using L = PairLayout<BN>;
+  constexpr int STAGES = L::STAGES;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = smem + STAGES * L::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + EPI_STAGING);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: the leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int tiles_m = (g.M + 255) / 256, tiles_n = (g.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (g.K + BK - 1) / BK;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators of BN fp32 columns
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 16);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // both CTAs' barriers are initialised before either one signals the other's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % tiles_m) * 256 + (int)rank * 128;
+        const int n0 = (tile / tiles_m) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&empty[s], phase ^ 1, g.error))) break;
+          uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + L::A_BYTES;
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * L::STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d_pair(a_dst, &map_a, bar, k0, m0);  // box {64 k, 128 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * 8192, &map_a, bar, m0 + j * 64, k0);  // box {64 m, 64 k}
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(b_dst, &map_b, bar, k0, n0);  // box {64 k, BN/2 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(b_dst + j * 8192, &map_b, bar, n0 + j * 64, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = instr_desc(256, BN, A_MN, B_MN);
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+        const uint32_t buf = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&full[s], phase, g.error))) break;
+          tc_fence_after();
+          if (kb == 0) {  // both CTAs' epilogues have drained this accumulator
+            if (!(ok = mbar_wait(&acc_empty[buf], acc_phase ^ 1, g.error))) break;
+            tc_fence_after();
+          }
+          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+          const uint64_t a_desc = A_MN ? smem_desc(a_addr, 8192, 1024) : smem_desc(a_addr, 16, 1024);
+          const uint64_t b_desc = B_MN ? smem_desc(b_addr, 8192, 1024) : smem_desc(b_addr, 16, 1024);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t a_k = a_desc + (uint64_t)((A_MN ? 2048 : 32) * k >> 4);
+            const uint64_t b_k = b_desc + (uint64_t)((B_MN ? 2048 : 32) * k >> 4);
+            mma_bf16_pair(d_tmem, a_k, b_k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit_pair(&empty[s], 3);  // both CTAs may refill the stage once these MMAs have read it
+        }
+        if (ok) mma_commit_pair(&acc_full[buf], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2 .. 9, both CTAs)
+    const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
+    uint32_t local_tile = 0;
+    bool ok = true;
+    const bool out_f32 = g.flags & EPI_OUT_F32;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+      const int m0 = (tile % tiles_m) * 256 + (int)rank * 128;
+      const int n0 = (tile / tiles_m) * BN;
+      const uint32_t buf = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      ok = mbar_wait_warp(&acc_full[buf], acc_phase, g.error);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      const bool interior_rows = row < g.M && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0;
+      const bool bias_vec = (g.flags & EPI_BIAS) && (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0;
+      constexpr int CHUNKS = BN / 32;
+      const int c_begin = group * (CHUNKS / 2), c_end = c_begin + CHUNKS / 2;
+      if (!(g.flags & EPI_DISCARD)) {
+        uint32_t ra[32], rb[32];
+        uint8_t* stage = staging + (warp - 2) * 4096;
+        const int row0 = m0 + quarter * 32;
+        const int rows_valid = g.M - row0 < 32 ? g.M - row0 : 32;
+        const bool pair_ok = !out_f32 && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && rows_valid > 0 &&
+                             !((g.flags & EPI_ACCUMULATE) && (g.flags & (EPI_RESIDUAL | EPI_DGELU)));
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; c += 2) {
+          tmem_ld32(taddr + c * 32, ra);
+          tmem_ld32(taddr + (c + 1) * 32, rb);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (g.flags & EPI_LOAD_ONLY) {
+            if (ra[0] == 0x7fc0dead && rb[31] == 0x7fc0dead) stage[0] = 1;
+            continue;
+          }
+          if (pair_ok && col0 + 64 <= g.N) {
+            epilogue_pair_interior(ra, rb, stage, row, row0, rows_valid, col0, g, g.out, bias_vec, lane, out_map, pre_map);
+          } else {
+            if (interior_rows && col0 + 32 <= g.N) epilogue_chunk_interior(ra, row, col0, g, g.out, out_f32, bias_vec);
+            else epilogue_chunk_generic(ra, row, col0, g, g.out, out_f32);
+            if (interior_rows && col0 + 64 <= g.N) epilogue_chunk_interior(rb, row, col0 + 32, g, g.out, out_f32, bias_vec);
+            else epilogue_chunk_generic(rb, row, col0 + 32, g, g.out, out_f32);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+    drain_stores(lane);
+  }
+
+  // ------------------------------------------------------------------ teardown
+  // Neither CTA may leave (or free TMEM) while its partner can still signal its barriers or read its tiles.
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+
+// Sums split-K partial tiles (fp32, fixed order) into the bf16 output, four columns per thread.
+__global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__ partials, int splits, long long stride, long long quads,
+                                                        int N, int ldc, __nv_bfloat16* __restrict__ out, bool accumulate) {
+  const int per_row = ldc / 4;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (long long)gridDim.x * blockDim.x) {
+    const int col = (int)(q % per_row) * 4;
+    if (col >= N) continue;  // row padding
+    float4 acc = *reinterpret_cast<const float4*>(partials + q * 4);
+    for (int p = 1; p < splits; ++p) {
+      const float4 v = *reinterpret_cast<const float4*>(partials + p * stride + q * 4);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat16* o = out + q * 4;
+    float r[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col + j < N) {
+        if (accumulate) r[j] += __bfloat162float(o[j]);
+        o[j] = __float2bfloat16_rn(r[j]);
+      }
+    }
   }
 }
 
@@ -642,12 +926,27 @@ int make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
+// Tensor maps for the epilogue's TMA stores: 32-row x 64-column bf16 blocks of out (and of the kept pre-activation).
+// Returns 1 if the output qualifies (bf16, 16-byte aligned rows), 0 if the epilogue must store by itself.
+int g_tma_store_enabled = 1;
+int make_store_maps(CUtensorMap* mo, CUtensorMap* mp, void* out, void* aux_out, int M, int N, int ldc, int flags) {
+  memset(mo, 0, sizeof(*mo));
+  memset(mp, 0, sizeof(*mp));
+  if (!g_tma_store_enabled || (flags & EPI_OUT_F32) || (ldc & 7) || ((uintptr_t)out & 15) || N < 64 || M < 32) return 0;
+  const bool keep_pre = (flags & EPI_GELU) && aux_out != nullptr;
+  if (keep_pre && ((uintptr_t)aux_out & 15)) return 0;
+  if (make_map(mo, out, N, M, ldc, 64, 32)) return 0;
+  if (keep_pre && make_map(mp, aux_out, N, M, ldc, 64, 32)) return 0;
+  return 1;
+}
+
 int* g_error_host = nullptr;
 int* g_error_dev = nullptr;
 int g_sm_count = 0;
 
 template <int BM, int BN, bool A_MN, bool B_MN>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int max_ctas, cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mp, const GemmArgs& g, int max_ctas,
+                cudaStream_t stream) {
   auto kernel = k_gemm<BM, BN, A_MN, B_MN>;
   using L = SmemLayout<BM, BN>;
   static bool configured = false;
@@ -656,10 +955,45 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * g.splits;
   int ctas = tiles < g_sm_count ? tiles : g_sm_count;
   if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
-  kernel<<<ctas, L::THREADS, L::TOTAL, stream>>>(ma, mb, g, GatherArgs{});
+  kernel<<<ctas, L::THREADS, L::TOTAL, stream>>>(ma, mb, mo, mp, g, GatherArgs{});
+  return (int)cudaGetLastError();
+}
+
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mp, const GemmArgs& g,
+                     int max_ctas, cudaStream_t stream) {
+  auto kernel = k_gemm_pair<BN, A_MN, B_MN>;
+  using L = PairLayout<BN>;
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(g_sm_count & ~1);
+    cfg.blockDim = dim3(L::THREADS);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = g_sm_count / 2;
+    }
+    max_pairs = n < g_sm_count / 2 ? n : g_sm_count / 2;
+  }
+  const int tiles = ((g.M + 255) / 256) * ((g.N + BN - 1) / BN);
+  int pairs = tiles < max_pairs ? tiles : max_pairs;
+  if (max_ctas > 1 && pairs > max_ctas / 2) pairs = max_ctas / 2;
+  kernel<<<2 * pairs, L::THREADS, L::TOTAL, stream>>>(ma, mb, mo, mp, g);
   return (int)cudaGetLastError();
 }
 
@@ -670,10 +1004,20 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
 // weight-gradient shapes (few output tiles, K = tokens) want 128x128 tiles to fill the machine.
 void choose_tile(int M, int N, int K, int sms, int forced, int* bm, int* bn) {
   struct Shape { int bm, bn; double cost; };  // cost: relative time of one tile at equal K
-  const Shape shapes[3] = {{256, 256, K <= 1024 ? 5.0 : 4.0}, {128, 256, 2.3}, {128, 128, 1.5}};
+  const Shape shapes[4] = {{256, 256, K <= 1024 ? 5.0 : 4.0}, {128, 256, 2.3}, {128, 128, 1.5}, {128, 192, 1.8}};
   if (forced >= 0 && forced < 3) {
     *bm = shapes[forced].bm;
     *bn = shapes[forced].bn;
+    return;
+  }
+  if (forced == 3 || forced == 4) {  // CTA-pair kernel (bm = 512 marks it): 256 x 256 or 256 x 128 per pair
+    *bm = 512;
+    *bn = forced == 3 ? 256 : 128;
+    return;
+  }
+  if (forced == 5) {
+    *bm = 128;
+    *bn = 192;
     return;
   }
   double best = 1e30;
@@ -691,6 +1035,7 @@ void choose_tile(int M, int N, int K, int sms, int forced, int* bm, int* bn) {
 }
 
 int g_forced_tile = -1;
+int g_forced_splits = 0;
 
 }  // namespace
 
@@ -705,9 +1050,14 @@ int tb_gemm_error() { return g_error_host != nullptr ? *g_error_host : 0; }
 //   a_mn == 0: A is [M, K] with leading dimension lda (K contiguous); a_mn == 1: A is [K, M], lda (M contiguous).
 //   b_mn == 0: B is [N, K] with leading dimension ldb (K contiguous); b_mn == 1: B is [K, N], ldb (N contiguous).
 // Leading dimensions must be multiples of 8 elements and base pointers 16-byte aligned (TMA).
-int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
-                 int flags, const void* bias, const void* aux_in, void* aux_out, int max_ctas, cudaStream_t stream) {
+int tb_gemm_bf16_splitk(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
+                        int flags, const void* bias, const void* aux_in, void* aux_out, int max_ctas, int splits, void* partials,
+                        cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (splits > 1) {
+    const int k_blocks = (K + 63) / 64, k_per = (k_blocks + splits - 1) / splits;
+    if (partials == nullptr || ((uintptr_t)partials & 15) || (ldc & 3) || (splits - 1) * k_per >= k_blocks) return -14;  // no empty part
+  }
   if ((lda & 7) || (ldb & 7) || (((uintptr_t)A | (uintptr_t)B) & 15)) return -12;
   if (g_error_host == nullptr) {
     if (cudaHostAlloc((void**)&g_error_host, 64, cudaHostAllocMapped) != cudaSuccess) return -13;
@@ -719,27 +1069,94 @@ int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, i
   }
   int BM = 128, BN = 128;
   choose_tile(M, N, K, g_sm_count, g_forced_tile, &BM, &BN);
+  if (splits > 1 && (BM == 512 || BN == 192 || g_forced_tile < 0)) {
+    // few output tiles and a long reduction: large single-CTA tiles, the parts fill the machine
+    BM = 128;
+    BN = N > 128 ? 256 : 128;
+  }
+  const bool paired = BM == 512;  // a 256 x BN tile shared by a CTA pair: per CTA 128 rows of A, BN/2 rows of B
   CUtensorMap ma, mb;
   int rc;
-  if (!a_mn) rc = make_map(&ma, A, K, M, lda, 64, BM);
+  if (!a_mn) rc = make_map(&ma, A, K, M, lda, 64, paired ? 128 : BM);
   else rc = make_map(&ma, A, M, K, lda, 64, 64);
   if (rc) return rc;
-  if (!b_mn) rc = make_map(&mb, B, K, N, ldb, 64, BN);
+  if (!b_mn) rc = make_map(&mb, B, K, N, ldb, 64, paired ? BN / 2 : BN);
   else rc = make_map(&mb, B, N, K, ldb, 64, 64);
   if (rc) return rc;
-  GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev};
+  CUtensorMap mo, mp;
+  const int tma_store = splits > 1 ? 0 : make_store_maps(&mo, &mp, out, aux_out, M, N, ldc, flags);
+  if (splits > 1) {
+    memset(&mo, 0, sizeof(mo));
+    memset(&mp, 0, sizeof(mp));
+  }
+  // with split-K each part only stores its fp32 partial tile; tb_splitk_reduce applies the rest
+  const int kflags = splits > 1 ? (EPI_OUT_F32 | (flags & (EPI_DISCARD | EPI_NO_STORE | EPI_LOAD_ONLY))) : flags;
+  GemmArgs g{M, N, K, ldc, kflags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev, tma_store,
+             splits > 1 ? splits : 1, (float*)partials, (long long)M * ldc};
   tb_note_launch(1);
+#define GO2(BN_) \
+  do { \
+    if (!a_mn && !b_mn) return launch_gemm_pair<BN_, false, false>(ma, mb, mo, mp, g, max_ctas, stream); \
+    if (!a_mn && b_mn) return launch_gemm_pair<BN_, false, true>(ma, mb, mo, mp, g, max_ctas, stream); \
+    if (a_mn && b_mn) return launch_gemm_pair<BN_, true, true>(ma, mb, mo, mp, g, max_ctas, stream); \
+    return launch_gemm_pair<BN_, true, false>(ma, mb, mo, mp, g, max_ctas, stream); \
+  } while (0)
+  if (paired && BN == 256) GO2(256);
+  if (paired) GO2(128);
+#undef GO2
 #define GO(BM_, BN_) \
   do { \
-    if (!a_mn && !b_mn) return launch_gemm<BM_, BN_, false, false>(ma, mb, g, max_ctas, stream); \
-    if (!a_mn && b_mn) return launch_gemm<BM_, BN_, false, true>(ma, mb, g, max_ctas, stream); \
-    if (a_mn && b_mn) return launch_gemm<BM_, BN_, true, true>(ma, mb, g, max_ctas, stream); \
-    return launch_gemm<BM_, BN_, true, false>(ma, mb, g, max_ctas, stream); \
+    if (!a_mn && !b_mn) return launch_gemm<BM_, BN_, false, false>(ma, mb, mo, mp, g, max_ctas, stream); \
+    if (!a_mn && b_mn) return launch_gemm<BM_, BN_, false, true>(ma, mb, mo, mp, g, max_ctas, stream); \
+    if (a_mn && b_mn) return launch_gemm<BM_, BN_, true, true>(ma, mb, mo, mp, g, max_ctas, stream); \
+    return launch_gemm<BM_, BN_, true, false>(ma, mb, mo, mp, g, max_ctas, stream); \
   } while (0)
   if (BM == 256) GO(256, 256);
   if (BN == 256) GO(128, 256);
+  if (BN == 192) GO(128, 192);
   GO(128, 128);
 #undef GO
+}
+
+int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
+                 int flags, const void* bias, const void* aux_in, void* aux_out, int max_ctas, cudaStream_t stream) {
+  return tb_gemm_bf16_splitk(A, B, out, M, N, K, lda, ldb, ldc, a_mn, b_mn, flags, bias, aux_in, aux_out, max_ctas, 1, nullptr, stream);
+}
+
+// How many parts to cut the reduction into (1: do not split).  Splitting pays when the output has too few 128 x 256
+// tiles to occupy even a quarter of the SMs and the reduction is long -- the square weight gradients, whose K is the
+// token count (measured on B200: 768 x 768 x 8192 goes from 52 to 34 us; at 72 tiles the split no longer pays).
+int tb_gemm_splits(int M, int N, int K) {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (g_forced_splits > 0) return g_forced_splits;
+  const int tiles = ((M + 127) / 128) * ((N + (N > 128 ? 255 : 127)) / (N > 128 ? 256 : 128));
+  const int k_blocks = (K + 63) / 64;
+  if (tiles * 4 > g_sm_count || k_blocks < 32) return 1;
+  int s = g_sm_count / tiles;
+  if (s > k_blocks / 16) s = k_blocks / 16;
+  if (s > 8) s = 8;
+  while (s > 1 && (s - 1) * ((k_blocks + s - 1) / s) >= k_blocks) --s;  // no empty part
+  return s < 1 ? 1 : s;
+}
+
+void tb_gemm_force_splits(int n) { g_forced_splits = n; }
+
+// out[M, N] (bf16, row stride ldc) = sum over the parts, in order, of partials[p][M, ldc] (fp32); with
+// EPI_ACCUMULATE in `flags`, added to what out holds.
+int tb_splitk_reduce(const void* partials, int splits, int M, int N, int ldc, void* out, int flags, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  const long long quads = (long long)M * (ldc / 4);
+  const int threads = 256;
+  long long blocks = (quads + threads - 1) / threads;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  tb_note_launch(1);
+  k_splitk_reduce<<<(int)blocks, threads, 0, stream>>>((const float*)partials, splits, (long long)M * ldc, quads, N, ldc,
+                                                     (__nv_bfloat16*)out, (flags & EPI_ACCUMULATE) != 0);
+  return (int)cudaGetLastError();
 }
 
 // out[M, N] = A[M, K] . W[N, K]^T (+ epilogue) where W is gathered by the kernel itself: rank q's shard (peer
@@ -768,7 +1185,10 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
   if (rc) return rc;
   rc = make_map(&mb, (const char*)full + w_off, K, N, K, 64, BN);
   if (rc) return rc;
-  GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev};
+  CUtensorMap mo, mp;
+  const int tma_store = make_store_maps(&mo, &mp, out, aux_out, M, N, ldc, flags);
+  GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev, tma_store,
+             1, nullptr, 0};
   GatherArgs ga{};
   for (int q = 0; q < n_ranks; ++q) {
     ga.shard[q] = (const char*)shards[q];
@@ -795,13 +1215,16 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
   }
   const int tiles = ((M + BM - 1) / BM) * tiles_n;
   int ctas = tiles < g_sm_count ? tiles : g_sm_count;
-  void* params[] = {(void*)&ma, (void*)&mb, (void*)&g, (void*)&ga};
+  void* params[] = {(void*)&ma, (void*)&mb, (void*)&mo, (void*)&mp, (void*)&g, (void*)&ga};
   tb_note_launch(1);
   return (int)cudaLaunchCooperativeKernel((const void*)kernel, dim3(ctas), dim3(384), params, L::TOTAL, stream);
 }
 
 // Forces a tile shape for every later call (0: 256x256, 1: 128x256, 2: 128x128; -1: automatic).  For tuning.
 void tb_gemm_force_tile(int which) { g_forced_tile = which; }
+
+// 1 (default): bf16 outputs leave through TMA stores; 0: the epilogue warps store them.  For measurements.
+void tb_gemm_tma_store(int on) { g_tma_store_enabled = on; }
 
 const char* tb_gemm_last_error() { return g_map_error; }
 

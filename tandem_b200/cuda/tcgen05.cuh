@@ -53,6 +53,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
   return true;
 }
 
+// The same for a whole warp that has nothing else to do (the epilogue waiting for an accumulator): one lane polls,
+// sleeping between polls, so the warp neither competes for issue slots with the producer and MMA threads nor
+// keeps the barrier's shared-memory word busy; the others wait at the warp barrier.  Returns the result to all lanes.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* error) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0 && !mbar_try_wait(bar, parity)) {
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+      __nanosleep(128);
+      if (clock64() - start > (1ll << WAIT_LIMIT_CYCLES_SHIFT)) {
+        *error = 1;
+        __threadfence_system();
+        ok = false;
+        break;
+      }
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
                    smem_u32(dst)),
@@ -123,5 +143,71 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool a_mn, bool 
          ((uint32_t)(m >> 4) << 24);
 }
 
+
+// ------------------------------------------------------------------ CTA pairs (cta_group::2)
+// Two CTAs of a cluster on neighbouring SMs run one 256-row MMA together: each holds 128 rows of A, half of
+// the B tile and 128 rows of the accumulator; the leader (cluster rank 0) issues the instructions.
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// The shared::cluster address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// Tile load into this CTA's shared memory whose bytes are counted on an mbarrier of the pair's leader
+// (`bar_cluster_addr` from map_to_cta).  Each CTA reads its own tile from global memory.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                   smem_u32(dst)),
+               "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+               : "memory");
+}
+
+// Issued by the same warp of both CTAs of the pair.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// One arrival on the mbarrier at this shared-memory offset in every CTA of `cta_mask`, once all MMAs issued so
+// far by this thread have completed.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "h"(cta_mask)
+               : "memory");
+}
 
 }  // namespace tc

@@ -37,10 +37,20 @@ def gemm(a, b, M, N, K, lda, ldb, a_mn, b_mn, flags=0, bias=None, aux_in=None, a
         raise ValueError("aux_in must share the output's row stride")
     if out.dtype == torch.float32:
         flags |= OUT_F32
-    rc = lib().tb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), flags,
-                            bias.data_ptr() if bias is not None else None,
-                            aux_in.data_ptr() if aux_in is not None else None,
-                            aux_out.data_ptr() if aux_out is not None else None, 0, stream(a))
+    splits = lib().tb_gemm_splits(M, N, K) if flags in (0, ACCUMULATE) and ldc % 4 == 0 else 1
+    if splits > 1:
+        # few output tiles, long reduction (the weight gradients): the reduction is cut into parts that fill the SMs,
+        # each part leaves an fp32 partial product, and one pass sums them in a fixed order into the bf16 output
+        partials = torch.empty((splits, M, ldc), dtype=torch.float32, device=a.device)
+        rc = lib().tb_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), flags,
+                                       None, None, None, 0, splits, partials.data_ptr(), stream(a))
+        if rc == 0:
+            rc = lib().tb_splitk_reduce(partials.data_ptr(), splits, M, N, ldc, out.data_ptr(), flags, stream(a))
+    else:
+        rc = lib().tb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), flags,
+                                bias.data_ptr() if bias is not None else None,
+                                aux_in.data_ptr() if aux_in is not None else None,
+                                aux_out.data_ptr() if aux_out is not None else None, 0, stream(a))
     if rc in (-11, -12):
         raise RuntimeError(f"gemm: operand not addressable by TMA (M={M} N={N} K={K} lda={lda} ldb={ldb} a_mn={a_mn} b_mn={b_mn} "
                            f"a={a.data_ptr():#x} b={b.data_ptr():#x}): {lib().tb_gemm_last_error().decode()}")

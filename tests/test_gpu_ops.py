@@ -28,11 +28,23 @@ def no_gemm_timeouts():
     assert not gemm_error(), "a GEMM wait ran out"
 
 
+@pytest.fixture
+def force_tile():
+    """Pins the GEMM's tile shape (0: 256x256, 1: 128x256, 2: 128x128, 3/4: CTA-pair 256x256 / 256x128, 5: 128x192) for one test."""
+    from tandem_b200.ops._lib import lib
+
+    yield lib().tb_gemm_force_tile
+    lib().tb_gemm_force_tile(-1)
+
+
+@pytest.mark.parametrize("tile", [-1, 0, 1, 2, 3, 4, 5])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (256, 384, 768), (1024, 2304, 768), (512, 65, 768),
                                    (384, 768, 3072), (130, 72, 200)])
-def test_gemm_three_layouts(M, N, K):
+def test_gemm_three_layouts(M, N, K, tile, force_tile):
     from tandem_b200.ops._lib import empty_padded
     from tandem_b200.ops.gemm import gemm
+
+    force_tile(tile)
 
     def padded(rows, cols):
         t = empty_padded(rows, cols, torch.bfloat16, "cuda")
@@ -52,8 +64,38 @@ def test_gemm_three_layouts(M, N, K):
     close(out32, at.float().t() @ bt.float(), rtol=2e-3, atol=2e-3)
 
 
-def test_gemm_epilogues():
+@pytest.mark.parametrize("splits", [2, 3, 8])
+@pytest.mark.parametrize("M,N,K", [(768, 768, 8192), (384, 200, 2048), (130, 72, 4096)])
+def test_gemm_split_k(M, N, K, splits):
+    """Weight-gradient shapes: the reduction is cut into parts whose fp32 partial tiles are summed by a second kernel."""
     from tandem_b200.ops import gemm as G
+    from tandem_b200.ops._lib import empty_padded, lib
+
+    at, bt = rnd(K, M, scale=0.5), rnd(K, N, scale=0.5)
+    want = at.float().t() @ bt.float()
+    lib().tb_gemm_force_splits(splits)
+    try:
+        out = G.gemm(at, bt, M, N, K, M, N, True, True) if M % 8 == 0 and N % 8 == 0 else None
+        if out is None:
+            a2, b2 = empty_padded(K, M, torch.bfloat16, "cuda"), empty_padded(K, N, torch.bfloat16, "cuda")
+            a2.copy_(at), b2.copy_(bt)
+            out = G.gemm(a2, b2, M, N, K, a2.stride(0), b2.stride(0), True, True)
+        close(out, want)
+        acc = torch.ones_like(out)
+        G.gemm(at if M % 8 == 0 and N % 8 == 0 else a2, bt if M % 8 == 0 and N % 8 == 0 else b2, M, N, K,
+               M if M % 8 == 0 and N % 8 == 0 else a2.stride(0), N if M % 8 == 0 and N % 8 == 0 else b2.stride(0), True, True,
+               G.ACCUMULATE, out=acc)
+        close(acc, want + 1)
+    finally:
+        lib().tb_gemm_force_splits(0)
+    assert lib().tb_gemm_splits(768, 768, 8192) > 1 and lib().tb_gemm_splits(8192, 3072, 768) == 1 and lib().tb_gemm_splits(3072, 768, 8192) == 1
+
+
+@pytest.mark.parametrize("tile", [-1, 1, 3, 5])
+def test_gemm_epilogues(tile, force_tile):
+    from tandem_b200.ops import gemm as G
+
+    force_tile(tile)
 
     M, N, K = 256, 512, 384
     a, w, bias, res = rnd(M, K, scale=0.5), rnd(N, K, scale=0.5), rnd(N), rnd(M, N)
@@ -70,6 +112,9 @@ def test_gemm_epilogues():
     acc = torch.ones(M, N, dtype=torch.float32, device="cuda")
     G.gemm(a, w, M, N, K, K, K, False, False, G.ACCUMULATE, out=acc)
     close(acc, a.float() @ w.float().t() + 1, rtol=2e-3, atol=2e-3)
+    acc16 = torch.ones(M, N, dtype=torch.bfloat16, device="cuda")
+    G.gemm(a, w, M, N, K, K, K, False, False, G.ACCUMULATE, out=acc16)
+    close(acc16, a.float() @ w.float().t() + 1)
 
 
 @pytest.mark.parametrize("N", [768, 65])
