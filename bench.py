@@ -37,8 +37,23 @@ import torch
 
 MODEL = dict(vocab=65, seq=512, layers=12, heads=12, dim=768)
 GLOBAL_BATCH = 16
+MODEL_LABEL, MODEL_DESC = "85.8M", "gpt-85.8M (L12 d768 h12 mlp3072 vocab65)"
 LR, WD = 3e-4, 0.1
 PUBLISHED_TOKENS_PER_S = 10265.0  # the reference's own "tandem DDP" row: 2x T4, fp32 (its README / bench/t4 results)
+MICRO_BATCHES = 16  # pipeline strategies
+
+# The other training configurations of the benchmark plan (--model); the flagship above is the default.
+OTHER_MODELS = {
+    "1.3b": (dict(vocab=50304, seq=2048, layers=24, heads=16, dim=2048), 64, "1.3B", "gpt-1.3B (L24 d2048 h16 mlp8192 vocab50304)"),
+    "pp24": (dict(vocab=50304, seq=1024, layers=24, heads=16, dim=1024), 64, "pp24L", "gpt-24L (L24 d1024 h16 mlp4096 vocab50304), 16 micro-batches of 4"),
+}
+
+
+def select_model(name):
+    global MODEL, GLOBAL_BATCH, MODEL_LABEL, MODEL_DESC, PUBLISHED_TOKENS_PER_S
+    if name in OTHER_MODELS:
+        MODEL, GLOBAL_BATCH, MODEL_LABEL, MODEL_DESC = OTHER_MODELS[name]
+        PUBLISHED_TOKENS_PER_S = None  # the reference publishes nothing for this configuration
 
 
 # ---------------------------------------------------------------------------------------------- clocks
@@ -152,11 +167,11 @@ def result_line(args, impl, strategy, dev_ms, e2e_ms, h2d, d2h, launches, clocks
     tokens = GLOBAL_BATCH * MODEL["seq"]
     value = tokens / (dev_ms / 1e3)
     row = {
-        "metric": f"gpt_85.8M_{strategy}_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "metric": f"gpt_{MODEL_LABEL}_{strategy}_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": value / PUBLISHED_TOKENS_PER_S, "dtype": dtype, "data": "synthetic uniform-random token ids, random-init weights",
+        "vs_baseline": value / PUBLISHED_TOKENS_PER_S if PUBLISHED_TOKENS_PER_S else None, "dtype": dtype, "data": "synthetic uniform-random token ids, random-init weights",
         "impl": impl,
-        "config": {"model": "gpt-85.8M (L12 d768 h12 mlp3072 vocab65)", "global_batch": GLOBAL_BATCH, "seq_len": MODEL["seq"],
+        "config": {"model": MODEL_DESC, "global_batch": GLOBAL_BATCH, "seq_len": MODEL["seq"],
                    "parallelism": f"{strategy}{args.gpus}", "optimizer": "AdamW lr 3e-4 wd 0.1",
                    "l2": "no explicit flush: each step streams parameters, gradients, optimizer state and activations "
                          "(>1.3 GB) through the 126 MB L2", "timing": "CUDA events on the training stream, max over ranks"},
@@ -210,17 +225,28 @@ def run_ours(args):
     elif args.strategy == "zero3":
         wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD), fuse_gather_gemm=bool(args.fuse))
         finish = lambda: (wrapped.step(), wrapped.zero_grad())
+    elif args.strategy in ("gpipe", "1f1b"):
+        from tandem_b200.pipeline import Pipeline
+
+        wrapped = Pipeline(model, g, MICRO_BATCHES, args.strategy)  # one stage per GPU; stage traffic on NCCL p2p
+        opt = torch.optim.AdamW(wrapped.parameters(), lr=LR, weight_decay=WD, fused=True)
     else:
         raise SystemExit(f"unknown strategy {args.strategy}")
+    pipelined = args.strategy in ("gpipe", "1f1b")
 
     def step_fn(x, y):
+        if pipelined:
+            loss = wrapped.train_step(x, y)
+            opt.step()
+            opt.zero_grad()
+            return loss if loss is not None else torch.zeros((), device=dev)
         with torch.autocast("cuda", dtype=torch.bfloat16, enabled=not pure_bf16):
             loss = wrapped(x, y)
         loss.backward()
         finish()
         return loss
 
-    per_rank = GLOBAL_BATCH // world
+    per_rank = GLOBAL_BATCH if pipelined else GLOBAL_BATCH // world
     graphed = args.graph and args.strategy == "ddp"
     if graphed:
         from tandem_b200.parallel.graph import GraphedStep
@@ -236,7 +262,8 @@ def run_ours(args):
         g.all_reduce(gathered)  # CPU tensor: host control plane
         return float(gathered.max())
 
-    batches = token_batches(8, per_rank, rank, world, MODEL["vocab"], MODEL["seq"])
+    # a pipeline feeds the whole batch to every stage (the first uses the tokens, the last the targets)
+    batches = token_batches(8, per_rank, 0 if pipelined else rank, 1 if pipelined else world, MODEL["vocab"], MODEL["seq"])
     sampler = ClockSampler(dev.index)
     if rank == 0:
         sampler.start()
@@ -275,8 +302,18 @@ def run_torch(args):
         dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(0)
     model = GPT(Config(**MODEL)).to(dev)
-    wrapped = DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
-    opt = torch.optim.AdamW(model.parameters(), lr=LR, weight_decay=WD, fused=True)
+    if args.strategy == "zero3" and world > 1:
+        from torch.distributed.fsdp import FullyShardedDataParallel, MixedPrecision
+        from torch.distributed.fsdp.wrap import ModuleWrapPolicy
+
+        from tandem_b200.models.gpt import Block
+
+        bf16 = torch.bfloat16
+        wrapped = FullyShardedDataParallel(model, auto_wrap_policy=ModuleWrapPolicy({Block}), device_id=dev, use_orig_params=True,
+                                           mixed_precision=MixedPrecision(param_dtype=bf16, reduce_dtype=bf16, buffer_dtype=bf16))
+    else:
+        wrapped = DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    opt = torch.optim.AdamW(wrapped.parameters(), lr=LR, weight_decay=WD, fused=True)
 
     def step_fn(x, y):
         with torch.autocast("cuda", dtype=torch.bfloat16):
@@ -304,7 +341,8 @@ def run_torch(args):
     dev_ms, e2e_ms, h2d, d2h, _, last = timed_loops(step_fn, batches, args.steps, args.warmup, dev, barrier, reduce_max)
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
-        print(json.dumps(result_line(args, "torch", "ddp", dev_ms, e2e_ms, h2d, d2h, 0, clocks, "bf16", {"final_loss": last})),
+        print(json.dumps(result_line(args, "torch", "fsdp" if args.strategy == "zero3" else "ddp", dev_ms, e2e_ms, h2d, d2h, 0, clocks,
+                                     "bf16", {"final_loss": last})),
               flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -390,13 +428,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
-    ap.add_argument("--strategy", default="ddp", choices=["ddp", "zero1", "zero2", "zero3"])
+    ap.add_argument("--strategy", default="ddp", choices=["ddp", "zero1", "zero2", "zero3", "gpipe", "1f1b"])
+    ap.add_argument("--model", default="85.8m", choices=["85.8m", "1.3b", "pp24"],
+                    help="85.8m: the flagship; 1.3b: the ZeRO-3 configuration; pp24: the 24-layer pipeline configuration")
     ap.add_argument("--kernels", default=os.environ.get("TANDEM_BENCH_KERNELS", "b200"), choices=["torch", "b200"])
     ap.add_argument("--ref-backend", default="python", choices=["python", "cpp"])
     ap.add_argument("--fuse", type=int, default=1, help="zero3: gather each block's qkv weight inside its GEMM kernel")
     ap.add_argument("--graph", type=int, default=1, help="replay the ddp step as a CUDA graph (ours, ddp only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    select_model(args.model)
     if args.impl == "reference":
         run_reference(args)
     elif args.impl == "torch":

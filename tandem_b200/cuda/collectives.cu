@@ -480,6 +480,31 @@ k_allreduce_nvls(CommCtx c, char* mc, long long nvec, int smode, float sval) {
   comm_barrier(c, sh);
 }
 
+// NVLS all-gather: each rank streams ITS chunk of the buffer to the multicast address, and the switch
+// writes it into every rank's copy (its own included).  A rank sends len bytes once instead of
+// serving n - 1 peers' loads.  off and len are multiples of 16.
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
+k_allgather_nvls(CommCtx c, const char* local, char* mc, long long off, long long len) {
+  __shared__ int sh[2];
+  if (threadIdx.x == 0) sh[1] = 0;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  comm_barrier(c, sh);  // every rank's buffer may be written from here on
+  if (!sh[1]) {
+    const long long nvec = len / 16;
+    for (long long v = tid; v < nvec; v += nth * 4) {
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v + u * nth < nvec) x[u] = ld_vec(local + off + (v + u * nth) * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v + u * nth < nvec) multimem_st(mc + off + (v + u * nth) * 16, x[u]);
+    }
+  }
+  comm_barrier(c, sh);
+}
+
 // A barrier and nothing else (one block per rank).
 __global__ void k_barrier(CommCtx c) {
   __shared__ int sh[2];
@@ -730,6 +755,14 @@ int tb_all_reduce_nvls(TbComm* c, void* mc, long long numel, int dtype, int aver
   int blocks = blocks_for(c, bytes / c->ctx.n, (long long)TB_COMM_THREADS * 16 * 4);
   if (dtype == TB_F32) return (int)launch(c, k_allreduce_nvls<float>, blocks, stream, c->ctx, (char*)mc, bytes / 16, smode, sval);
   return (int)launch(c, k_allreduce_nvls<__nv_bfloat16>, blocks, stream, c->ctx, (char*)mc, bytes / 16, smode, sval);
+}
+
+// In-switch all-gather, in place: rank r's chunk is bytes [off, off + len) of the buffer whose local address is
+// `local` and whose multicast address is `mc`; grid_bytes (the largest chunk) fixes the grid on every rank.
+int tb_all_gather_nvls(TbComm* c, const void* local, void* mc, long long off, long long len, long long grid_bytes, cudaStream_t stream) {
+  if (c->emulated || (off & 15) || (len & 15) || (((uintptr_t)mc | (uintptr_t)local) & 15)) return -4;
+  int blocks = blocks_for(c, grid_bytes, (long long)TB_COMM_THREADS * 16 * 4);
+  return (int)launch(c, k_allgather_nvls, blocks, stream, c->ctx, (const char*)local, (char*)mc, off, len);
 }
 
 // Folds chunk r = [offs[r], offs[r+1]) of every rank's buffer into rank r's buffer.

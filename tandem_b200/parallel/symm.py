@@ -80,6 +80,7 @@ def cuda_lib():
         "tb_barrier": ([vp, vp], i),
         "tb_all_reduce": ([vp, pp, pp, pp, ll, i, i, i, i, vp], i),
         "tb_all_reduce_nvls": ([vp, vp, ll, i, i, vp], i),
+        "tb_all_gather_nvls": ([vp, vp, vp, ll, ll, ll, vp], i),
         "tb_reduce_scatter": ([vp, pp, pp, ll, pll, i, i, i, pp, ctypes.POINTER(AdamArgs), vp], i),
         "tb_gather_pull": ([vp, pp, pp, pll, pll, pll, pp, i, ll, vp], i),
         "tb_adamw": ([vp, vp, i, vp, vp, vp, ll, ctypes.POINTER(f), i, f, vp], i),
@@ -488,7 +489,13 @@ class SymmetricComm:
         lens = [offs[q + 1] - offs[q] for q in range(self.n)]
         peers = self._peers_of(flat)
         if flat.numel() and self.n > 1:
-            if peers is not None:
+            mc = self._multicast_of(flat) if peers is not None else 0
+            want_nvls = self.algo == ALGO["nvls"] or (self.algo == ALGO["auto"] and self.n >= self.nvls_min_ranks and max(lens) >= self.nvls_min_bytes)
+            if mc and want_nvls and mc % 16 == 0 and flat.data_ptr() % 16 == 0 and all(o % 16 == 0 for o in offs):
+                # each rank multicasts its own chunk through the switch (multimem.st)
+                check_rc(self.lib.tb_all_gather_nvls(self._launch_comm, flat.data_ptr(), mc, offs[self.rank], lens[self.rank], max(lens),
+                                                     self._launch_stream.cuda_stream), "all_gather (NVLS)")
+            elif peers is not None:
                 self._pull(peers, flat.data_ptr(), offs[:-1], offs[:-1], lens, None, True)
             else:
                 step = self.scratch_half

@@ -330,6 +330,21 @@ def nvls_rank(rank, world, init, out):
                 g.all_reduce(x, op="avg")  # large enough to pick the NVLS kernel by itself
                 ok = ok and torch.allclose(x.double().cpu(), want / world, rtol=1e-2, atol=1e-2)
                 g.release(x)
+        # all-gather through the switch: each rank multicasts its own chunk (multimem.st)
+        from tandem_b200.parallel.symm import ALGO
+
+        auto, g._sym.algo = g._sym.algo, ALGO["nvls"]
+        for dtype in (torch.float32, torch.bfloat16):
+            n = 1 << 20
+            full = data(7, n, dtype)
+            x = g.empty(n, dtype)
+            x.fill_(-7)
+            lo, hi = n * rank // world, n * (rank + 1) // world
+            x[lo:hi].copy_(full[lo:hi])
+            g.all_gather(x)
+            ok = ok and torch.equal(x.cpu(), full)
+            g.release(x)
+        g._sym.algo = auto
         g.check()
         result["ok"] = ok
     g.close()
@@ -338,7 +353,7 @@ def nvls_rank(rank, world, init, out):
 
 
 @needs2
-def test_nvls_multimem_all_reduce():
+def test_nvls_multimem_all_reduce_and_all_gather():
     import torch.multiprocessing as mp
     import uuid
 
