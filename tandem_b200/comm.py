@@ -140,11 +140,28 @@ class Group:
         if self.device.type == "cuda":
             if self.device.index is None:
                 self.device = torch.device("cuda", torch.cuda.current_device())
+            if self.transport == "device" and self._ranks_share_a_gpu():
+                # Collective kernels of different ranks wait on one another; as separate processes on ONE GPU
+                # nothing guarantees that they run at the same time.  Such groups (the reference's
+                # launch(gpus=[0, 0])) stage through the host engine instead.
+                self.transport = "host"
             if self.transport == "device":
                 from .parallel.symm import SymmetricComm
 
                 self._sym = SymmetricComm(self)
         self.barrier()
+
+    def _ranks_share_a_gpu(self):
+        if self.size == 1:
+            return False
+        ids = torch.zeros(self.size, dtype=torch.int64)
+        import hashlib
+
+        props = torch.cuda.get_device_properties(self.device)
+        name = f"{getattr(props, 'uuid', '')}/{getattr(props, 'pci_bus_id', self.device.index)}/{self.device.index}"
+        ids[self.rank] = int(hashlib.sha1(name.encode()).hexdigest()[:15], 16)
+        self._engine.all_gather(ids.data_ptr(), ids.numel(), 4, [1] * self.size).wait()
+        return len(set(ids.tolist())) < self.size
 
     # ------------------------------------------------------------------ construction helpers
     @staticmethod

@@ -307,6 +307,22 @@ def test_fsdp_with_qkv_weight_gathered_inside_the_gemm():
         assert torch.equal(fused[r][1], plain[r][1]), (fused[r][1] - plain[r][1]).abs().max()
 
 
+def shared_gpu_rank(g):
+    x = torch.full((1000,), float(g.rank + 1), device=g.device)
+    g.all_reduce(x)
+    y = torch.arange(8, device=g.device, dtype=torch.float32) * (g.rank + 1)
+    g.broadcast(y, root=1)
+    return g.transport, g.fused, float(x[0]), float(y[7])
+
+
+def test_ranks_sharing_one_gpu_stage_through_the_host():
+    """Two ranks on GPU 0 (the reference's one-GPU engine benchmark layout): their collective kernels would wait on
+    one another as separate launches on one GPU, so the group must fall back to host staging by itself."""
+    from tandem_b200 import launch
+
+    assert launch(shared_gpu_rank, 2, device="cuda", gpus=[0, 0]) == [("host", False, 3.0, 14.0)] * 2
+
+
 def nvls_rank(rank, world, init, out):
     """All-reduce through the NVSwitch multicast mapping (multimem.ld_reduce / multimem.st)."""
     import torch.distributed as dist
