@@ -34,6 +34,8 @@ extern "C" void tb_note_launch(int n);
 
 namespace {
 
+int g_bwd_two_per_sm = 0;
+
 using namespace tc;
 
 constexpr int TILE = 128;           // queries per CTA, keys per step
@@ -82,17 +84,28 @@ __device__ __forceinline__ void mma_kmajor(uint32_t d_tmem, const uint8_t* a, co
 template <int HD>
 struct FwdSmem {
   static constexpr int TILE_BYTES = (HD / 64) * STRIP;
-  static constexpr int Q = 0, KV = Q + TILE_BYTES /* [2 buffers][K, V] */, P = KV + 4 * TILE_BYTES, STATS = P + 2 * STRIP,
-                       BARS = STATS + 2 * TILE * 4;
-  static constexpr int TOTAL = BARS + 64 + 1024;
+  // STATS (the two column halves' row maxima / sums, 1 KB) shares P's bytes: it is written at the end of pass 0 and
+  // after the last step, read at the start of pass 1 and at the very end, never while P is live.  With HD = 64 the
+  // total stays under 113 KB, so that two CTAs fit one SM (each also holds 256 TMEM columns): one computes its
+  // softmax while the other's MMAs run.  The buffer is declared 1024-byte aligned instead of being rounded up.
+  static constexpr int Q = 0, KV = Q + TILE_BYTES /* [2 buffers][K, V] */, P = KV + 4 * TILE_BYTES, STATS = P,
+                       BARS = P + 2 * STRIP;
+  static constexpr int TOTAL = BARS + 64;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, HD == 64 ? 2 : 1)
 k_attn_fwd(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int T, int H, int d,
            float scale_log2e, int* error) {
-  extern __shared__ uint8_t raw_smem[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t fwd_smem[];
+  uint8_t* smem = fwd_smem;
+  if (smem_u32(smem) & 1023) {  // the swizzled tiles need 1024-byte alignment; nothing is allocated yet
+    if (threadIdx.x == 0) {
+      *error = 1;
+      __threadfence_system();
+    }
+    return;
+  }
   using L = FwdSmem<HD>;
   constexpr int TILE_BYTES = L::TILE_BYTES;
   uint8_t *sQ = smem + L::Q, *sKV = smem + L::KV, *sP = smem + L::P;
@@ -156,6 +169,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict__ 
     tc_fence_after();
     if (it == qt + 1) {  // first step of pass 1: combine the two halves' row maxima
       m2 = fmaxf(stats[r], stats[TILE + r]);
+      __syncthreads();  // everyone has read the maxima before P (the same bytes) is written
     }
     const bool diagonal = j == qt;
 #pragma unroll 1
@@ -447,6 +461,210 @@ k_attn_bwd(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ 
   }
 }
 
+
+// Backward for HD = 64 shaped so that TWO CTAs share an SM (256 TMEM columns and under 113 KB of shared memory
+// each): while one CTA computes its exponentials the other's MMAs run.  S and dP take turns in the same 128 TMEM
+// columns (P stays packed in registers between them), dQ follows in the first 64 of those; P and dS take turns in
+// one shared-memory buffer; Q and dO are single-buffered.  Per query tile:
+//   S = Q.K^T                     -> P = exp(S*scale - lse) to registers (bf16 pairs) and shared memory
+//   dV += P^T.dO ;  dP = dO.V^T   -> dS = P * (dP - D) * scale over P's bytes in shared memory
+//   dK += dS^T.Q ;  dQ = dS.K     -> fp32 atomic adds into the dQ scratch
+// TMEM: [0,128) S / dP / dQ;  [128,192) dV;  [192,256) dK.
+struct Bwd64Smem {
+  static constexpr int K = 0, V = K + STRIP, Q = V + STRIP, DO = Q + STRIP, PS = DO + STRIP, BARS = PS + 2 * STRIP;
+  static constexpr int TOTAL = BARS + 64;
+};
+
+__global__ void __launch_bounds__(256, 2)
+k_attn_bwd64(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const float* __restrict__ lse,
+             const float* __restrict__ delta, float* __restrict__ dq32, __nv_bfloat16* __restrict__ dqkv, int T, int H, int d, float scale,
+             int* error) {
+  constexpr int HD = 64;
+  extern __shared__ __align__(1024) uint8_t bwd_smem[];
+  uint8_t* smem = bwd_smem;
+  if (smem_u32(smem) & 1023) {  // the swizzled tiles need 1024-byte alignment; nothing is allocated yet
+    if (threadIdx.x == 0) {
+      *error = 1;
+      __threadfence_system();
+    }
+    return;
+  }
+  using L = Bwd64Smem;
+  uint8_t *sK = smem + L::K, *sV = smem + L::V, *sQ = smem + L::Q, *sDO = smem + L::DO, *sPS = smem + L::PS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);  // 0: K/V, 1: Q/dO, 2: MMA
+  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 4);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int r = tid & 127, half = tid >> 7;
+  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int n_tiles = T / TILE;
+  constexpr uint32_t TMEM_COLS = 256;
+
+  if (tid == 0) {
+    for (int i = 0; i < 3; ++i) mbar_init(&bars[i], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    tmem_alloc(holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *holder;
+  const uint32_t tSP = tmem, tDQ = tmem, tDV = tmem + 128, tDK = tmem + 192;
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  Waiter wkv{&bars[0], 0, error}, wq{&bars[1], 0, error}, mm{&bars[2], 0, error};
+  constexpr uint32_t idesc_s = instr_desc(128, 128, false, false);
+  constexpr uint32_t idesc_kv = instr_desc(128, HD, true, true);
+  constexpr uint32_t idesc_dq = instr_desc(128, HD, false, true);
+
+  auto issue_q = [&](int i) {  // thread 0 only
+    mbar_expect_tx(&bars[1], 2 * STRIP);
+    load_tile<HD>(sQ, &map_qkv, &bars[1], h * HD, b * T + i * TILE);
+    load_tile<HD>(sDO, &map_do, &bars[1], h * HD, b * T + i * TILE);
+  };
+
+  if (tid == 0) {
+    mbar_expect_tx(&bars[0], 2 * STRIP);
+    load_tile<HD>(sK, &map_qkv, &bars[0], d + h * HD, b * T + kt * TILE);
+    load_tile<HD>(sV, &map_qkv, &bars[0], 2 * d + h * HD, b * T + kt * TILE);
+    issue_q(kt);
+  }
+  bool ok = wkv.wait();
+  uint8_t* my_strip = sPS + half * STRIP;
+
+  for (int i = kt; i < n_tiles && ok; ++i) {
+    const int qrow0 = b * T + i * TILE;
+    if (!(ok = wq.wait())) break;
+    tc_fence_after();
+    if (tid == 0) {
+      mma_kmajor<HD>(tSP, sQ, sK, idesc_s, false);  // S[q, k]
+      mma_commit(&bars[2]);
+    }
+    if (!(ok = mm.wait())) break;
+    tc_fence_after();
+    const int q_idx = i * TILE + r;
+    const float row_lse = lse[((size_t)b * H + h) * T + q_idx];
+    const float row_delta = delta[((size_t)b * H + h) * T + q_idx];
+    const bool diagonal = i == kt;
+    uint4 packed[8];  // this thread's 64 probabilities as bf16 pairs
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int col0 = half * 64 + c * 32;
+      uint32_t rs[32];
+      tmem_ld32(tSP + lane_base + col0, rs);
+      tmem_ld_wait();
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed[c * 4 + v]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float pv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = col0 + v * 8 + 2 * e + u;
+            float p = __expf(__uint_as_float(rs[v * 8 + 2 * e + u]) * scale - row_lse);
+            if (diagonal && kt * TILE + col > q_idx) p = 0.f;
+            pv[u] = p;
+          }
+          p2[e] = __floats2bfloat162_rn(pv[0], pv[1]);
+        }
+        *reinterpret_cast<uint4*>(my_strip + swz(r, c * 4 + v)) = packed[c * 4 + v];
+      }
+    }
+    tc_fence_before();
+    fence_async_smem();
+    __syncthreads();  // S has been read everywhere (dP may overwrite it) and P is complete
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)  // dV += P^T.dO: P and dO MN-major over the queries
+        mma_bf16(tDV, smem_desc(smem_u32(sPS) + kk * 2048, STRIP, 1024), smem_desc(smem_u32(sDO) + kk * 2048, STRIP, 1024), idesc_kv,
+                 (i > kt || kk > 0) ? 1u : 0u);
+      mma_kmajor<HD>(tSP, sDO, sV, idesc_s, false);  // dP[q, k]
+      mma_commit(&bars[2]);
+    }
+    if (!(ok = mm.wait())) break;  // P's bytes may be overwritten: the dV MMAs have read them
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int col0 = half * 64 + c * 32;
+      uint32_t rp[32];
+      tmem_ld32(tSP + lane_base + col0, rp);
+      tmem_ld_wait();
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&packed[c * 4 + v]);
+        __nv_bfloat162 s2[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 p = __bfloat1622float2(p2[e]);
+          s2[e] = __floats2bfloat162_rn(p.x * (__uint_as_float(rp[v * 8 + 2 * e]) - row_delta) * scale,
+                                        p.y * (__uint_as_float(rp[v * 8 + 2 * e + 1]) - row_delta) * scale);
+        }
+        *reinterpret_cast<uint4*>(my_strip + swz(r, c * 4 + v)) = *reinterpret_cast<const uint4*>(s2);
+      }
+    }
+    tc_fence_before();
+    fence_async_smem();
+    __syncthreads();  // dP has been read everywhere (dQ may overwrite it) and dS is complete
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)  // dK += dS^T.Q
+        mma_bf16(tDK, smem_desc(smem_u32(sPS) + kk * 2048, STRIP, 1024), smem_desc(smem_u32(sQ) + kk * 2048, STRIP, 1024), idesc_kv,
+                 (i > kt || kk > 0) ? 1u : 0u);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)  // dQ = dS.K: dS K-major over the keys, K MN-major over the keys
+        mma_bf16(tDQ, smem_desc(smem_u32(sPS + (kk >> 2) * STRIP) + (kk & 3) * 32, 16, 1024), smem_desc(smem_u32(sK) + kk * 2048, STRIP, 1024),
+                 idesc_dq, kk > 0 ? 1u : 0u);
+      mma_commit(&bars[2]);
+    }
+    if (!(ok = mm.wait())) break;
+    tc_fence_after();
+    if (tid == 0 && i + 1 < n_tiles) issue_q(i + 1);  // Q and dO are free only now
+    constexpr int COLS = HD / 2;
+    float* dq_row = dq32 + (size_t)(qrow0 + r) * d + h * HD + half * COLS;
+    {
+      uint32_t raw[32];
+      tmem_ld32(tDQ + lane_base + half * COLS, raw);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        atomicAdd(reinterpret_cast<float4*>(dq_row + e * 4),
+                  make_float4(__uint_as_float(raw[4 * e]), __uint_as_float(raw[4 * e + 1]), __uint_as_float(raw[4 * e + 2]),
+                              __uint_as_float(raw[4 * e + 3])));
+    }
+    tc_fence_before();
+    __syncthreads();  // dQ has left TMEM before the next tile's S lands there
+  }
+  if (ok) {
+    constexpr int COLS = HD / 2;
+    __nv_bfloat16* dk = dqkv + (size_t)(b * T + kt * TILE + r) * 3 * d + d + h * HD + half * COLS;
+    __nv_bfloat16* dv = dk + d;
+#pragma unroll 1
+    for (int part = 0; part < 2; ++part) {
+      __nv_bfloat16* dst = part == 0 ? dv : dk;
+      uint32_t raw[32];
+      tmem_ld32((part == 0 ? tDV : tDK) + half * COLS + lane_base, raw);
+      tmem_ld_wait();
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        __nv_bfloat162 y[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = __floats2bfloat162_rn(__uint_as_float(raw[v * 8 + 2 * e]), __uint_as_float(raw[v * 8 + 2 * e + 1]));
+        *reinterpret_cast<uint4*>(dst + v * 8) = *reinterpret_cast<const uint4*>(y);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
 // dqkv[row, 0:d] = bf16(dq32[row, :])
 __global__ void __launch_bounds__(256) k_attn_dq_out(const float* __restrict__ dq32, __nv_bfloat16* __restrict__ dqkv, long long rows, int d) {
   const long long n8 = rows * (d / 8);
@@ -516,7 +734,11 @@ int tb_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int
   tb_note_launch(1);
   if (HD == 64) {
     static bool once = false;
-    if (!once) { cudaFuncSetAttribute(k_attn_fwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL); once = true; }
+    if (!once) {
+      cudaFuncSetAttribute(k_attn_fwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL);
+      cudaFuncSetAttribute(k_attn_fwd<64>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);  // two CTAs per SM
+      once = true;
+    }
     k_attn_fwd<64><<<grid, 256, FwdSmem<64>::TOTAL, stream>>>(map, (__nv_bfloat16*)out, lse, T, H, d, scale_log2e, g_err_dev);
   } else {
     static bool once = false;
@@ -525,6 +747,9 @@ int tb_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int
   }
   return (int)cudaGetLastError();
 }
+
+// 1: the HD = 64 backward runs as k_attn_bwd64 (two CTAs per SM); 0: as k_attn_bwd<64>.  For measurements.
+void tb_attn_bwd_variant(int two_per_sm) { g_bwd_two_per_sm = two_per_sm; }
 
 // dqkv[B*T, 3d] from qkv, out, d_out, lse.  delta: fp32 [B*H*T] scratch; dq32: fp32 [B*T*d] scratch (zeroed here).
 int tb_attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, void* dqkv, float* delta, float* dq32, int B, int T,
@@ -543,7 +768,15 @@ int tb_attn_bwd(const void* qkv, const void* out, const void* d_out, const float
   cudaMemsetAsync(dq32, 0, sizeof(float) * rows * d, stream);
   k_attn_delta<<<(unsigned)((rows * H + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, delta, T, H, HD, rows);
   dim3 grid(T / TILE, H, B);
-  if (HD == 64) {
+  if (HD == 64 && g_bwd_two_per_sm) {
+    static bool once = false;
+    if (!once) {
+      cudaFuncSetAttribute(k_attn_bwd64, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::TOTAL);
+      cudaFuncSetAttribute(k_attn_bwd64, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      once = true;
+    }
+    k_attn_bwd64<<<grid, 256, Bwd64Smem::TOTAL, stream>>>(map_qkv, map_do, lse, delta, dq32, (__nv_bfloat16*)dqkv, T, H, d, scale, g_err_dev);
+  } else if (HD == 64) {
     static bool once = false;
     if (!once) { cudaFuncSetAttribute(k_attn_bwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::TOTAL); once = true; }
     k_attn_bwd<64><<<grid, 256, BwdSmem<64>::TOTAL, stream>>>(map_qkv, map_do, lse, delta, dq32, (__nv_bfloat16*)dqkv, T, H, d, scale, g_err_dev);

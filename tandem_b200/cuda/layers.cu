@@ -99,11 +99,14 @@ k_ln_fwd(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ 
 
 // dx for each row, and per-block partial sums of dw = sum dy*xhat and db = sum dy into
 // part[blockIdx.x][2][D] (fp32).  A second kernel adds the partials in a fixed order.
+// add (optional): a second gradient of the same input, summed into dx in fp32 before the one rounding
+// -- the residual branch's gradient in a pre-LayerNorm block, which autograd would otherwise add with a
+// separate pass over the activations.
 template <int MAXV>
 __global__ void __launch_bounds__(256, MAXV <= 4 ? 2 : 1)  // two blocks per SM where the row fits: a capture showed 171 registers and 12 % occupancy
 k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-         const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
-         float* __restrict__ part, int M, int D) {
+         const float* __restrict__ mean_in, const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ add,
+         __nv_bfloat16* __restrict__ dx, float* __restrict__ part, int M, int D) {
   extern __shared__ float sh[];  // [warps][2][D]
   const int warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,6 +148,12 @@ k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__
         float o[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = rstd * (g[j][e] - s1 - xh[j][e] * s2);
+        if (add != nullptr) {
+          float a[8];
+          load8(add + (size_t)row * D + vi * 8, a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += a[e];
+        }
         store8(dx + (size_t)row * D + vi * 8, o);
       }
     }
@@ -339,8 +348,17 @@ int tb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float
 // scratch: fp32 [blocks * 2 * D] with blocks = tb_layernorm_bwd_blocks(M).
 int tb_layernorm_bwd_blocks(int M) { return grid_for(M, 8 * 4, 592); }
 
+int tb_layernorm_bwd_add(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, const void* add, void* dx,
+                         void* dw, void* db, float* scratch, int M, int D, cudaStream_t s);
+
 int tb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx, void* dw,
                      void* db, float* scratch, int M, int D, cudaStream_t s) {
+  return tb_layernorm_bwd_add(dy, x, w, mean, rstd, nullptr, dx, dw, db, scratch, M, D, s);
+}
+
+// The same with `add` ([M, D] bf16, may be null; may alias dx) summed into dx.
+int tb_layernorm_bwd_add(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, const void* add, void* dx,
+                         void* dw, void* db, float* scratch, int M, int D, cudaStream_t s) {
   if (D % 8 || D > 32 * 8 * 8) return -20;
   const int blocks = tb_layernorm_bwd_blocks(M);
   const size_t smem = (size_t)8 * 2 * D * sizeof(float);
@@ -349,7 +367,7 @@ int tb_layernorm_bwd(const void* dy, const void* x, const void* w, const float* 
   do {                                                                                                                 \
     if (smem > 48 * 1024) cudaFuncSetAttribute(k_ln_bwd<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
     k_ln_bwd<V><<<blocks, 256, smem, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,  \
-                                          mean, rstd, (__nv_bfloat16*)dx, scratch, M, D);                              \
+                                          mean, rstd, (const __nv_bfloat16*)add, (__nv_bfloat16*)dx, scratch, M, D);   \
   } while (0)
   if (D <= 256 * 1) LN(1);
   else if (D <= 256 * 2) LN(2);

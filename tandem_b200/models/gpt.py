@@ -14,6 +14,7 @@ Two compute paths share those parameters:
 """
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -42,6 +43,11 @@ class Config:
             "1.3b": dict(vocab=50304, seq=2048, layers=24, heads=16, dim=2048),  # 1.42B (untied head)
         }
         return Config(**presets[name])
+
+
+# Pre-LayerNorm blocks sum the residual branch's gradient inside the LayerNorm backward kernel (TANDEM_RESIDUAL_LN=0:
+# leave that addition to autograd).
+RESIDUAL_LN = os.environ.get("TANDEM_RESIDUAL_LN", "0") != "0"
 
 
 def _b200():
@@ -84,9 +90,15 @@ class Block(nn.Module):
     def forward(self, x):
         if self.kernels == "b200" and x.is_cuda:
             ops = _b200()
-            x = self.attn(ops.layer_norm(x, self.ln1.weight, self.ln1.bias, self.ln1.eps), residual=x)
-            return ops.mlp(ops.layer_norm(x, self.ln2.weight, self.ln2.bias, self.ln2.eps), self.fc.weight, self.fc.bias,
-                           self.out.weight, self.out.bias, residual=x)
+            if not RESIDUAL_LN:
+                x = self.attn(ops.layer_norm(x, self.ln1.weight, self.ln1.bias, self.ln1.eps), residual=x)
+                return ops.mlp(ops.layer_norm(x, self.ln2.weight, self.ln2.bias, self.ln2.eps), self.fc.weight, self.fc.bias,
+                               self.out.weight, self.out.bias, residual=x)
+            # residual_layer_norm hands x through, so both gradients of x meet in the LayerNorm backward kernel
+            x, n = ops.residual_layer_norm(x, self.ln1.weight, self.ln1.bias, self.ln1.eps)
+            x = self.attn(n, residual=x)
+            x, n = ops.residual_layer_norm(x, self.ln2.weight, self.ln2.bias, self.ln2.eps)
+            return ops.mlp(n, self.fc.weight, self.fc.bias, self.out.weight, self.out.bias, residual=x)
         x = x + self.attn(self.ln1(x))
         return x + self.out(F.gelu(self.fc(self.ln2(x))))
 

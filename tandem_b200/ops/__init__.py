@@ -47,6 +47,12 @@ def layer_norm(x, weight, bias, eps=1e-5):
     return f(x, weight, bias, eps)
 
 
+def residual_layer_norm(x, weight, bias, eps=1e-5):
+    from .norm import residual_layer_norm as f
+
+    return f(x, weight, bias, eps)
+
+
 def causal_attention(qkv, heads):
     from .attention import causal_attention as f
 

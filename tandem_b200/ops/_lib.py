@@ -27,6 +27,7 @@ def lib():
         "tb_layernorm_fwd": ([vp, vp, vp, vp, vp, vp, i, i, f, vp], i),
         "tb_layernorm_bwd_blocks": ([i], i),
         "tb_layernorm_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp], i),
+        "tb_layernorm_bwd_add": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp], i),
         "tb_col_sum": ([vp, i, i, i, vp, vp, vp], i),
         "tb_xent_fwd": ([vp, vp, vp, vp, vp, i, i, i, vp], i),
         "tb_xent_bwd": ([vp, vp, vp, vp, i, i, i, i, vp], i),

@@ -21,6 +21,8 @@ def _fns():
     L.tb_attn_fwd.restype = i
     L.tb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, vp]
     L.tb_attn_bwd.restype = i
+    L.tb_attn_bwd_variant.argtypes = [i]
+    L.tb_attn_bwd_variant.restype = None
     L.tb_attn_error.argtypes = []
     L.tb_attn_error.restype = i
     return L
@@ -66,3 +68,8 @@ def causal_attention(qkv, heads):
 def attention_error():
     """True once any attention kernel gave up on a wait (results since then are invalid)."""
     return bool(_fns().tb_attn_error())
+
+
+def backward_variant(two_per_sm):
+    """HD = 64 backward: True runs the kernel shaped for two CTAs per SM, False the one-CTA-per-SM kernel."""
+    _fns().tb_attn_bwd_variant(int(bool(two_per_sm)))

@@ -178,6 +178,27 @@ def test_layer_norm_matches_fp32(D):
     close(b.grad, bf.grad)
 
 
+def test_residual_layer_norm_sums_both_gradients():
+    from tandem_b200 import ops
+
+    M, D = 300, 768
+    x = rnd(M, D).requires_grad_()
+    w, b = (1 + rnd(D, scale=0.1)).requires_grad_(), rnd(D, scale=0.1).requires_grad_()
+    xr, n = ops.residual_layer_norm(x, w, b)
+    up, un = rnd(M, D), rnd(M, D)
+    (xr.float() * up.float()).sum().backward(retain_graph=True)  # only the residual branch: the gradient passes through
+    close(x.grad, up)
+    x.grad = None
+    ((xr.float() * up.float()).sum() + (n.float() * un.float()).sum()).backward()
+    xf, wf, bf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    nf = torch.nn.functional.layer_norm(xf, (D,), wf, bf)
+    ((xf * up.float()).sum() + (nf * un.float()).sum()).backward()
+    close(n, nf)
+    close(x.grad, xf.grad)
+    close(w.grad, wf.grad, rtol=3e-2, atol=3e-2)
+    close(b.grad, bf.grad, rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("V", [65, 50304])
 def test_cross_entropy_matches_fp32(V):
     from tandem_b200 import ops
@@ -238,11 +259,13 @@ def test_gpt_on_b200_kernels_tracks_torch_path():
         assert ((g - w).norm() / denom).item() < 6e-2, (name, ((g - w).norm() / denom).item())
 
 
-@pytest.mark.parametrize("B,T,H,hd", [(2, 128, 2, 64), (2, 512, 3, 64), (1, 256, 2, 128)])
-def test_causal_attention_matches_fp32(B, T, H, hd):
+@pytest.mark.parametrize("two_per_sm", [False, True])
+@pytest.mark.parametrize("B,T,H,hd", [(2, 128, 2, 64), (2, 512, 3, 64), (1, 256, 2, 128), (3, 1024, 2, 64)])
+def test_causal_attention_matches_fp32(B, T, H, hd, two_per_sm):
     from tandem_b200 import ops
-    from tandem_b200.ops.attention import attention_error
+    from tandem_b200.ops.attention import attention_error, backward_variant
 
+    backward_variant(two_per_sm)
     d = H * hd
     qkv = rnd(B, T, 3 * d).requires_grad_()
     y = ops.causal_attention(qkv, H)
