@@ -252,20 +252,30 @@ class Group:
         return self.device.type == "cpu" or t.device.type == "cpu"
 
     def _staged(self, name, flat, run, result_of, nbytes, async_op):
-        """GPU tensor through pinned host memory and the CPU runtime (transport="host")."""
+        """GPU tensor through pinned host memory and the CPU runtime (transport="host"): three jobs queued on
+        the progress thread, which runs them in order -- copy to the host, the CPU collective, copy back."""
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
         host = torch.empty(flat.shape, dtype=flat.dtype, pin_memory=True)
+        dev = self.device
 
-        def job():
+        def stage_in():
             ready.synchronize()
-            host.copy_(flat)
-            run(host).wait()
-            flat.copy_(host)
-            torch.cuda.current_stream(self.device).synchronize()
+            with torch.cuda.device(dev):
+                host.copy_(flat)
+                torch.cuda.current_stream(dev).synchronize()
+
+        self.submit(name + ":stage", stage_in, None, 0, True)
+        inner = run(host)  # queued behind stage_in
+
+        def stage_out():
+            inner.wait()  # it ran before this job on the same thread: returns at once, or raises its error
+            with torch.cuda.device(dev):
+                flat.copy_(host)
+                torch.cuda.current_stream(dev).synchronize()
             return result_of()
 
-        return self.submit(name, job, None, nbytes, async_op)
+        return self.submit(name, stage_out, None, nbytes, async_op)
 
     def empty(self, numel, dtype, device=None, zero=True):
         """A flat tensor for communication buffers.  On GPU ranks it comes from

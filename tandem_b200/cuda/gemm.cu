@@ -322,9 +322,10 @@ __device__ __forceinline__ void store_block(uint8_t* stage, const uint4 (&v)[8],
   }
 }
 
-// Before an epilogue warp leaves: its bulk stores have completed.
+// Before an epilogue warp leaves: its bulk stores have read their shared-memory blocks (the writes themselves
+// complete with the grid).
 __device__ __forceinline__ void drain_stores(int lane) {
-  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   __syncwarp();
 }
 
@@ -434,14 +435,17 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
     *n0 = n_idx * BN;
   };
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], BM == 128 ? 8 : 4);  // one arrival per epilogue warp that drains it
+  if (warp == 0) {  // one lane per barrier; warp 1 allocates TMEM meanwhile
+    if (lane < STAGES) {
+      mbar_init(&full[lane], 1);
+      mbar_init(&empty[lane], 1);
+    } else if (lane < STAGES + 2) {
+      mbar_init(&acc_full[lane - STAGES], 1);
+      mbar_init(&acc_empty[lane - STAGES], BM == 128 ? 8 : 4);  // one arrival per epilogue warp that drains it
+    } else if (lane == STAGES + 2) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      if (g.tma_store) prefetch_tensormap(&map_out);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }

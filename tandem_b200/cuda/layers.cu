@@ -200,10 +200,19 @@ k_reduce_partials(const float* __restrict__ part, int parts, int width, __nv_bfl
 }
 
 // ------------------------------------------------------------------------------------ column sums
+// Ticket words for k_col_sum's single-launch mode: all zero between launches.
+__device__ unsigned g_col_sum_tickets[8192];
+
 // part[blockIdx.y][c] = sum of x[r, c] over the block's row slice; 32 columns x 32 row lanes.
+// With `tickets` (one zero word per column group) the kernel also finishes the job: the last row slice of a
+// column group to arrive adds the group's partials -- in slice order, with the same grouping as
+// k_reduce_partials, so the result does not depend on which block came last -- writes out[c] and leaves the
+// ticket at zero for the next launch.
 __global__ void __launch_bounds__(1024)
-k_col_sum(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __restrict__ part) {
+k_col_sum(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __restrict__ part, unsigned* tickets,
+          __nv_bfloat16* __restrict__ out) {
   __shared__ float sh[32][33];
+  __shared__ int is_last;
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + cx;
   const int rows_per = (M + gridDim.y - 1) / gridDim.y;
@@ -218,6 +227,25 @@ k_col_sum(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __re
     for (int k = 0; k < 32; ++k) t += sh[k][cx];
     part[(size_t)blockIdx.y * N + col] = t;
   }
+  if (tickets == nullptr) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&tickets[blockIdx.x], 1u) == gridDim.y - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float lane_sum = 0.f;
+  if (ry < 8 && col < N)
+    for (int p = ry; p < (int)gridDim.y; p += 8) lane_sum += __ldcg(part + (size_t)p * N + col);
+  if (ry < 8) sh[ry][cx] = lane_sum;
+  __syncthreads();
+  if (ry == 0 && col < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sh[k][cx];
+    out[col] = __float2bfloat16_rn(t);
+  }
+  if (threadIdx.x == 0) tickets[blockIdx.x] = 0;
 }
 
 // ------------------------------------------------------------------------------------ cross-entropy
@@ -382,8 +410,28 @@ int tb_layernorm_bwd_add(const void* dy, const void* x, const void* w, const flo
 int tb_col_sum(const void* x, int M, int N, int ld, void* out_bf16, float* scratch, cudaStream_t s) {
   const int slices = M >= 2048 ? 32 : (M >= 256 ? 8 : 1);
   dim3 grid((N + 31) / 32, slices);
+  // One launch: each column group's last block finishes the sum.  The ticket words come from a fixed pool handed
+  // out round-robin, so launches in flight at the same time never share one (a pool's worth of launches would
+  // have to overlap); matrices wider than the pool take the two-kernel path.
+  constexpr int POOL = 8192;
+  static unsigned* pool = nullptr;
+  static int pool_device = -1, next = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (pool == nullptr || pool_device != dev) {
+    if (cudaGetSymbolAddress((void**)&pool, g_col_sum_tickets) != cudaSuccess) return (int)cudaGetLastError();
+    pool_device = dev;
+  }
+  if ((int)grid.x <= POOL) {
+    if (next + (int)grid.x > POOL) next = 0;
+    unsigned* tickets = pool + next;
+    next += grid.x;
+    tb_note_launch(1);
+    k_col_sum<<<grid, 1024, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, scratch, tickets, (__nv_bfloat16*)out_bf16);
+    return (int)cudaGetLastError();
+  }
   tb_note_launch(2);
-  k_col_sum<<<grid, 1024, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, scratch);
+  k_col_sum<<<grid, 1024, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, scratch, nullptr, nullptr);
   k_reduce_partials<<<(N + 31) / 32, 256, 0, s>>>(scratch, slices, N, (__nv_bfloat16*)out_bf16, nullptr, N);
   return (int)cudaGetLastError();
 }
@@ -460,7 +508,7 @@ extern "C" int tb_col_sum_noalloc(const void* x_bf16, int M, int N, int ld, void
   const int slices = M >= 2048 ? 32 : (M >= 256 ? 8 : 1);
   dim3 grid((N + 31) / 32, slices);
   tb_note_launch(2);
-  k_col_sum<<<grid, 1024, 0, stream>>>((const __nv_bfloat16*)x_bf16, M, N, ld, scratch);
+  k_col_sum<<<grid, 1024, 0, stream>>>((const __nv_bfloat16*)x_bf16, M, N, ld, scratch, nullptr, nullptr);
   k_reduce_partials<<<(N + 31) / 32, 256, 0, stream>>>(scratch, slices, N, (__nv_bfloat16*)out_bf16, nullptr, N);
   return (int)cudaGetLastError();
 }

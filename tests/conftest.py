@@ -15,6 +15,11 @@ def pytest_collection_modifyitems(config, items):
     import torch
 
     if torch.cuda.is_available():
+        # a GPU test that stops making progress must end by itself (pytest-timeout, when it is installed)
+        if config.pluginmanager.hasplugin("timeout"):
+            for item in items:
+                if "gpu" in item.keywords and item.get_closest_marker("timeout") is None:
+                    item.add_marker(pytest.mark.timeout(600))
         return
     skip = pytest.mark.skip(reason="no CUDA device")
     for item in items:
