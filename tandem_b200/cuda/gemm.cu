@@ -1008,7 +1008,7 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
 // weight-gradient shapes (few output tiles, K = tokens) want 128x128 tiles to fill the machine.
 void choose_tile(int M, int N, int K, int sms, int forced, int* bm, int* bn) {
   struct Shape { int bm, bn; double cost; };  // cost: relative time of one tile at equal K
-  const Shape shapes[4] = {{256, 256, K <= 1024 ? 5.0 : 4.0}, {128, 256, 2.3}, {128, 128, 1.5}, {128, 192, 1.8}};
+  const Shape shapes[4] = {{256, 256, K <= 1024 ? 5.0 : 4.0}, {128, 256, 2.3}, {128, 128, 1.5}, {128, 192, 2.15}};
   if (forced >= 0 && forced < 3) {
     *bm = shapes[forced].bm;
     *bn = shapes[forced].bn;
