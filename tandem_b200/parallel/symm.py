@@ -490,7 +490,11 @@ class SymmetricComm:
         peers = self._peers_of(flat)
         if flat.numel() and self.n > 1:
             mc = self._multicast_of(flat) if peers is not None else 0
-            want_nvls = self.algo == ALGO["nvls"] or (self.algo == ALGO["auto"] and self.n >= self.nvls_min_ranks and max(lens) >= self.nvls_min_bytes)
+            # measured at 8 ranks: multicasting wins or ties up to 64 MB in total (1 MB: 25 us vs 38 us pulled),
+            # loses beyond (256 MB: 656 us vs 404 us)
+            total = offs[-1]
+            want_nvls = self.algo == ALGO["nvls"] or (self.algo == ALGO["auto"] and self.n >= self.nvls_min_ranks
+                                                      and self.nvls_min_bytes <= total <= (32 << 20))
             if mc and want_nvls and mc % 16 == 0 and flat.data_ptr() % 16 == 0 and all(o % 16 == 0 for o in offs):
                 # each rank multicasts its own chunk through the switch (multimem.st)
                 check_rc(self.lib.tb_all_gather_nvls(self._launch_comm, flat.data_ptr(), mc, offs[self.rank], lens[self.rank], max(lens),
