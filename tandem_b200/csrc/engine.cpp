@@ -213,9 +213,10 @@ void Engine::loop() {
 // ------------------------------------------------------------------ counters
 void Engine::wait_count(int r, int which, std::uint64_t value, const char* what) {
   Window* w = win(r);
+  auto reached = [&] { return w->count[which].v.load(std::memory_order_acquire) >= value; };
+  if (reached()) return;  // the usual case for all but the first wait of a round: no label to build
   std::string label = std::string(what) + " (rank " + std::to_string(r) + ")";
-  wait_for([&] { return w->count[which].v.load(std::memory_order_acquire) >= value; }, w->bell, timeout_s_,
-           &win(0)->abort_word, label.c_str());
+  wait_for(reached, w->bell, timeout_s_, &win(0)->abort_word, label.c_str());
 }
 
 void Engine::publish(int which, std::uint64_t value) {
@@ -270,6 +271,7 @@ void Engine::do_all_reduce(unsigned char* p, std::int64_t numel, DType d, bool a
     claim_slot(R);
     unsigned char* mine = slot(me, R);
     for (int c = 0; c < n; ++c) {
+      if (c == me) continue;  // nobody reads this rank's own chunk from its slot: it is folded in from `p` below
       std::int64_t lo, len;
       piece(c, &lo, &len);
       copy_in(mine + c * per * esz, p + (off[c] + lo) * esz, static_cast<std::size_t>(len), d, divisor);
@@ -280,12 +282,20 @@ void Engine::do_all_reduce(unsigned char* p, std::int64_t numel, DType d, bool a
     for (int r = 0; r < n; ++r)
       if (r != me) wait_count(r, POSTED, R + 1, "a rank to post its operands");
     if (len > 0) {
-      // Fold ranks me+1, me+2, ..., me: the association a ring reduce-scatter yields for chunk `me`.
+      // Fold ranks me+1, me+2, ..., me: the association a ring reduce-scatter yields for chunk `me`.  The partial
+      // sum of the peers' operands is built in this rank's own slot area for the chunk (free, see above); the last
+      // addition takes this rank's operand straight from `p` (divided on the way when averaging) and writes the
+      // result to `p` and, for an all-reduce, to the slot where the peers will fetch it -- one pass, no copies.
       unsigned char* acc = p + (off[me] + lo) * esz;
       const std::int64_t at = me * per * esz;
-      std::memcpy(acc, slot((me + 1) % n, R) + at, static_cast<std::size_t>(len * esz));
-      for (int j = 2; j <= n; ++j) add_into(acc, slot((me + j) % n, R) + at, static_cast<std::size_t>(len), d);
-      if (gather) std::memcpy(mine + at, acc, static_cast<std::size_t>(len * esz));
+      const std::size_t count = static_cast<std::size_t>(len);
+      const unsigned char* sum = slot((me + 1) % n, R) + at;
+      if (n > 2) {
+        add2(mine + at, sum, slot((me + 2) % n, R) + at, count, d);
+        for (int j = 3; j < n; ++j) add_into(mine + at, slot((me + j) % n, R) + at, count, d);
+        sum = mine + at;
+      }
+      add_own(acc, gather ? mine + at : nullptr, sum, count, d, divisor);
     }
     publish(REDUCED, R + 1);
     if (gather) {

@@ -58,18 +58,50 @@ struct Arith<_Float16> {
   static _Float16 div(_Float16 a, int n) { return static_cast<_Float16>(static_cast<float>(a) / static_cast<float>(n)); }
 };
 
+// The arrays these loops get never overlap (a tensor, this rank's slot, a peer's slot), which is what lets the
+// compiler vectorise them; the one exception, add_own_t's copy == sum, is written as an in-place update.
 template <class T>
 void add_into_t(void* dst, const void* src, std::size_t n) {
-  T* d = static_cast<T*>(dst);
-  const T* s = static_cast<const T*>(src);
+  T* __restrict d = static_cast<T*>(dst);
+  const T* __restrict s = static_cast<const T*>(src);
   for (std::size_t i = 0; i < n; ++i) d[i] = Arith<T>::add(d[i], s[i]);
 }
 
 template <class T>
 void copy_div_t(void* dst, const void* src, std::size_t n, int divisor) {
-  T* d = static_cast<T*>(dst);
-  const T* s = static_cast<const T*>(src);
+  T* __restrict d = static_cast<T*>(dst);
+  const T* __restrict s = static_cast<const T*>(src);
   for (std::size_t i = 0; i < n; ++i) d[i] = Arith<T>::div(s[i], divisor);
+}
+
+// dst[i] = a[i] + b[i]
+template <class T>
+void add2_t(void* dst, const void* a, const void* b, std::size_t n) {
+  T* __restrict d = static_cast<T*>(dst);
+  const T* __restrict x = static_cast<const T*>(a);
+  const T* __restrict y = static_cast<const T*>(b);
+  for (std::size_t i = 0; i < n; ++i) d[i] = Arith<T>::add(x[i], y[i]);
+}
+
+// own[i] = sum[i] + own[i] / divisor (divisor 0: no division); the result also goes to copy[i] when copy is given.
+// copy is either a separate array or `sum` itself.
+template <class T>
+void add_own_t(void* own, void* copy, const void* sum, std::size_t n, int divisor) {
+  T* __restrict o = static_cast<T*>(own);
+  if (copy == nullptr) {
+    const T* __restrict s = static_cast<const T*>(sum);
+    if (divisor) for (std::size_t i = 0; i < n; ++i) o[i] = Arith<T>::add(s[i], Arith<T>::div(o[i], divisor));
+    else for (std::size_t i = 0; i < n; ++i) o[i] = Arith<T>::add(s[i], o[i]);
+  } else if (copy == sum) {
+    T* __restrict s = static_cast<T*>(copy);
+    if (divisor) for (std::size_t i = 0; i < n; ++i) o[i] = s[i] = Arith<T>::add(s[i], Arith<T>::div(o[i], divisor));
+    else for (std::size_t i = 0; i < n; ++i) o[i] = s[i] = Arith<T>::add(s[i], o[i]);
+  } else {
+    T* __restrict c = static_cast<T*>(copy);
+    const T* __restrict s = static_cast<const T*>(sum);
+    if (divisor) for (std::size_t i = 0; i < n; ++i) o[i] = c[i] = Arith<T>::add(s[i], Arith<T>::div(o[i], divisor));
+    else for (std::size_t i = 0; i < n; ++i) o[i] = c[i] = Arith<T>::add(s[i], o[i]);
+  }
 }
 
 template <class F>
@@ -91,6 +123,16 @@ auto by_dtype(DType d, F&& f) {
 // dst[i] += src[i]
 inline void add_into(void* dst, const void* src, std::size_t n, DType d) {
   by_dtype(d, [&](auto tag) { add_into_t<decltype(tag)>(dst, src, n); });
+}
+
+// dst[i] = a[i] + b[i]
+inline void add2(void* dst, const void* a, const void* b, std::size_t n, DType d) {
+  by_dtype(d, [&](auto tag) { add2_t<decltype(tag)>(dst, a, b, n); });
+}
+
+// own[i] = sum[i] + own[i] / divisor, also stored to copy[i] if copy != nullptr (see add_own_t)
+inline void add_own(void* own, void* copy, const void* sum, std::size_t n, DType d, int divisor) {
+  by_dtype(d, [&](auto tag) { add_own_t<decltype(tag)>(own, copy, sum, n, divisor); });
 }
 
 // dst[i] = src[i] / divisor (divisor 0: plain copy)

@@ -49,7 +49,9 @@ inline void ring(Bell& bell) {
 template <class Pred>
 void wait_for(Pred pred, Bell& bell, double timeout_s, const std::atomic<std::uint32_t>* abort_word,
               const char* what) {
-  for (int i = 0; i < 128; ++i) {
+  // A peer that is running answers within microseconds: poll for about that long before paying for a futex
+  // sleep and its wake-up (tens of microseconds).
+  for (int i = 0; i < 512; ++i) {
     if (pred()) return;
 #if defined(__x86_64__)
     __builtin_ia32_pause();

@@ -56,7 +56,7 @@ def build_host(force=False, verbose=False):
     if not force and not _newer(HOST_LIB, deps):
         return HOST_LIB
     tmp = HOST_LIB + f".{os.getpid()}.tmp"
-    cmd = ["g++", "-O2", "-std=c++17", "-Wall", "-Wextra", "-fPIC", "-shared", "-fvisibility=hidden",
+    cmd = ["g++", "-O3", "-std=c++17", "-Wall", "-Wextra", "-fPIC", "-shared", "-fvisibility=hidden",
            f"-I{sysconfig.get_paths()['include']}", f"-I{pybind11.get_include()}", *srcs, "-o", tmp, "-lrt", "-lpthread"]
     _run(cmd, verbose)
     os.replace(tmp, HOST_LIB)
