@@ -13,11 +13,13 @@
         Step time, tokens/s and peak memory per strategy, with the share of communication hidden
         behind compute (profile of the last step) and an optional Chrome trace (--trace out.json).
 
-One JSON line per measurement, also appended to --out.  On GPUs every time is device time from
-CUDA events, reduced as the maximum over ranks; bus bandwidth = algorithm bandwidth x 2(n-1)/n.
+One JSON line per measurement, also appended to --out; the rows carry the reference driver's keys
+(bench/run.py:268-271, 347-348, 422-439, 451-459) plus bus bandwidth.  On GPUs every time is device time
+from CUDA events, reduced as the maximum over ranks; bus bandwidth = algorithm bandwidth x 2(n-1)/n.
 """
 
 import argparse
+import dataclasses
 import json
 import os
 import statistics
@@ -28,7 +30,7 @@ import torch
 import torch.multiprocessing as mp
 
 from . import launch
-from .data import synthetic, uniform_tokens
+from .data import synthetic
 from .ddp import DDP
 from .model import GPT, Config, count_params, loss_fn
 from .optim import ShardedAdamW
@@ -36,404 +38,502 @@ from .pipeline import Pipeline
 from .profile import Timeline, chrome_trace, summarize
 from .zero import FSDP, ZeRO
 
-LR, WD = 3e-4, 0.1
-OUT = None
+LEARNING_RATE, WEIGHT_DECAY = 3e-4, 0.1
+CORPUS_BYTES = 200_000
 
 
-def emit(row):
-    line = json.dumps(row)
-    print(line, flush=True)
-    if OUT:
-        with open(OUT, "a") as f:
-            f.write(line + "\n")
+# ---------------------------------------------------------------------------------------------- plumbing
+class Rows:
+    """JSON lines to stdout and, when a path is set, to a file."""
+
+    path = None
+
+    @classmethod
+    def write(cls, **fields):
+        text = json.dumps(fields)
+        print(text, flush=True)
+        if cls.path:
+            with open(cls.path, "a") as f:
+                f.write(text + "\n")
 
 
-def setup(device, index, deterministic):
-    if device == "cuda":
-        torch.cuda.set_device(index)
-        if deterministic:
-            os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
-            torch.use_deterministic_algorithms(True)
-            torch.backends.cuda.enable_flash_sdp(False)
-            torch.backends.cuda.enable_mem_efficient_sdp(False)
-        return torch.device("cuda", index)
-    torch.set_num_threads(1)
-    return torch.device("cpu")
+@dataclasses.dataclass
+class Job:
+    """What one training run does; travels to the ranks as one picklable value."""
+
+    strategy: str
+    config: Config
+    steps: int
+    rows: int                      # rows of the global batch
+    micro: int = 4                 # micro-batches (pipeline strategies, single-process accumulation)
+    deterministic: bool = False
+    keep_weights: bool = False
+    profile: bool = False
 
 
-def flat_weights(params):
-    return torch.cat([p.detach().reshape(-1).float().cpu() for p in params])
+def claim_device(kind, index, deterministic):
+    """Makes `index` this process's device and, when asked, pins torch to reproducible kernels."""
+    if kind != "cuda":
+        torch.set_num_threads(1)
+        return torch.device("cpu")
+    torch.cuda.set_device(index)
+    if deterministic:
+        os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+        torch.use_deterministic_algorithms(True)
+        for switch in (torch.backends.cuda.enable_flash_sdp, torch.backends.cuda.enable_mem_efficient_sdp):
+            switch(False)  # leaves the math kernel, the only deterministic attention backward
+    return torch.device("cuda", index)
 
 
-class StepTimer:
-    """Wall time on CPU ranks, CUDA events on GPU ranks."""
+def to_host(parameters):
+    return torch.cat([p.detach().float().reshape(-1).cpu() for p in parameters])
 
-    def __init__(self, dev):
-        self.dev, self.times = dev, []
+
+def adamw(parameters):
+    return torch.optim.AdamW(parameters, lr=LEARNING_RATE, weight_decay=WEIGHT_DECAY, foreach=False)
+
+
+def peak_memory(device):
+    return torch.cuda.max_memory_allocated(device) if device.type == "cuda" else None
+
+
+class Stopwatch:
+    """`with watch: ...` appends the block's duration in seconds to `laps`: device time between two CUDA events
+    on a GPU, wall time on the host."""
+
+    def __init__(self, device):
+        self.cuda = device.type == "cuda"
+        self.laps = []
 
     def __enter__(self):
-        if self.dev.type == "cuda":
-            self.a, self.b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            self.a.record()
+        if self.cuda:
+            self._events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self._events[0].record()
         else:
-            self.t0 = time.perf_counter()
+            self._began = time.perf_counter()
+        return self
 
     def __exit__(self, *exc):
-        if self.dev.type == "cuda":
-            self.b.record()
-            self.b.synchronize()
-            self.times.append(self.a.elapsed_time(self.b) / 1e3)
+        if self.cuda:
+            first, last = self._events
+            last.record()
+            last.synchronize()
+            self.laps.append(first.elapsed_time(last) / 1e3)
         else:
-            self.times.append(time.perf_counter() - self.t0)
+            self.laps.append(time.perf_counter() - self._began)
+        return False
+
+    @staticmethod
+    def time(device, fn):
+        watch = Stopwatch(device)
+        with watch:
+            fn()
+        return watch.laps[0]
 
 
-# ------------------------------------------------------------------------------------------ ranks
-def ours_rank(g, strategy, cfg, steps, batch, micro, deterministic, want_weights, profile):
-    dev = setup(g.device.type, g.device.index or 0, deterministic)
+# ---------------------------------------------------------------------------------------------- our strategies
+class Replicated:
+    """DDP (with or without overlapping the all-reduces with backward) and torch's per-parameter AdamW."""
+
+    def __init__(self, model, group, job, spans):
+        self.model, self.spans = model, spans
+        self.wrapper = DDP(model, group, overlap=job.strategy != "ddp-nooverlap")
+        self.opt = adamw(model.parameters())
+        self.shard = (group.rank, group.size)
+
+    def train_step(self, x, y):
+        with self.spans.span("forward"):
+            loss = self.wrapper(x, y)
+        with self.spans.span("backward"):
+            loss.backward()
+        with self.spans.span("optimizer"):
+            self.opt.step()
+            self.opt.zero_grad()
+        return loss
+
+    def weights(self):
+        return to_host(self.model.parameters())
+
+
+class Sharded:
+    """ZeRO-1/2 and FSDP: the wrapper owns the sharded AdamW."""
+
+    def __init__(self, model, group, job, spans):
+        self.model, self.spans = model, spans
+        opt = ShardedAdamW(lr=LEARNING_RATE, weight_decay=WEIGHT_DECAY, fused=False if job.deterministic else None)
+        stage = int(job.strategy[-1])
+        self.wrapper = FSDP(model, group, opt) if stage == 3 else ZeRO(model, group, stage, opt)
+        self.stage = stage
+        self.shard = (group.rank, group.size)
+
+    def train_step(self, x, y):
+        with self.spans.span("forward"):
+            loss = self.wrapper(x, y)
+        with self.spans.span("backward"):
+            loss.backward()
+        with self.spans.span("optimizer"):
+            self.wrapper.step()
+            self.wrapper.zero_grad()
+        return loss
+
+    def weights(self):
+        if self.stage == 3:
+            return self.wrapper.full_parameters().float().cpu()
+        return to_host(self.model.parameters())
+
+
+class Staged:
+    """GPipe / 1F1B: every stage is handed the whole batch; the pipeline records its own F/B spans."""
+
+    def __init__(self, model, group, job, spans):
+        self.pipe = Pipeline(model, group, job.micro, job.strategy.split("-", 1)[1], timeline=spans)
+        self.opt = adamw(self.pipe.parameters())
+        self.shard = (0, 1)
+
+    def train_step(self, x, y):
+        loss = self.pipe.train_step(x, y)
+        self.opt.step()
+        self.opt.zero_grad()
+        return loss
+
+    def weights(self):
+        return to_host(self.pipe.parameters())
+
+
+def strategy_class(name):
+    if name.startswith("ddp"):
+        return Replicated
+    if name.startswith("zero"):
+        return Sharded
+    if name.startswith("pp-"):
+        return Staged
+    raise ValueError(f"unknown strategy {name}")
+
+
+def train_rank(group, job):
+    """One rank of one of our strategies: losses, per-step times, peak memory, optionally weights and a profile
+    of the last step."""
+    device = claim_device(group.device.type, group.device.index or 0, job.deterministic)
     torch.manual_seed(0)
-    text = synthetic(200_000)
-    model = GPT(cfg).to(dev)
-    tl = Timeline(enabled=profile, device=dev)
-    world, rank = g.size, g.rank
-    pipe = None
-    if strategy.startswith("ddp"):
-        wrapped = DDP(model, g, overlap=strategy != "ddp-nooverlap")
-        opt = torch.optim.AdamW(model.parameters(), lr=LR, weight_decay=WD, foreach=False)
-    elif strategy in ("zero1", "zero2"):
-        wrapped = ZeRO(model, g, int(strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD, fused=False if deterministic else None))
-    elif strategy == "zero3":
-        wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD, fused=False if deterministic else None))
-    else:
-        pipe = Pipeline(model, g, micro, strategy[3:], timeline=tl)
-        opt = torch.optim.AdamW(pipe.parameters(), lr=LR, weight_decay=WD, foreach=False)
-        world, rank = 1, 0
-    losses, timer = [], StepTimer(dev)
-    if dev.type == "cuda":
-        torch.cuda.reset_peak_memory_stats(dev)
-    for step in range(steps):
-        x, y = text.batch(step, batch, cfg.seq, rank=rank, world=world, device=dev)
-        if profile and step == steps - 1:
-            g.trace.clear()
-            g.waits.clear()
-            g.tracing = True
-            tl.spans.clear()
-        with timer:
-            if pipe is not None:
-                loss = pipe.train_step(x, y)
-                opt.step()
-                opt.zero_grad()
-            else:
-                with tl.span("forward"):
-                    loss = wrapped(x, y)
-                with tl.span("backward"):
-                    loss.backward()
-                with tl.span("optimizer"):
-                    if strategy.startswith("ddp"):
-                        opt.step()
-                        opt.zero_grad()
-                    else:
-                        wrapped.step()
-                        wrapped.zero_grad()
-        losses.append(None if loss is None else loss.item())
-    g.tracing = False
-    g._drain_spans()
-    out = {"losses": losses, "times": timer.times,
-           "peak_mem": torch.cuda.max_memory_allocated(dev) if dev.type == "cuda" else None}
-    if profile:
-        comm = [s for s in g.trace if s[0] != "barrier"]
-        out["profile"] = summarize(tl.spans, comm, list(g.waits), timer.times[-1])
-        out["trace"] = (tl.spans, comm)
-    if want_weights:
-        if strategy == "zero3":
-            out["weights"] = wrapped.full_parameters().float().cpu()
-        elif pipe is not None:
-            out["weights"] = flat_weights(pipe.parameters())
-        else:
-            out["weights"] = flat_weights(model.parameters())
-    return out
+    corpus = synthetic(CORPUS_BYTES)
+    model = GPT(job.config).to(device)
+    spans = Timeline(enabled=job.profile, device=device)
+    runner = strategy_class(job.strategy)(model, group, job, spans)
+    rank, world = runner.shard
+    if device.type == "cuda":
+        torch.cuda.reset_peak_memory_stats(device)
+    watch, losses = Stopwatch(device), []
+    for step in range(job.steps):
+        x, y = corpus.batch(step, job.rows, job.config.seq, rank=rank, world=world, device=device)
+        if job.profile and step + 1 == job.steps:  # trace the last step only
+            for log in (group.trace, group.waits, spans.spans):
+                log.clear()
+            group.tracing = True
+        with watch:
+            loss = runner.train_step(x, y)
+        losses.append(loss.item() if loss is not None else None)
+    group.tracing = False
+    group._drain_spans()
+    result = {"losses": losses, "times": watch.laps, "peak_mem": peak_memory(device)}
+    if job.profile:
+        collectives = [span for span in group.trace if span[0] != "barrier"]
+        result["profile"] = summarize(spans.spans, collectives, list(group.waits), watch.laps[-1])
+        result["trace"] = (spans.spans, collectives)
+    if job.keep_weights:
+        result["weights"] = runner.weights()
+    return result
 
 
-def torch_rank(rank, world, init, out, device, strategy, cfg, steps, batch, deterministic, want_weights):
+def run_ours(job, device, world):
+    return launch(train_rank, world, job, device=device)
+
+
+# ---------------------------------------------------------------------------------------------- baselines
+def _torch_rank(rank, world, rendezvous, prefix, device_kind, job):
     import torch.distributed as dist
 
-    dev = setup(device, rank, deterministic)
-    dist.init_process_group("nccl" if device == "cuda" else "gloo", init_method=f"file://{init}", rank=rank, world_size=world)
+    device = claim_device(device_kind, rank, job.deterministic)
+    backend = "nccl" if device_kind == "cuda" else "gloo"
+    dist.init_process_group(backend, init_method=f"file://{rendezvous}", rank=rank, world_size=world)
     torch.manual_seed(0)
-    text = synthetic(200_000)
-    model = GPT(cfg).to(dev)
-    if strategy == "torch-ddp":
-        from torch.nn.parallel import DistributedDataParallel
-
-        wrapped = DistributedDataParallel(model, device_ids=[rank] if device == "cuda" else None)
-    else:
-        from torch.distributed.fsdp import FullyShardedDataParallel, ShardingStrategy
+    corpus = synthetic(CORPUS_BYTES)
+    model = GPT(job.config).to(device)
+    sharded = job.strategy == "torch-fsdp"
+    if sharded:
+        from torch.distributed.fsdp import FullyShardedDataParallel as TorchFSDP
+        from torch.distributed.fsdp import ShardingStrategy
         from torch.distributed.fsdp.wrap import ModuleWrapPolicy
 
         from .model import Block, Embed, Head
 
-        wrapped = FullyShardedDataParallel(model, auto_wrap_policy=ModuleWrapPolicy({Embed, Block, Head}),
-                                           sharding_strategy=ShardingStrategy.FULL_SHARD,
-                                           device_id=dev if device == "cuda" else None, use_orig_params=True)
-    opt = torch.optim.AdamW(wrapped.parameters(), lr=LR, weight_decay=WD, foreach=False)
-    losses, timer = [], StepTimer(dev)
-    if dev.type == "cuda":
-        torch.cuda.reset_peak_memory_stats(dev)
-    for step in range(steps):
-        x, y = text.batch(step, batch, cfg.seq, rank=rank, world=world, device=dev)
-        with timer:
-            loss = wrapped(x, y)
+        wrapper = TorchFSDP(model, auto_wrap_policy=ModuleWrapPolicy({Embed, Block, Head}), use_orig_params=True,
+                            sharding_strategy=ShardingStrategy.FULL_SHARD, device_id=device if device_kind == "cuda" else None)
+    else:
+        from torch.nn.parallel import DistributedDataParallel
+
+        wrapper = DistributedDataParallel(model, device_ids=[rank] if device_kind == "cuda" else None)
+    opt = adamw(wrapper.parameters())
+    if device.type == "cuda":
+        torch.cuda.reset_peak_memory_stats(device)
+    watch, losses = Stopwatch(device), []
+    for step in range(job.steps):
+        x, y = corpus.batch(step, job.rows, job.config.seq, rank=rank, world=world, device=device)
+        with watch:
+            loss = wrapper(x, y)
             loss.backward()
             opt.step()
             opt.zero_grad()
         losses.append(loss.item())
-    res = {"losses": losses, "times": timer.times,
-           "peak_mem": torch.cuda.max_memory_allocated(dev) if dev.type == "cuda" else None}
-    if want_weights:
-        if strategy == "torch-fsdp":
-            from torch.distributed.fsdp import FullyShardedDataParallel
-
-            with FullyShardedDataParallel.summon_full_params(wrapped):
-                res["weights"] = flat_weights(model.parameters())
+    result = {"losses": losses, "times": watch.laps, "peak_mem": peak_memory(device)}
+    if job.keep_weights:
+        if sharded:
+            with TorchFSDP.summon_full_params(wrapper):
+                result["weights"] = to_host(model.parameters())
         else:
-            res["weights"] = flat_weights(model.parameters())
-    torch.save(res, f"{out}.{rank}")
+            result["weights"] = to_host(model.parameters())
+    torch.save(result, f"{prefix}.{rank}")
     dist.destroy_process_group()
 
 
-def run_torch(strategy, device, world, cfg, steps, batch, deterministic=False, want_weights=False):
-    with tempfile.TemporaryDirectory() as d:
-        mp.spawn(torch_rank, args=(world, os.path.join(d, "init"), os.path.join(d, "out"), device, strategy, cfg, steps, batch,
-                                   deterministic, want_weights), nprocs=world)
-        return [torch.load(os.path.join(d, f"out.{r}"), weights_only=False) for r in range(world)]
+def run_torch(job, device, world):
+    """torch DDP ("torch-ddp") or torch FSDP ("torch-fsdp") on `world` ranks: one result per rank."""
+    with tempfile.TemporaryDirectory() as scratch:
+        prefix = os.path.join(scratch, "rank")
+        mp.spawn(_torch_rank, args=(world, os.path.join(scratch, "rendezvous"), prefix, device, job), nprocs=world)
+        return [torch.load(f"{prefix}.{rank}", weights_only=False) for rank in range(world)]
 
 
-def run_ours(strategy, device, world, cfg, steps, batch, micro=4, deterministic=False, want_weights=False, profile=False):
-    return launch(ours_rank, world, strategy, cfg, steps, batch, micro, deterministic, want_weights, profile, device=device)
-
-
-def single_rank(_, device, cfg, steps, batch, micro, deterministic, out):
-    dev = setup(device, 0, deterministic)
+def _alone_rank(_index, device_kind, job, path):
+    device = claim_device(device_kind, 0, job.deterministic)
     torch.manual_seed(0)
-    text = synthetic(200_000)
-    model = GPT(cfg).to(dev)
-    opt = torch.optim.AdamW(model.parameters(), lr=LR, weight_decay=WD, foreach=False)
-    losses, timer = [], StepTimer(dev)
-    for step in range(steps):
-        x, y = text.batch(step, batch, cfg.seq, device=dev)
-        with timer:
-            total = 0
-            for xb, yb in zip(x.chunk(micro), y.chunk(micro)):
-                loss = loss_fn(model(xb), yb) / micro
-                loss.backward()
-                total = total + loss.detach()
+    corpus = synthetic(CORPUS_BYTES)
+    model = GPT(job.config).to(device)
+    opt = adamw(model.parameters())
+    watch, losses = Stopwatch(device), []
+    for step in range(job.steps):
+        x, y = corpus.batch(step, job.rows, job.config.seq, device=device)
+        with watch:
+            step_loss = 0
+            for xs, ys in zip(x.chunk(job.micro), y.chunk(job.micro)):
+                piece = loss_fn(model(xs), ys) / job.micro
+                piece.backward()
+                step_loss = step_loss + piece.detach()
             opt.step()
             opt.zero_grad()
-        losses.append(total.item())
-    torch.save({"losses": losses, "times": timer.times, "weights": flat_weights(model.parameters()),
-                "unit_sizes": [sum(p.numel() for p in u.parameters()) for u in model.units()],
-                "peak_mem": torch.cuda.max_memory_allocated(dev) if dev.type == "cuda" else None}, out)
+        losses.append(step_loss.item())
+    torch.save({"losses": losses, "times": watch.laps, "weights": to_host(model.parameters()), "peak_mem": peak_memory(device),
+                "unit_sizes": [sum(p.numel() for p in unit.parameters()) for unit in model.units()]}, path)
 
 
-def run_single(device, cfg, steps, batch, micro, deterministic=False):
-    with tempfile.TemporaryDirectory() as d:
-        out = os.path.join(d, "single.pt")
-        mp.spawn(single_rank, args=(device, cfg, steps, batch, micro, deterministic, out), nprocs=1)
-        return torch.load(out, weights_only=False)
+def run_alone(job, device):
+    """One process accumulating gradients over `job.micro` micro-batches per step (run in a child so that its
+    device settings do not leak into this process)."""
+    with tempfile.TemporaryDirectory() as scratch:
+        path = os.path.join(scratch, "alone.pt")
+        mp.spawn(_alone_rank, args=(device, job, path), nprocs=1)
+        return torch.load(path, weights_only=False)
 
 
-# ------------------------------------------------------------------------------------------ sections
-def compare(name, ours, ref, ref_name):
-    a, b = ours[0], ref[0]
-    emit({"section": "verify", "strategy": name, "against": ref_name, "losses_equal": a["losses"] == b["losses"],
-          "weights_equal": bool(torch.equal(a["weights"], b["weights"])),
-          "max_weight_diff": float((a["weights"] - b["weights"]).abs().max()), "steps": len(b["losses"]),
-          "final_loss": a["losses"][-1]})
-
-
+# ---------------------------------------------------------------------------------------------- verify
 def verify(device, world):
-    cfg = Config(seq=128, layers=4, heads=4, dim=256)
-    kw = dict(cfg=cfg, steps=20, batch=16, deterministic=True, want_weights=True)
-    ref = run_torch("torch-ddp", device, world, **kw)
-    emit({"section": "verify", "model_params": count_params(GPT(cfg)), "device": device, "ranks": world, "torch": torch.__version__})
+    config = Config(seq=128, layers=4, heads=4, dim=256)
+    base = Job("torch-ddp", config, steps=20, rows=16, deterministic=True, keep_weights=True)
+    Rows.write(section="verify", model_params=count_params(GPT(config)), device=device, ranks=world, torch=torch.__version__)
+    reference = run_torch(base, device, world)[0]
+
+    def against_torch_ddp(name, result):
+        diff = (result["weights"] - reference["weights"]).abs().max()
+        Rows.write(section="verify", strategy=name, against="torch-ddp", losses_equal=result["losses"] == reference["losses"],
+                   weights_equal=bool(torch.equal(result["weights"], reference["weights"])), max_weight_diff=float(diff),
+                   steps=len(reference["losses"]), final_loss=result["losses"][-1])
+
     try:
-        compare("torch-fsdp", run_torch("torch-fsdp", device, world, **kw), ref, "torch-ddp")
-    except Exception as e:
-        emit({"section": "verify", "strategy": "torch-fsdp", "error": repr(e)[:300]})
-    for s in ("ddp", "zero1", "zero2", "zero3"):
-        compare(s, run_ours(s, device, world, **kw), ref, "torch-ddp")
-    single = run_single(device, cfg, 20, 16, 4, deterministic=True)
-    for s in ("pp-gpipe", "pp-1f1b"):
-        ours = run_ours(s, device, world, micro=4, **kw)
-        stages = torch.cat([o["weights"] for o in ours])
-        emit({"section": "verify", "strategy": s, "against": "single-process accumulation", "stages": world,
-              "losses_equal": ours[-1]["losses"] == single["losses"], "weights_equal": bool(torch.equal(stages, single["weights"])),
-              "max_weight_diff": float((stages - single["weights"]).abs().max())})
+        against_torch_ddp("torch-fsdp", run_torch(dataclasses.replace(base, strategy="torch-fsdp"), device, world)[0])
+    except Exception as error:
+        Rows.write(section="verify", strategy="torch-fsdp", error=repr(error)[:300])
+    for name in ("ddp", "zero1", "zero2", "zero3"):
+        against_torch_ddp(name, run_ours(dataclasses.replace(base, strategy=name), device, world)[0])
+
+    alone = run_alone(dataclasses.replace(base, strategy="alone"), device)
+    for name in ("pp-gpipe", "pp-1f1b"):
+        stages = run_ours(dataclasses.replace(base, strategy=name), device, world)
+        weights = torch.cat([stage["weights"] for stage in stages])
+        Rows.write(section="verify", strategy=name, against="single-process accumulation", stages=world,
+                   losses_equal=stages[-1]["losses"] == alone["losses"], weights_equal=bool(torch.equal(weights, alone["weights"])),
+                   max_weight_diff=float((weights - alone["weights"]).abs().max()))
 
 
-def ar_ours(g, sizes, reps):
-    dev = setup(g.device.type, g.device.index or 0, False)
-    out = {}
-    for mb in sizes:
-        x = g.empty(mb * (1 << 20) // 4, torch.float32, dev)
-        x.fill_(1.0)
-        g.all_reduce(x)
-        ts = []
-        for _ in range(reps):
-            g.barrier()
-            timer = StepTimer(dev)
-            with timer:
-                g.all_reduce(x)
-            ts.append(timer.times[0])
-        out[mb] = statistics.median(ts)
-        g.release(x)
-    return out
+# ---------------------------------------------------------------------------------------------- all-reduce by size
+MEGABYTES = (1, 4, 16, 64, 256)
+REPEATS = 10
 
 
-def ar_torch(rank, world, init, out, device, sizes, reps):
+def _median_all_reduce(device, tensor, all_reduce, barrier):
+    all_reduce(tensor)  # warm-up, and the first touch of the buffers
+    laps = []
+    for _ in range(REPEATS):
+        barrier()
+        laps.append(Stopwatch.time(device, lambda: all_reduce(tensor)))
+    return statistics.median(laps)
+
+
+def _ours_all_reduce_rank(group):
+    device = claim_device(group.device.type, group.device.index or 0, False)
+    medians = {}
+    for mb in MEGABYTES:
+        tensor = group.empty((mb << 20) // 4, torch.float32, device)
+        tensor.fill_(1.0)
+        medians[mb] = _median_all_reduce(device, tensor, group.all_reduce, group.barrier)
+        group.release(tensor)
+    return medians
+
+
+def _torch_all_reduce_rank(rank, world, rendezvous, prefix, device_kind):
     import torch.distributed as dist
 
-    dev = setup(device, rank, False)
-    dist.init_process_group("nccl" if device == "cuda" else "gloo", init_method=f"file://{init}", rank=rank, world_size=world)
-    res = {}
-    for mb in sizes:
-        x = torch.ones(mb * (1 << 20) // 4, device=dev)
-        dist.all_reduce(x)
-        ts = []
-        for _ in range(reps):
-            dist.barrier()
-            timer = StepTimer(dev)
-            with timer:
-                dist.all_reduce(x)
-            ts.append(timer.times[0])
-        res[mb] = statistics.median(ts)
-    torch.save(res, f"{out}.{rank}")
+    device = claim_device(device_kind, rank, False)
+    dist.init_process_group("nccl" if device_kind == "cuda" else "gloo", init_method=f"file://{rendezvous}", rank=rank, world_size=world)
+    medians = {mb: _median_all_reduce(device, torch.ones((mb << 20) // 4, device=device), dist.all_reduce, dist.barrier)
+               for mb in MEGABYTES}
+    torch.save(medians, f"{prefix}.{rank}")
     dist.destroy_process_group()
 
 
 def allreduce(device, world):
-    sizes, reps = [1, 4, 16, 64, 256], 10
-    ours = launch(ar_ours, world, sizes, reps, device=device)
-    with tempfile.TemporaryDirectory() as d:
-        mp.spawn(ar_torch, args=(world, os.path.join(d, "init"), os.path.join(d, "o"), device, sizes, reps), nprocs=world)
-        ref = [torch.load(os.path.join(d, f"o.{r}")) for r in range(world)]
-    base = "nccl" if device == "cuda" else "gloo"
-    bus = 2 * (world - 1) / world
-    for mb in sizes:
-        t_ours, t_ref = max(o[mb] for o in ours), max(o[mb] for o in ref)
-        emit({"section": "allreduce", "MB": mb, "ranks": world, "ours_ms": t_ours * 1e3, f"{base}_ms": t_ref * 1e3,
-              "ours_GBps": mb / 1024 / t_ours, f"{base}_GBps": mb / 1024 / t_ref, "ours_bus_GBps": mb / 1024 / t_ours * bus,
-              f"{base}_bus_GBps": mb / 1024 / t_ref * bus})
+    ours = launch(_ours_all_reduce_rank, world, device=device)
+    with tempfile.TemporaryDirectory() as scratch:
+        prefix = os.path.join(scratch, "rank")
+        mp.spawn(_torch_all_reduce_rank, args=(world, os.path.join(scratch, "rendezvous"), prefix, device), nprocs=world)
+        theirs = [torch.load(f"{prefix}.{rank}") for rank in range(world)]
+    library = "nccl" if device == "cuda" else "gloo"
+    bus_factor = 2 * (world - 1) / world
+    for mb in MEGABYTES:
+        slowest_ours = max(rank[mb] for rank in ours)
+        slowest_theirs = max(rank[mb] for rank in theirs)
+        gigabytes = mb / 1024
+        Rows.write(**{"section": "allreduce", "MB": mb, "ranks": world,
+                      "ours_ms": slowest_ours * 1e3, f"{library}_ms": slowest_theirs * 1e3,
+                      "ours_GBps": gigabytes / slowest_ours, f"{library}_GBps": gigabytes / slowest_theirs,
+                      "ours_bus_GBps": gigabytes / slowest_ours * bus_factor, f"{library}_bus_GBps": gigabytes / slowest_theirs * bus_factor})
 
 
-def contention_rank(g, mb, reps, gemms):
-    """Device time of a 64 MB all-reduce alone, then while the default stream runs GEMMs it does not depend on."""
-    dev = setup("cuda", g.device.index or 0, False)
-    x = g.empty(mb * (1 << 20) // 4, torch.float32, dev)
-    a = torch.randn(4096, 4096, device=dev).bfloat16()
-    g.all_reduce(x)
-    a @ a
+# ---------------------------------------------------------------------------------------------- contention
+def _contention_rank(group, megabytes, repeats, gemms):
+    """Device time of one all-reduce alone, then while the training stream runs GEMMs that do not depend on it."""
+    device = claim_device("cuda", group.device.index or 0, False)
+    message = group.empty((megabytes << 20) // 4, torch.float32, device)
+    matrix = torch.randn(4096, 4096, device=device).bfloat16()
+
+    def gemm_burst(count):
+        for _ in range(count):
+            matrix @ matrix
+
+    group.all_reduce(message)
+    gemm_burst(1)
     torch.cuda.synchronize()
 
-    def once(busy):
-        g.barrier()
-        x.fill_(1.0)
-        g.trace.clear()
-        g.tracing = True
-        t0 = torch.cuda.Event(enable_timing=True)
-        t1 = torch.cuda.Event(enable_timing=True)
-        t0.record()
-        w = g.all_reduce(x, async_op=True)
-        for _ in range(gemms if busy else 0):
-            a @ a
-        w.wait()
-        t1.record()
+    def all_reduce_with(gemm_count):
+        """(seconds the collective ran, seconds from its launch to the end of the GEMMs and the wait)"""
+        group.barrier()
+        message.fill_(1.0)
+        group.trace.clear()
+        group.tracing = True
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        handle = group.all_reduce(message, async_op=True)
+        gemm_burst(gemm_count)
+        handle.wait()
+        end.record()
         torch.cuda.synchronize()
-        g.tracing = False
-        g._drain_spans()
-        _, s, e, _ = g.trace[-1]
-        assert torch.equal(x, torch.full_like(x, float(g.size))), "wrong all-reduce result"
-        return e - s, t0.elapsed_time(t1) / 1e3
+        group.tracing = False
+        group._drain_spans()
+        _name, started, finished, _bytes = group.trace[-1]
+        assert torch.equal(message, torch.full_like(message, float(group.size))), "wrong all-reduce result"
+        return finished - started, begin.elapsed_time(end) / 1e3
 
-    def gemm_alone():
-        timer = StepTimer(dev)
-        with timer:
-            for _ in range(gemms):
-                a @ a
-        return timer.times[0]
-
-    alone = statistics.median(once(False)[0] for _ in range(reps))
-    busy = [once(True) for _ in range(reps)]
-    return {"comm_alone_ms": alone * 1e3, "comm_busy_ms": statistics.median(c for c, _ in busy) * 1e3,
-            "gemms_ms": statistics.median(gemm_alone() for _ in range(reps)) * 1e3,
-            "gemms_plus_comm_ms": statistics.median(t for _, t in busy) * 1e3}
+    quiet = statistics.median(all_reduce_with(0)[0] for _ in range(repeats))
+    loaded = [all_reduce_with(gemms) for _ in range(repeats)]
+    gemms_only = statistics.median(Stopwatch.time(device, lambda: gemm_burst(gemms)) for _ in range(repeats))
+    return {"comm_alone_ms": quiet * 1e3, "comm_busy_ms": statistics.median(ran for ran, _ in loaded) * 1e3,
+            "gemms_ms": gemms_only * 1e3, "gemms_plus_comm_ms": statistics.median(total for _, total in loaded) * 1e3}
 
 
 def contention(world):
-    emit({"section": "contention", "gpu": torch.cuda.get_device_name(0), "ranks": world})
-    for priority in (0, -1):
-        r = launch(contention_rank, world, 64, 5, 16, device="cuda", priority=priority)
-        row = {"section": "contention", "priority": priority}
-        for k in r[0]:
-            row[k] = round(max(o[k] for o in r), 3)
-        row["slowdown"] = round(row["comm_busy_ms"] / row["comm_alone_ms"], 2)
-        emit(row)
+    Rows.write(section="contention", gpu=torch.cuda.get_device_name(0), ranks=world)
+    for priority in (0, -1):  # communication stream at normal and at high priority
+        per_rank = launch(_contention_rank, world, 64, 5, 16, device="cuda", priority=priority)
+        worst = {key: round(max(rank[key] for rank in per_rank), 3) for key in per_rank[0]}
+        Rows.write(section="contention", priority=priority, **worst, slowdown=round(worst["comm_busy_ms"] / worst["comm_alone_ms"], 2))
 
 
-def bench(device, world, preset, steps, batch, trace_path):
-    cfg = Config.preset(preset)
-    tokens = batch * cfg.seq
-    emit({"section": "bench", "model": preset, "params": count_params(GPT(cfg)), "global_batch": batch, "seq": cfg.seq,
-          "device": device, "ranks": world})
+# ---------------------------------------------------------------------------------------------- training matrix
+def bench(device, world, preset, steps, rows, trace_path):
+    config = Config.preset(preset)
+    Rows.write(section="bench", model=preset, params=count_params(GPT(config)), global_batch=rows, seq=config.seq,
+               device=device, ranks=world)
+    tokens = rows * config.seq
 
-    def report(name, res):
-        per_rank = [statistics.median(r["times"][2:]) if len(r["times"]) > 2 else r["times"][-1] for r in res]
-        med = max(per_rank)
-        row = {"section": "bench", "strategy": name, "step_ms": med * 1e3, "tokens_per_s": tokens / med,
-               "peak_mem_MB": [None if r.get("peak_mem") is None else round(r["peak_mem"] / 2 ** 20) for r in res],
-               "final_loss": statistics.mean(r["losses"][-1] for r in res if r["losses"][-1] is not None)}
-        if "profile" in res[0]:
-            row["profile_rank0"] = {k: (round(v, 5) if isinstance(v, float) else v) for k, v in res[0]["profile"].items()}
-        emit(row)
+    def report(name, per_rank):
+        def typical(times):  # the first two steps warm up allocators and bucket order
+            return statistics.median(times[2:]) if len(times) > 2 else times[-1]
 
-    report("single", [run_single(device, cfg, steps, batch, 1)])
-    for s in ("torch-ddp", "torch-fsdp"):
+        step_s = max(typical(rank["times"]) for rank in per_rank)
+        final = [rank["losses"][-1] for rank in per_rank if rank["losses"][-1] is not None]
+        fields = {"section": "bench", "strategy": name, "step_ms": step_s * 1e3, "tokens_per_s": tokens / step_s,
+                  "peak_mem_MB": [None if rank.get("peak_mem") is None else round(rank["peak_mem"] / 2 ** 20) for rank in per_rank],
+                  "final_loss": statistics.mean(final)}
+        if "profile" in per_rank[0]:
+            fields["profile_rank0"] = {k: (round(v, 5) if isinstance(v, float) else v) for k, v in per_rank[0]["profile"].items()}
+        Rows.write(**fields)
+
+    def attempt(name, run):
         try:
-            report(s, run_torch(s, device, world, cfg, steps, batch))
-        except Exception as e:
-            emit({"section": "bench", "strategy": s, "error": repr(e)[:300]})
-    for s in ("ddp", "ddp-nooverlap", "zero1", "zero2", "zero3", "pp-gpipe", "pp-1f1b"):
-        try:
-            res = run_ours(s, device, world, cfg, steps, batch, profile=s in ("ddp", "ddp-nooverlap", "zero3"))
-            report(s, res)
-            if trace_path and s == "ddp":
-                chrome_trace([r["trace"] for r in res], trace_path)
-        except Exception as e:
-            emit({"section": "bench", "strategy": s, "error": repr(e)[:300]})
+            return run()
+        except Exception as error:
+            Rows.write(section="bench", strategy=name, error=repr(error)[:300])
+            return None
+
+    job = Job("alone", config, steps, rows, micro=1)
+    report("single", [run_alone(job, device)])
+    for name in ("torch-ddp", "torch-fsdp"):
+        result = attempt(name, lambda: run_torch(dataclasses.replace(job, strategy=name), device, world))
+        if result is not None:
+            report(name, result)
+    for name in ("ddp", "ddp-nooverlap", "zero1", "zero2", "zero3", "pp-gpipe", "pp-1f1b"):
+        traced = name in ("ddp", "ddp-nooverlap", "zero3")
+        result = attempt(name, lambda: run_ours(dataclasses.replace(job, strategy=name, micro=4, profile=traced), device, world))
+        if result is None:
+            continue
+        report(name, result)
+        if trace_path and name == "ddp":
+            chrome_trace([rank["trace"] for rank in result], trace_path)
 
 
 def main():
-    global OUT
-    ap = argparse.ArgumentParser()
-    ap.add_argument("what", nargs="?", default="verify", choices=["verify", "allreduce", "contention", "bench", "all"])
-    ap.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
-    ap.add_argument("--ranks", type=int, default=2)
-    ap.add_argument("--model", default="medium")
-    ap.add_argument("--steps", type=int, default=12)
-    ap.add_argument("--batch", type=int, default=16)
-    ap.add_argument("--trace", default=None)
-    ap.add_argument("--out", default=None)
-    a = ap.parse_args()
-    OUT = a.out
-    if a.device == "cuda" and torch.cuda.device_count() < a.ranks:
-        raise SystemExit(f"needs {a.ranks} GPUs, found {torch.cuda.device_count()}")
-    if a.what in ("verify", "all"):
-        verify(a.device, a.ranks)
-    if a.what in ("allreduce", "all"):
-        allreduce(a.device, a.ranks)
-    if a.what in ("contention", "all") and a.device == "cuda":
-        contention(a.ranks)
-    if a.what in ("bench", "all"):
-        bench(a.device, a.ranks, a.model, a.steps, a.batch, a.trace)
+    parser = argparse.ArgumentParser(description="verification and benchmark driver")
+    parser.add_argument("what", nargs="?", default="verify", choices=["verify", "allreduce", "contention", "bench", "all"])
+    parser.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
+    parser.add_argument("--ranks", type=int, default=2)
+    parser.add_argument("--model", default="medium")
+    parser.add_argument("--steps", type=int, default=12)
+    parser.add_argument("--batch", type=int, default=16)
+    parser.add_argument("--trace", default=None)
+    parser.add_argument("--out", default=None)
+    args = parser.parse_args()
+    Rows.path = args.out
+    if args.device == "cuda" and torch.cuda.device_count() < args.ranks:
+        raise SystemExit(f"needs {args.ranks} GPUs, found {torch.cuda.device_count()}")
+    sections = ("verify", "allreduce", "contention", "bench") if args.what == "all" else (args.what,)
+    for section in sections:
+        if section == "verify":
+            verify(args.device, args.ranks)
+        elif section == "allreduce":
+            allreduce(args.device, args.ranks)
+        elif section == "contention":
+            if args.device == "cuda":
+                contention(args.ranks)
+        else:
+            bench(args.device, args.ranks, args.model, args.steps, args.batch, args.trace)
 
 
 if __name__ == "__main__":
