@@ -86,8 +86,8 @@ PYBIND11_MODULE(_host, m) {
   py::class_<Channel>(m, "Channel")
       .def_static("create", &Channel::create, py::arg("name"), py::arg("slots"), py::arg("slot_bytes"))
       .def_static("open", &Channel::open, py::arg("name"))
-      .def_property_readonly("slots", &Channel::slots)
-      .def_property_readonly("slot_bytes", &Channel::slot_bytes)
+      .def_property_readonly("slots", &Channel::slot_count)
+      .def_property_readonly("slot_bytes", &Channel::slot_capacity)
       .def(
           "send",
           [](Channel& c, const py::bytes& b, double timeout) {

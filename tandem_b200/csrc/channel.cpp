@@ -66,8 +66,8 @@ Channel Channel::open(const std::string& name) {
   return Channel(std::move(shm));
 }
 
-std::size_t Channel::slots() const noexcept { return valid() ? header(shm_)->slots : 0; }
-std::size_t Channel::slot_bytes() const noexcept { return valid() ? header(shm_)->slot_bytes : 0; }
+std::size_t Channel::slot_count() const noexcept { return valid() ? header(shm_)->slots : 0; }
+std::size_t Channel::slot_capacity() const noexcept { return valid() ? header(shm_)->slot_bytes : 0; }
 
 void Channel::wait_writable(double timeout_s) {
   Header* h = header(shm_);
@@ -88,16 +88,16 @@ void Channel::send(const void* data, std::size_t n, double timeout_s) {
   ring(h->written.bell);
 }
 
-std::pair<const void*, std::size_t> Channel::peek(double timeout_s) {
+MessageView Channel::front(double timeout_s) {
   Header* h = header(shm_);
   std::uint64_t r = h->read.count.load(std::memory_order_relaxed);
   wait_for([&] { return h->written.count.load(std::memory_order_acquire) > r; }, h->written.bell, timeout_s, abort_,
            "a message in the channel");
   Entry* e = entry(shm_, r);
-  return {e->bytes, static_cast<std::size_t>(e->length)};
+  return MessageView{e->bytes, static_cast<std::size_t>(e->length)};
 }
 
-void Channel::release() {
+void Channel::pop() {
   Header* h = header(shm_);
   std::uint64_t r = h->read.count.load(std::memory_order_relaxed);
   h->read.count.store(r + 1, std::memory_order_release);
@@ -111,11 +111,12 @@ void Channel::wake_all() {
 }
 
 std::size_t Channel::recv(void* out, std::size_t capacity, double timeout_s) {
-  auto [p, n] = peek(timeout_s);
-  if (n > capacity) throw std::length_error("message of " + std::to_string(n) + " bytes does not fit " + std::to_string(capacity));
-  if (n) std::memcpy(out, p, n);
-  release();
-  return n;
+  const MessageView head = front(timeout_s);
+  if (head.size > capacity)
+    throw std::length_error("message of " + std::to_string(head.size) + " bytes does not fit " + std::to_string(capacity));
+  if (head.size) std::memcpy(out, head.data, head.size);
+  pop();
+  return head.size;
 }
 
 }  // namespace tb

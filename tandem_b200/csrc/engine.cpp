@@ -388,13 +388,13 @@ void Engine::do_exchange(const unsigned char* sp, std::int64_t sbytes, int dst, 
     }
     if (ro < rbytes) {
       std::int64_t want = std::min(per, rbytes - ro);
-      auto [data, len] = in_[src].peek(timeout_s_);
-      if (static_cast<std::int64_t>(len) != want) {
+      const MessageView piece = in_[src].front(timeout_s_);
+      if (static_cast<std::int64_t>(piece.size) != want) {
         throw std::runtime_error("out of step with rank " + std::to_string(src) + ": expected a piece of " +
-                                 std::to_string(want) + " bytes, got " + std::to_string(len));
+                                 std::to_string(want) + " bytes, got " + std::to_string(piece.size));
       }
-      std::memcpy(rp + ro, data, len);
-      in_[src].release();
+      std::memcpy(rp + ro, piece.data, piece.size);
+      in_[src].pop();
       ro += want;
     }
   }
