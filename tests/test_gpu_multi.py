@@ -16,9 +16,10 @@ needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs"
 
 
 def data(rank, n, dtype, seed=0):
-    g = torch.Generator().manual_seed(seed * 1000 + rank)
-    hi = 30 if dtype in (torch.bfloat16, torch.float16) else 100
-    return torch.randint(-hi, hi, (n,), generator=g).to(dtype)
+    """Rank `rank`'s integer-valued operand (the generator of the CPU collective tests)."""
+    from test_comm import operand
+
+    return operand(rank, n, dtype, salt=seed)
 
 
 def gpu_collectives(g):
