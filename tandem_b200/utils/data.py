@@ -1,54 +1,65 @@
-"""Token batches.  `Text` and `synthetic` follow the reference's tandem/data.py:9-41
-(every rank draws the global batch from a per-step seed and keeps its rows, so N
-ranks see exactly what one process would).  `uniform_tokens` is the benchmark
-input named by the baseline configs: token ids uniform in [0, vocab) from a seed."""
+"""Token batches for training runs and benchmarks.
+
+Every rank derives the WHOLE global batch of a step from a seed that depends only on (seed, step) and keeps the
+rows that belong to it, so N ranks together see exactly the rows one process would.  `Text` (byte-level text,
+vocabulary 256) and `synthetic` produce the same batches as the reference's tandem/data.py:9-41 for the same
+arguments; `uniform_tokens` is the benchmark input of the baseline configurations: ids uniform in [0, vocab).
+"""
 
 import torch
 
 
+def _step_generator(seed, step):
+    gen = torch.Generator()
+    gen.manual_seed(seed * 1_000_003 + step)
+    return gen
+
+
+def _rows_of_rank(count, rank, world):
+    """The slice of a global batch of `count` rows that rank `rank` of `world` trains on."""
+    if count % world:
+        raise ValueError(f"global batch {count} does not divide over {world} ranks")
+    share = count // world
+    return slice(rank * share, (rank + 1) * share)
+
+
 class Text:
+    """A byte string as a token stream; batches are windows of seq + 1 bytes at random offsets."""
+
     def __init__(self, path=None, data=None):
         if data is None:
-            with open(path, "rb") as f:
-                data = f.read()
+            with open(path, "rb") as source:
+                data = source.read()
         self.data = torch.frombuffer(bytearray(data), dtype=torch.uint8).long()
 
     def batch(self, step, batch, seq, seed=0, rank=0, world=1, device="cpu"):
-        """Rows [rank*batch/world, (rank+1)*batch/world) of global batch `step`,
-        as (inputs, targets) shifted by one position."""
-        if batch % world:
-            raise ValueError(f"global batch {batch} does not divide over {world} ranks")
-        gen = torch.Generator().manual_seed(seed * 1_000_003 + step)
-        starts = torch.randint(0, self.data.numel() - seq - 1, (batch,), generator=gen)
-        per = batch // world
-        idx = starts[rank * per:(rank + 1) * per, None] + torch.arange(seq + 1)[None, :]
-        rows = self.data[idx]
-        return rows[:, :-1].to(device, non_blocking=True), rows[:, 1:].to(device, non_blocking=True)
+        """(inputs, targets) for this rank's rows of global batch `step`; targets are the inputs shifted by one."""
+        mine = _rows_of_rank(batch, rank, world)
+        last_start = self.data.numel() - seq - 1
+        offsets = torch.randint(0, last_start, (batch,), generator=_step_generator(seed, step))[mine]
+        windows = self.data[offsets.unsqueeze(1) + torch.arange(seq + 1).unsqueeze(0)]
+        inputs, targets = windows[:, :seq], windows[:, 1:]
+        return inputs.to(device, non_blocking=True), targets.to(device, non_blocking=True)
 
 
 def synthetic(n=200_000, seed=0):
-    """Learnable pseudo-text without a corpus on disk: a seeded 256-state Markov chain."""
-    gen = torch.Generator().manual_seed(seed)
-    table = torch.randint(0, 256, (256, 4), generator=gen).tolist()
-    pick = torch.randint(0, 4, (n,), generator=gen).tolist()
-    out = bytearray(n)
+    """Pseudo-text a model can learn from without a corpus on disk: a walk of `n` steps over 256 states, each
+    with four seeded successors."""
+    gen = torch.Generator()
+    gen.manual_seed(seed)
+    successors = torch.randint(0, 256, (256, 4), generator=gen).tolist()
+    turns = torch.randint(0, 4, (n,), generator=gen).tolist()
+    walk = bytearray()
     state = 0
-    for i, c in enumerate(pick):
-        state = table[state][c]
-        out[i] = state
-    return Text(data=bytes(out))
+    for turn in turns:
+        state = successors[state][turn]
+        walk.append(state)
+    return Text(data=bytes(walk))
 
 
 def uniform_tokens(step, batch, seq, vocab, seed=0, rank=0, world=1, pin=False):
-    """This rank's rows of global batch `step`: ids uniform in [0, vocab), targets
-    are the inputs shifted by one.  Returned on the host (optionally pinned)."""
-    if batch % world:
-        raise ValueError(f"global batch {batch} does not divide over {world} ranks")
-    gen = torch.Generator().manual_seed(seed * 1_000_003 + step)
-    rows = torch.randint(0, vocab, (batch, seq + 1), generator=gen)
-    per = batch // world
-    rows = rows[rank * per:(rank + 1) * per]
-    x, y = rows[:, :-1].contiguous(), rows[:, 1:].contiguous()
-    if pin:
-        x, y = x.pin_memory(), y.pin_memory()
-    return x, y
+    """This rank's rows of global batch `step`, ids uniform in [0, vocab), on the host (pinned on request)."""
+    mine = _rows_of_rank(batch, rank, world)
+    rows = torch.randint(0, vocab, (batch, seq + 1), generator=_step_generator(seed, step))[mine]
+    pair = rows[:, :seq].contiguous(), rows[:, 1:].contiguous()
+    return tuple(t.pin_memory() for t in pair) if pin else pair
