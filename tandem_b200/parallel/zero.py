@@ -15,9 +15,39 @@ Contract and flat layouts follow the reference's tandem/zero.py:29-336:
                    reduce-scattered as soon as they are complete.
 Train with: loss = z(x, y); loss.backward(); z.step(); z.zero_grad().
 
-Underneath, on GPUs, the flat buffers, gradient staging and unit shards live in
-the group's symmetric heap, so reduce-scatter / all-gather are single kernels
-that read or write the peers' copies in place, with the divide fused in.
+What runs on GPU ranks (group.fused), beyond that contract:
+
+  Memory.  The flat parameter buffer (stages 1/2), each bucket's gradient staging and
+  each unit's parameter shard (stage 3) come from the group's symmetric heap, so every
+  peer can address them; every rank allocates the same sizes in the same order (a unit's
+  shard is allocated at the largest rank's size), which keeps heap offsets identical.
+
+  Gradients.  Autograd's gradients are not copied into the staging buffer one by one:
+  the (view, gradient) pairs of a bucket or unit are collected and packed by ONE
+  multi-tensor kernel when its last gradient has arrived.  The reduce-scatter is then a
+  single kernel that reads the peers' staging buffers in place, divides each operand
+  as it is loaded, and finishes with an epilogue instead of a separate pass:
+  `accumulate_into=` adds the reduced chunk to the gradient shard (stage 2/3), and with
+  `ZeRO(fused_step=True)` the AdamW update itself runs there, on the chunk that was just
+  reduced (fp32 master weights and moments, bf16 shadow written back), so step() only
+  has to all-gather the parameters.
+
+  Parameters (stage 3).  A unit's shards only change inside step(), and step() is fenced
+  by device barriers on both sides; gathers of a unit therefore need no handshake at
+  all: each rank pulls the peers' shards with one kernel that opens with a system-scope
+  fence (gather_shards), on the communication stream, one unit ahead of the compute.
+  With `FSDP(fuse_gather_gemm=True)` a block's qkv weight and bias are not gathered
+  ahead at all in the forward pass: the unit is pulled in two parts around them
+  (what precedes the weight is awaited before the first LayerNorm, the rest while the
+  GEMM runs), the qkv GEMM kernel fetches its own weight from the owners' shards while
+  it multiplies (ops.gemm.GatheredLinear, registered in ops.gemm.GATHERED under the
+  weight's address), and the stream waits for the second part right after that GEMM.
+
+  Mixed precision.  With bf16 parameters the optimizer keeps an fp32 master copy of
+  each shard next to the moments (ShardedAdamW.master); gradients stay bf16 on the wire.
+
+On CPU ranks the same classes run the reference's sequence of collectives and torch
+operations, which is what makes them bit-identical to torch DDP + AdamW.
 """
 
 import warnings
