@@ -89,7 +89,7 @@ def optimizer_state(wrapped, opt):
     g = getattr(wrapped, "g", None)
     if isinstance(opt, ShardedAdamW):
         hyper = {"lr": opt.lr, "betas": tuple(opt.betas), "eps": opt.eps, "weight_decay": opt.weight_decay}
-        out = {"kind": "adamw", "hyper": hyper, "step": 0.0, "exp_avg": {}, "exp_avg_sq": {}}
+        out = {"kind": "adamw", "hyper": hyper, "step": 0.0, "exp_avg": {}, "exp_avg_sq": {}, "master": {}}
         names = {id(p): n for n, p in _named(wrapped)}
         layouts = [("flat", wrapped.flat)] if isinstance(wrapped, ZeRO) else [(u.index, u.flat) for u in wrapped.units]
         for key, layout in layouts:
@@ -97,14 +97,16 @@ def optimizer_state(wrapped, opt):
                 continue
             step, m, v = opt.state[key]
             out["step"] = step
-            fm = _gather_flat(g, m, layout.numel, g.size).cpu()
-            fv = _gather_flat(g, v, layout.numel, g.size).cpu()
+            parts = {"exp_avg": _gather_flat(g, m, layout.numel, g.size).cpu(),
+                     "exp_avg_sq": _gather_flat(g, v, layout.numel, g.size).cpu()}
+            if key in opt.master:  # 16-bit parameters: the fp32 master weights are optimizer state too
+                parts["master"] = _gather_flat(g, opt.master[key], layout.numel, g.size).cpu()
             offs = sorted(layout.offset.values()) + [layout.numel]
             for p in layout.params:
                 a = layout.offset[p]
                 b = offs[offs.index(a) + 1]
-                out["exp_avg"][names[id(p)]] = fm[a:b].clone()
-                out["exp_avg_sq"][names[id(p)]] = fv[a:b].clone()
+                for kind, flat in parts.items():
+                    out[kind][names[id(p)]] = flat[a:b].clone()
         return out
     if hasattr(opt, "slots"):  # BucketAdamW: replicated state, bucket-major
         names = {id(p): n for n, p in _named(wrapped)}
@@ -133,17 +135,34 @@ def load_optimizer_state(wrapped, opt, state):
         h = state["hyper"]
         opt.lr, opt.betas, opt.eps, opt.weight_decay = h["lr"], tuple(h["betas"]), h["eps"], h["weight_decay"]
         layouts = [("flat", wrapped.flat, wrapped.buf)] if isinstance(wrapped, ZeRO) else [(u.index, u.flat, u.shard) for u in wrapped.units]
+        saved_master = state.get("master") or {}
         for key, layout, like in layouts:
-            fm = torch.zeros(layout.numel, dtype=torch.float32)
-            fv = torch.zeros(layout.numel, dtype=torch.float32)
+            shard = like[layout.lo:layout.hi] if like.numel() == layout.numel else like  # ZeRO passes the whole buffer
+            sixteen = like.dtype in (torch.bfloat16, torch.float16)
+            wide = torch.float64 if like.dtype == torch.float64 else torch.float32
+            fm = torch.zeros(layout.numel, dtype=wide)
+            fv = torch.zeros(layout.numel, dtype=wide)
+            fw = torch.zeros(layout.numel, dtype=wide) if sixteen else None
+            have_master = sixteen
             for p in layout.params:
                 a = layout.offset[p]
-                m, v = state["exp_avg"][names[id(p)]], state["exp_avg_sq"][names[id(p)]]
+                name = names[id(p)]
+                m, v = state["exp_avg"][name], state["exp_avg_sq"][name]
                 fm[a:a + m.numel()].copy_(m.reshape(-1))
                 fv[a:a + v.numel()].copy_(v.reshape(-1))
-            dev, dt = like.device, like.dtype
-            opt.state[key] = [float(state["step"]), fm[layout.lo:layout.hi].to(dev, dt).clone(),
-                              fv[layout.lo:layout.hi].to(dev, dt).clone()]
+                if sixteen:
+                    if name in saved_master:
+                        fw[a:a + m.numel()].copy_(saved_master[name].reshape(-1))
+                    else:
+                        have_master = False
+            dev = like.device
+            # Moments (and the master copy) of a 16-bit shard stay fp32: the update kernels address them as float.
+            opt.state[key] = [float(state["step"]), fm[layout.lo:layout.hi].to(dev).clone(), fv[layout.lo:layout.hi].to(dev).clone()]
+            if sixteen:
+                # a checkpoint written from fp32 training has no master: start it from the (just loaded) parameters
+                opt.master[key] = fw[layout.lo:layout.hi].to(dev).clone() if have_master else shard.detach().to(wide).clone()
+            else:
+                opt.master.pop(key, None)
         return
     opt.step_count = float(state["step"])
     if hasattr(opt, "_step_dev"):

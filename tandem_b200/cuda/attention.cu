@@ -35,6 +35,7 @@ extern "C" void tb_note_launch(int n);
 namespace {
 
 int g_bwd_two_per_sm = 0;
+int g_fwd_variant = 1;  // 0: two-pass kernel; 1: warp-specialised, P through shared memory; 2: warp-specialised, P in TMEM
 
 using namespace tc;
 
@@ -245,6 +246,267 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict__ 
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ forward, warp-specialised
+// One CTA per PAIR of 128-query tiles of one head, 320 threads in four roles:
+//   warp 0       TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring of tile slots
+//   warp 1       MMA issuer (one thread): S_i = Q_i.K_j^T and O_i += P_i.V_j for the two query tiles i in turn
+//   warps 2-5    softmax of query tile 0: one thread per query row (= TMEM lane)
+//   warps 6-9    softmax of query tile 1
+// Single pass with an online softmax: a row keeps the maximum it is currently scaled by (m_used) and only rescales its
+// accumulator row in TMEM (tcgen05.ld, multiply, tcgen05.st) when a new maximum exceeds it by more than 2^8; otherwise
+// the probabilities simply run up to 256, which fp32 accumulation and bf16 probabilities absorb.  The rescale needs no
+// barrier of its own: S_i(j) is committed after O_i += P.V of step j-1 on the in-order tensor pipe, and the next one is
+// only issued after this row's thread has arrived on p_full.
+// The two tiles alternate on the tensor pipe: while the softmax threads of one tile work on S_i(j) (exponentials), the
+// MMAs of the other tile run.  P goes to the MMA either through shared memory (bf16, swizzled K-major strips) or, with
+// P_TMEM, stays in TMEM over the first 64 columns of S (bf16 pairs) and is the A operand of a TMEM-sourced MMA.
+// TMEM: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+HD)  O_1 [256+HD, 256+2HD).
+template <int HD, bool P_TMEM>
+struct Fwd2Smem {
+  static constexpr int TILE_BYTES = (HD / 64) * STRIP;
+  static constexpr int Q = 0;                                       // two query tiles
+  static constexpr int P = Q + 2 * TILE_BYTES;                      // two P tiles of 2 strips (absent with P_TMEM)
+  static constexpr int RING = P + (P_TMEM ? 0 : 4 * STRIP);
+  static constexpr int BUDGET = 224 * 1024;
+  static constexpr int SLOTS_FIT = (BUDGET - RING) / TILE_BYTES;
+  static constexpr int SLOTS = SLOTS_FIT > 6 ? 6 : SLOTS_FIT;       // K and V tiles in flight
+  static constexpr int BARS = RING + SLOTS * TILE_BYTES;
+  static constexpr int TOTAL = BARS + 256;
+  static_assert(SLOTS >= 3, "the K/V ring needs at least three slots");
+};
+
+template <int HD, bool P_TMEM>
+__global__ void __launch_bounds__(320, 1)
+k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int B, int T, int H,
+              int d, float scale_log2e, int* error) {
+  extern __shared__ __align__(1024) uint8_t fwd2_smem[];
+  uint8_t* smem = fwd2_smem;
+  if (smem_u32(smem) & 1023) {  // the swizzled tiles need 1024-byte alignment; nothing is allocated yet
+    if (threadIdx.x == 0) {
+      *error = 1;
+      __threadfence_system();
+    }
+    return;
+  }
+  using L = Fwd2Smem<HD, P_TMEM>;
+  constexpr int TILE_BYTES = L::TILE_BYTES, SLOTS = L::SLOTS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
+  uint64_t *q_full = bars, *s_full = bars + 2, *p_full = bars + 4, *o_full = bars + 6, *kv_full = bars + 8, *kv_empty = bars + 8 + SLOTS;
+  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 8 + 2 * SLOTS);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // heaviest pairs (most key tiles) first over the whole grid
+  const int n_qt = T / TILE, n_pairs = (n_qt + 1) / 2;
+  const int pair = n_pairs - 1 - (int)blockIdx.x / (H * B);
+  const int rest = (int)blockIdx.x % (H * B);
+  const int h = rest % H, b = rest / H;
+  const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
+  const int n0 = qt0 + 1, n1 = qt1 < n_qt ? qt1 + 1 : 0;  // key tiles each query tile visits
+  const int n_steps = n1 > n0 ? n1 : n0;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);  // one arrival per softmax warp of the tile
+      mbar_init(&o_full[i], 1);
+    }
+    for (int s = 0; s < SLOTS; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tensormap(&map);
+  }
+  if (warp == 1) {
+    tmem_alloc(holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&q_full[0], TILE_BYTES);
+      load_tile<HD>(smem + L::Q, &map, &q_full[0], h * HD, b * T + qt0 * TILE);
+      if (n1) {
+        mbar_expect_tx(&q_full[1], TILE_BYTES);
+        load_tile<HD>(smem + L::Q + TILE_BYTES, &map, &q_full[1], h * HD, b * T + qt1 * TILE);
+      }
+      bool ok = true;
+      for (int ld = 0; ld < 2 * n_steps && ok; ++ld) {  // load 2j: K_j, load 2j+1: V_j
+        const int s = ld % SLOTS, j = ld >> 1, part = ld & 1;
+        if (!(ok = mbar_wait(&kv_empty[s], ((ld / SLOTS) & 1) ^ 1, error))) break;
+        mbar_expect_tx(&kv_full[s], TILE_BYTES);
+        load_tile<HD>(smem + L::RING + s * TILE_BYTES, &map, &kv_full[s], (1 + part) * d + h * HD, b * T + j * TILE);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc(128, 128, false, false);
+      constexpr uint32_t idesc_o = instr_desc(128, HD, false, true);
+      auto slot_of = [&](int ld) { return smem + L::RING + (ld % SLOTS) * TILE_BYTES; };
+      auto wait_slot = [&](int ld) { return mbar_wait(&kv_full[ld % SLOTS], (ld / SLOTS) & 1, error); };
+      auto issue_s = [&](int i, int j) {  // S_i = Q_i . K_j^T
+        mma_kmajor<HD>(tmem + i * 128, smem + L::Q + i * TILE_BYTES, slot_of(2 * j), idesc_s, false);
+        mma_commit(&s_full[i]);
+      };
+      auto issue_pv = [&](int i, int j) {  // O_i (+)= P_i . V_j: eight steps of 16 keys; V is MN-major (head dim contiguous)
+        const uint32_t tO = tmem + 256 + i * HD;
+        const uint32_t v_addr = smem_u32(slot_of(2 * j + 1));
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t v_desc = smem_desc(v_addr + kk * 2048, STRIP, 1024);
+          if (P_TMEM) {
+            mma_bf16_ts(tO, tmem + i * 128 + kk * 8, v_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          } else {
+            const uint8_t* sP = smem + L::P + i * 2 * STRIP;
+            mma_bf16(tO, smem_desc(smem_u32(sP + (kk >> 2) * STRIP) + (kk & 3) * 32, 16, 1024), v_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+      };
+      bool ok = mbar_wait(&q_full[0], 0, error) && (!n1 || mbar_wait(&q_full[1], 0, error)) && wait_slot(0);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        if (n1) issue_s(1, 0);
+        mma_commit(&kv_empty[0]);  // K_0 is free once these have read it
+      }
+      for (int j = 0; j < n_steps && ok; ++j) {
+        if (!(ok = wait_slot(2 * j + 1))) break;                       // V_j
+        if (j + 1 < n_steps && !(ok = wait_slot(2 * j + 2))) break;    // K_{j+1}
+        tc_fence_after();
+        for (int i = 0; i < 2 && ok; ++i) {
+          const int n_i = i == 0 ? n0 : n1;
+          if (j >= n_i) continue;
+          if (!(ok = mbar_wait(&p_full[i], j & 1, error))) break;      // P_i(j) is in place, O_i rescaled if it had to be
+          tc_fence_after();
+          issue_pv(i, j);
+          if (j == n_i - 1) mma_commit(&o_full[i]);
+          else issue_s(i, j + 1);
+        }
+        if (!ok) break;
+        mma_commit(&kv_empty[(2 * j + 1) % SLOTS]);                    // V_j
+        if (j + 1 < n_steps) mma_commit(&kv_empty[(2 * j + 2) % SLOTS]);  // K_{j+1}
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax (warps 2-5: tile 0, warps 6-9: tile 1)
+    const int i = (warp - 2) >> 2;
+    const int n_i = i == 0 ? n0 : n1;
+    const int qt = i == 0 ? qt0 : qt1;
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                      // query row within the tile = TMEM lane
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + i * 128 + lane_base;
+    const uint32_t tO = tmem + 256 + i * HD + lane_base;
+    uint8_t* sP = smem + L::P + i * 2 * STRIP;
+    float m_used = -INFINITY, l = 0.f;  // m_used in raw score units
+    bool ok = true;
+    for (int j = 0; j < n_i && ok; ++j) {
+      if (!(ok = mbar_wait_warp_spin(&s_full[i], j & 1, error))) break;
+      tc_fence_after();
+      uint32_t raw[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, raw[c]);
+      tmem_ld_wait();
+      float mx = -INFINITY;
+      if (j == qt) {  // the diagonal tile: keys beyond the query are masked
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c * 32 + e > r) raw[c][e] = 0xff800000u;  // -inf
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(raw[c][e]));
+      if (j == 0) {
+        m_used = mx;
+      } else {
+        const bool need = (mx - m_used) * scale_log2e > 8.f;
+        if (__any_sync(0xffffffffu, need)) {  // rare after the first tiles: rescale this warp's accumulator rows
+          const float f = need ? ex2_approx((m_used - mx) * scale_log2e) : 1.f;
+          if (need) m_used = mx;
+          l *= f;
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+            tmem_st32(tO + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float mc = m_used * scale_log2e;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {  // 64 keys at a time: 32 registers of bf16 pairs
+        uint32_t pk[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int col = hh * 64 + 2 * e;
+          const float p0 = ex2_approx(fmaf(__uint_as_float(raw[col >> 5][col & 31]), scale_log2e, -mc));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(raw[(col + 1) >> 5][(col + 1) & 31]), scale_log2e, -mc));
+          sum0 += p0;
+          sum1 += p1;
+          const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+          pk[e] = *reinterpret_cast<const uint32_t*>(&pp);
+        }
+        if (P_TMEM) {
+          tmem_st32(tS + hh * 32, pk);  // P over the first 64 columns of S: keys 2c, 2c+1 in column c
+        } else {
+          uint8_t* strip = sP + hh * STRIP;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) *reinterpret_cast<uint4*>(strip + swz(r, v)) = *reinterpret_cast<const uint4*>(&pk[4 * v]);
+        }
+      }
+      l += sum0 + sum1;
+      if (P_TMEM) tmem_st_wait();
+      else fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[i]);
+    }
+    if (ok && n_i > 0) ok = mbar_wait_warp_spin(&o_full[i], 0, error);
+    if (ok && n_i > 0) {
+      tc_fence_after();
+      const float inv_l = 1.f / l;
+      const int q_idx = qt * TILE + r;
+      __nv_bfloat16* o_row = out + (size_t)(b * T + q_idx) * d + h * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tO + c * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          __nv_bfloat162 y[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            y[e] = __floats2bfloat162_rn(__uint_as_float(o[v * 8 + 2 * e]) * inv_l, __uint_as_float(o[v * 8 + 2 * e + 1]) * inv_l);
+          *reinterpret_cast<uint4*>(o_row + c * 32 + v * 8) = *reinterpret_cast<const uint4*>(y);
+        }
+      }
+      lse[((size_t)b * H + h) * T + q_idx] = (m_used * scale_log2e + log2f(l)) * 0.69314718055994530942f;  // natural log
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -732,6 +994,26 @@ int tb_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int
   const float scale_log2e = 1.4426950408889634f / sqrtf((float)HD);
   dim3 grid(T / TILE, H, B);
   tb_note_launch(1);
+  if (g_fwd_variant > 0) {
+    const int n_pairs = (T / TILE + 1) / 2;
+    const unsigned ctas = (unsigned)(n_pairs * H * B);
+#define LAUNCH_WS(HD_, PT_) \
+  do { \
+    static bool once = false; \
+    if (!once) { \
+      cudaError_t e = cudaFuncSetAttribute(k_attn_fwd_ws<HD_, PT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<HD_, PT_>::TOTAL); \
+      if (e != cudaSuccess) return (int)e; \
+      once = true; \
+    } \
+    k_attn_fwd_ws<HD_, PT_><<<ctas, 320, Fwd2Smem<HD_, PT_>::TOTAL, stream>>>(map, (__nv_bfloat16*)out, lse, B, T, H, d, scale_log2e, g_err_dev); \
+  } while (0)
+    if (HD == 64 && g_fwd_variant == 1) LAUNCH_WS(64, false);
+    else if (HD == 64) LAUNCH_WS(64, true);
+    else if (g_fwd_variant == 1) LAUNCH_WS(128, false);
+    else LAUNCH_WS(128, true);
+#undef LAUNCH_WS
+    return (int)cudaGetLastError();
+  }
   if (HD == 64) {
     static bool once = false;
     if (!once) {
@@ -747,6 +1029,8 @@ int tb_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int
   }
   return (int)cudaGetLastError();
 }
+
+void tb_attn_fwd_variant(int v) { g_fwd_variant = v; }
 
 // 1: the HD = 64 backward runs as k_attn_bwd64 (two CTAs per SM); 0: as k_attn_bwd<64>.  For measurements.
 void tb_attn_bwd_variant(int two_per_sm) { g_bwd_two_per_sm = two_per_sm; }

@@ -23,6 +23,8 @@ def _fns():
     L.tb_attn_bwd.restype = i
     L.tb_attn_bwd_variant.argtypes = [i]
     L.tb_attn_bwd_variant.restype = None
+    L.tb_attn_fwd_variant.argtypes = [i]
+    L.tb_attn_fwd_variant.restype = None
     L.tb_attn_error.argtypes = []
     L.tb_attn_error.restype = i
     return L
@@ -73,3 +75,8 @@ def attention_error():
 def backward_variant(two_per_sm):
     """HD = 64 backward: True runs the kernel shaped for two CTAs per SM, False the one-CTA-per-SM kernel."""
     _fns().tb_attn_bwd_variant(int(bool(two_per_sm)))
+
+
+def forward_variant(which):
+    """0: the two-pass kernel; 1: warp-specialised single pass, P through shared memory; 2: the same with P kept in TMEM."""
+    _fns().tb_attn_fwd_variant(int(which))

@@ -39,6 +39,15 @@ class AdamArgs(ctypes.Structure):
 
     @classmethod
     def make(cls, param, exp_avg, exp_avg_sq, scalars, do_decay, shadow=None):
+        # The kernel addresses param / exp_avg / exp_avg_sq as float and shadow as bf16: anything else would make it
+        # read and write past the arrays.
+        for name, t in (("param", param), ("exp_avg", exp_avg), ("exp_avg_sq", exp_avg_sq)):
+            if t.dtype != torch.float32:
+                raise TypeError(f"AdamArgs: {name} must be float32 (got {t.dtype}); 16-bit shards are stepped through their fp32 master")
+        if shadow is not None and shadow.dtype != torch.bfloat16:
+            raise TypeError(f"AdamArgs: shadow must be bfloat16 (got {shadow.dtype})")
+        if not (param.numel() == exp_avg.numel() == exp_avg_sq.numel()) or (shadow is not None and shadow.numel() != param.numel()):
+            raise ValueError("AdamArgs: param, moments and shadow must have the same number of elements")
         decay, w1, b2, w2, bias2_sqrt, eps, neg_step = scalars
         inv = float(np.float32(1.0) / np.float32(bias2_sqrt))
         return cls(param.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(),
