@@ -34,5 +34,7 @@ struct AdamArgs {
   float* exp_avg_sq;
   __nv_bfloat16* shadow;  // optional bf16 copy of the updated parameter
   AdamScalars s;          // s.inv_bias2_sqrt is filled in by the host wrapper
+  const AdamScalars* s_dev;  // if not null: the scalars are read from device memory when the kernel starts (written by
+                             // k_adam_prepare), so a launch recorded in a CUDA graph sees each replay's step
 };
 

@@ -326,7 +326,8 @@ k_reduce_scatter(CommCtx c, PeerPtrs buf, Locals lin, long long numel, Bounds bo
   const long long nth = (long long)gridDim.x * blockDim.x;
   const char* local_in = lin.p[blockIdx.y];
   T* acc_out = reinterpret_cast<T*>(acc.p[blockIdx.y]);
-  const AdamArgs& adam = adams.a[blockIdx.y];
+  AdamArgs adam = adams.a[blockIdx.y];
+  if (EPI == 2 && adam.s_dev != nullptr) adam.s = *adam.s_dev;
   const long long lo = bounds.off[rank], hi = bounds.off[rank + 1];
   if (local_in != nullptr) {
     local_copy<T>(buf.p[rank], local_in, numel, smode, sval);

@@ -1,41 +1,95 @@
-"""Data parallelism with bucketed, overlapped gradient averaging.
+"""Data parallelism over gradient arenas.
 
-Same contract as the reference's tandem/ddp.py:35-129 (and torch's DDP): every
-rank starts from rank 0's weights; gradients are views into flat buckets of
-about `bucket_bytes`; a bucket's all-reduce (op="avg": divide, then sum) is
-submitted as soon as its last gradient is produced, buckets are submitted
-strictly in index order so all ranks issue the same sequence, and after the
-first backward the buckets are rebuilt in the order gradients really arrived.
-`no_sync()` accumulates locally.
+What a user sees is the contract of the reference's tandem/ddp.py:35-129 (and of
+torch's DDP): every rank starts from rank 0's weights, gradients are averaged
+bucket by bucket while backward is still running (op="avg": divide, then sum),
+every rank issues the same sequence of collectives, the bucket order follows the
+order in which gradients really arrive, `no_sync()` accumulates locally, and a
+parameter that received no gradient is an error.
 
-What is different underneath on GPUs: bucket storage comes from the group's
-symmetric heap, so the all-reduce kernel reads the peers' buckets in place over
-NVLink with the divide fused into its loads (no staging copy, no separate div_
-kernel), on a high-priority stream while backward continues; the initial
-broadcast is one transfer per dtype instead of one per parameter; and gradients
-that autograd produced outside a bucket are packed by one multi-tensor kernel
-per bucket instead of one copy per parameter.
+How it is laid out here.  All gradients of one dtype live in ONE allocation, the
+arena, taken once from the group's symmetric heap (peer-mapped on GPU ranks).  A
+bucket ("span") is nothing but a slice [lo, hi) of its arena plus the parameters
+whose gradient slots fall inside it, so its collective runs in place on memory
+every peer can already address: no staging copy, no second buffer, and the
+divide is fused into the kernel's loads.  Learning the arrival order re-plans
+the offsets INSIDE the arena (one temporary snapshot carries the gradients over);
+nothing is allocated or released on the heap after construction.
+
+Spans are reduced through a pluggable reducer.  The default averages a span with
+one all-reduce.  `ShardedBucketAdamW` replaces it with reduce-scatter + AdamW on
+the freshly reduced chunk (inside the reduce-scatter kernel on GPUs) + all-gather
+of the updated parameters: the same NVLink bytes as the all-reduce, 1/n of the
+optimizer's memory traffic and state, identical values.
 """
 
+import collections
 import contextlib
 
 import torch
 from torch.autograd import Variable
 
 
-class Bucket:
-    def __init__(self, params, group):
-        self.params = params
+class Span:
+    """A slice of an arena that one collective reduces: the unit of overlap."""
+
+    __slots__ = ("arena", "lo", "hi", "params", "slot", "missing", "stray", "flight")
+
+    def __init__(self, arena, lo, hi, params):
+        self.arena, self.lo, self.hi, self.params = arena, lo, hi, params
+        self.slot = {p: arena.slot_of(p) for p in params}  # parameter -> its gradient's home, shaped like the parameter
+        self.missing = len(params)  # gradients of this backward still to come
+        self.stray = []             # parameters whose fresh gradient autograd left outside its slot
+        self.flight = None          # the collective in flight, if any
+
+    @property
+    def flat(self):
+        return self.arena.flat[self.lo:self.hi]
+
+    def rearm(self):
+        self.missing, self.stray, self.flight = len(self.params), [], None
+
+
+class GradArena:
+    """Every gradient of one (dtype, device) in one flat allocation; `where[p]` is p's offset."""
+
+    def __init__(self, group, params):
         first = params[0]
-        total = sum(p.numel() for p in params)
-        self.flat = group.empty(total, first.dtype, first.device)
-        self.views, at = {}, 0
-        for p in params:
-            self.views[p] = self.flat[at:at + p.numel()].view_as(p)
+        self.params = list(params)
+        self.flat = group.empty(sum(p.numel() for p in params), first.dtype, first.device)
+        self.where = {}
+
+    def place(self, order):
+        """Assigns offsets in the given order (a permutation of this arena's parameters)."""
+        at = 0
+        for p in order:
+            self.where[p] = at
             at += p.numel()
-        self.ready = 0
-        self.work = None
-        self.loose = []  # parameters whose fresh gradient still sits outside the bucket
+
+    def slot_of(self, p):
+        a = self.where[p]
+        return self.flat[a:a + p.numel()].view_as(p)
+
+    def snapshot(self):
+        """(copy of the gradients, copy of the offsets): what carry_over() needs after a re-plan."""
+        return self.flat.clone(), dict(self.where)
+
+    def carry_over(self, snapshot):
+        """After place() with a new order: moves every gradient from its old offset to its new one."""
+        old_flat, old_where = snapshot
+        for p in self.params:
+            n = p.numel()
+            self.flat[self.where[p]:self.where[p] + n].copy_(old_flat[old_where[p]:old_where[p] + n])
+
+
+class AllReduceSpans:
+    """Default reducer: one averaging all-reduce per span, in place on the arena."""
+
+    def __init__(self, group):
+        self.g = group
+
+    def __call__(self, span):
+        return self.g.all_reduce(span.flat, op="avg", async_op=True)
 
 
 class DDP(torch.nn.Module):
@@ -45,145 +99,190 @@ class DDP(torch.nn.Module):
         self.g = group
         self.bucket_bytes = bucket_bytes
         self.overlap = overlap
-        self._rebuild = rebuild
         self.params = [p for p in module.parameters() if p.requires_grad]
-        self._broadcast_initial()
-        # Until a backward shows the real order, assume reverse registration order.
-        self._make_buckets(list(reversed(self.params)))
-        self._sync = True
-        self._order = []
-        self._queued = False
+        self._share_initial_weights()
+        self.arenas = {}
         for p in self.params:
-            p.register_post_accumulate_grad_hook(self._on_grad)
+            self.arenas.setdefault((p.dtype, p.device), []).append(p)
+        self.arenas = {key: GradArena(group, ps) for key, ps in self.arenas.items()}
+        # Until a backward shows the real order, expect gradients in reverse registration order.
+        self._plan(list(reversed(self.params)))
+        self.reducer = AllReduceSpans(group)
+        self._reducing = True            # False inside no_sync()
+        self._learning = bool(rebuild)   # still recording the arrival order of the first reduced backward
+        self._seen = []
+        self._drain_armed = False
+        for p in self.params:
+            p.register_post_accumulate_grad_hook(self._arrived)
 
+    # ------------------------------------------------------------------ set-up
     @torch.no_grad()
-    def _broadcast_initial(self):
-        """Rank 0's weights to everyone, one flat transfer per dtype."""
-        by_dtype = {}
+    def _share_initial_weights(self):
+        """Rank 0's weights to everyone: one flat transfer per dtype instead of one per parameter."""
+        groups = {}
         for p in self.params:
-            by_dtype.setdefault((p.dtype, p.device), []).append(p)
-        for ps in by_dtype.values():
-            flat = torch.cat([p.detach().reshape(-1) for p in ps])
-            self.g.broadcast(flat, root=0)
+            groups.setdefault((p.dtype, p.device), []).append(p)
+        for ps in groups.values():
+            packed = torch.cat([p.detach().reshape(-1) for p in ps])
+            self.g.broadcast(packed, root=0)
             at = 0
             for p in ps:
-                p.copy_(flat[at:at + p.numel()].view_as(p))
+                p.copy_(packed[at:at + p.numel()].view_as(p))
                 at += p.numel()
 
-    def _make_buckets(self, order):
-        self.buckets, self.bucket_of = [], {}
-        current, size = [], 0
+    def _plan(self, order):
+        """Cuts `order` into spans of about bucket_bytes (a span never mixes dtypes) and places every
+        arena's parameters in that order, so each span is one contiguous slice."""
+        for key, arena in self.arenas.items():
+            arena.place([p for p in order if (p.dtype, p.device) == key])
+        self.buckets, self._span_of = [], {}
+        run, size = [], 0
+
+        def close():
+            arena = self.arenas[(run[0].dtype, run[0].device)]
+            lo = arena.where[run[0]]
+            span = Span(arena, lo, lo + sum(p.numel() for p in run), list(run))
+            self.buckets.append(span)
+            for p in run:
+                self._span_of[p] = span
+
         for p in order:
             nbytes = p.numel() * p.element_size()
-            if current and (size + nbytes > self.bucket_bytes or p.dtype != current[0].dtype):
-                self._close_bucket(current)
-                current, size = [], 0
-            current.append(p)
+            if run and (size + nbytes > self.bucket_bytes or (p.dtype, p.device) != (run[0].dtype, run[0].device)):
+                close()
+                run, size = [], 0
+            run.append(p)
             size += nbytes
-        if current:
-            self._close_bucket(current)
-        self._next = 0
+        if run:
+            close()
+        self._queue = collections.deque(self.buckets)
 
-    def _close_bucket(self, params):
-        b = Bucket(params, self.g)
-        for p in params:
-            self.bucket_of[p] = b
-        self.buckets.append(b)
+    @property
+    def rebuilding(self):
+        """True until the span layout is final (optimizers that mirror the layout wait for that)."""
+        return self._learning
 
+    # ------------------------------------------------------------------ the wrapper's surface
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
 
     @contextlib.contextmanager
     def no_sync(self):
         """Backward passes inside only accumulate; the next one outside reduces the sum."""
-        before, self._sync = self._sync, False
+        was, self._reducing = self._reducing, False
         try:
             yield
         finally:
-            self._sync = before
+            self._reducing = was
 
     def zero_grad(self):
-        """Zeroes the buckets and keeps every .grad a bucket view, so the next
-        backward accumulates straight into the buckets (no pack step).
-        `optimizer.zero_grad()` (set_to_none) works too: the hook then moves each
-        fresh gradient into its bucket."""
-        for b in self.buckets:
-            b.flat.zero_()
-            for p in b.params:
-                p.grad = b.views[p]
+        """Zeroes the arenas and points every .grad at its slot, so the next backward accumulates
+        straight into the arena (no pack step).  `optimizer.zero_grad()` (set_to_none) works too:
+        fresh gradients are then moved into their slots span by span."""
+        for arena in self.arenas.values():
+            arena.flat.zero_()
+        for span in self.buckets:
+            for p in span.params:
+                p.grad = span.slot[p]
 
-    def _pack(self, b):
-        """Moves gradients that autograd left outside the bucket into it."""
-        if not b.loose:
+    # ------------------------------------------------------------------ backward
+    def _settle(self, span):
+        """Moves the span's stray gradients into their slots: one multi-tensor copy on a GPU
+        (the reference copies parameter by parameter: tandem/ddp.py:92-94)."""
+        if not span.stray:
             return
         from ..ops import pack_into
 
-        pack_into(b.flat, [(b.views[p], p.grad) for p in b.loose])
-        for p in b.loose:
-            p.grad = b.views[p]
-        b.loose = []
+        pack_into(span.flat, [(span.slot[p], p.grad) for p in span.stray])
+        for p in span.stray:
+            p.grad = span.slot[p]
+        span.stray = []
 
-    def _on_grad(self, p):
-        b = self.bucket_of[p]
-        if p.grad is not b.views[p]:
-            b.loose.append(p)
-            if not p.grad.is_cuda or not self._sync:
-                self._pack(b)  # CPU, or accumulating: the view must hold the sum before the next backward
-        if not self._sync:
+    def _arrived(self, p):
+        span = self._span_of[p]
+        if p.grad.data_ptr() != span.slot[p].data_ptr():
+            span.stray.append(p)
+            if not p.grad.is_cuda or not self._reducing:
+                self._settle(span)  # CPU, or accumulating: the slot must hold the sum before the next backward
+        if not self._reducing:
             return
-        if not self._queued:
-            self._queued = True
-            Variable._execution_engine.queue_callback(self._finish_backward)
-        if self._rebuild:
-            self._order.append(p)
-        b.ready += 1
-        while self._next < len(self.buckets) and self.buckets[self._next].ready == len(self.buckets[self._next].params):
-            nb = self.buckets[self._next]
-            self._pack(nb)
-            nb.work = self.g.all_reduce(nb.flat, op="avg", async_op=True)
+        if not self._drain_armed:
+            self._drain_armed = True
+            Variable._execution_engine.queue_callback(self._drain)
+        if self._learning:
+            self._seen.append(p)
+        span.missing -= 1
+        # Spans go out strictly in plan order, whichever fills first: all ranks issue the same sequence.
+        while self._queue and self._queue[0].missing == 0:
+            head = self._queue.popleft()
+            self._settle(head)
+            head.flight = self.reducer(head)
             if not self.overlap:
-                nb.work.wait()
-            self._next += 1
+                head.flight.wait()
 
-    def _finish_backward(self):
-        self._queued = False
-        missing = [b for b in self.buckets if b.ready != len(b.params)]
-        if missing:
-            for b in self.buckets:
-                b.ready, b.work, b.loose = 0, None, []
-            self._next, self._order = 0, []
-            shapes = [tuple(p.shape) for b in missing for p in b.params if p.grad is None]
+    def _drain(self):
+        """End of backward: every span's collective has been issued (or something is missing)."""
+        self._drain_armed = False
+        starved = [s for s in self.buckets if s.missing]
+        if starved:
+            shapes = [tuple(p.shape) for s in starved for p in s.params if p.grad is None]
+            for s in self.buckets:
+                s.rearm()
+            self._queue = collections.deque(self.buckets)
+            self._seen = []
             raise RuntimeError(f"tandem_b200 DDP: some parameters received no gradient ({shapes[:3]}...); "
                                "every parameter must be used in the forward pass")
-        for b in self.buckets:
-            b.work.wait()
-            b.ready, b.work = 0, None
-        self._next = 0
-        if self._rebuild and len(self._order) == len(self.params):
-            order, self._order, self._rebuild = self._order, [], False
-            grads = {p: p.grad.detach().clone() for p in self.params}
-            self._make_buckets(order)
-            for p in self.params:
-                view = self.bucket_of[p].views[p]
-                view.copy_(grads[p])
-                p.grad = view
-        else:
-            self._order = []
+        for s in self.buckets:
+            s.flight.wait()
+            s.rearm()
+        self._queue = collections.deque(self.buckets)
+        seen, self._seen = self._seen, []
+        if self._learning and len(seen) == len(self.params):
+            self._learning = False
+            self._adopt_order(seen)
+
+    @torch.no_grad()
+    def _adopt_order(self, order):
+        """The spans, re-cut in the order gradients really arrived; gradients move with their slots."""
+        kept = {key: arena.snapshot() for key, arena in self.arenas.items()}
+        self._plan(order)
+        for key, arena in self.arenas.items():
+            arena.carry_over(kept[key])
+        for span in self.buckets:
+            for p in span.params:
+                p.grad = span.slot[p]
+
+
+def _mirror_parameters(ddp, symmetric):
+    """Re-lays the parameters as views of one flat buffer per arena, at their gradients' offsets, so a span's
+    parameters, gradients and optimizer state are parallel slices.  Returns {arena: flat parameter buffer}."""
+    if ddp.rebuilding:
+        raise RuntimeError("the span layout is not final yet: create the optimizer after the first backward or pass "
+                           "rebuild=False to DDP")
+    out = {}
+    with torch.no_grad():
+        for arena in ddp.arenas.values():
+            first = arena.params[0]
+            n = arena.flat.numel()
+            flat = ddp.g.empty(n, first.dtype, first.device) if symmetric else torch.empty(n, dtype=first.dtype, device=first.device)
+            for p in arena.params:
+                view = flat[arena.where[p]:arena.where[p] + p.numel()].view_as(p)
+                view.copy_(p)
+                p.data = view
+            out[arena] = flat
+    return out
 
 
 class BucketAdamW:
-    """AdamW over a DDP wrapper's buckets: one fused kernel per bucket.
+    """AdamW over a DDP wrapper's spans, replicated on every rank: one fused kernel per span.
 
-    Parameters are re-laid as views of one flat buffer per bucket, in the
-    bucket's gradient order, so a bucket's {parameters, gradients, moments} are
-    four parallel flat arrays and a step is `len(buckets)` launches instead of
-    nine ATen kernels per parameter (torch.optim.AdamW(foreach=False), which the
-    reference pairs with its DDP: bench/run.py:102).  With 16-bit parameters the
-    optimizer keeps fp32 master weights and moments and writes the 16-bit
-    parameters back as a shadow copy in the same kernel.
+    A span's {parameters, gradients, moments} are four parallel flat slices, so a step is `len(buckets)`
+    launches instead of nine ATen kernels per parameter (torch.optim.AdamW(foreach=False), which the
+    reference pairs with its DDP: bench/run.py:102).  With 16-bit parameters the optimizer keeps fp32
+    master weights and moments and writes the 16-bit parameters back in the same kernel.  On CPU ranks
+    it runs torch's operation sequence, so results equal torch's per-parameter AdamW bit for bit.
 
-    Create it once the buckets are final: pass rebuild=False to DDP, or create it
-    after the first backward.
+    Create it once the span layout is final: pass rebuild=False to DDP, or create it after the first backward.
     """
 
     def __init__(self, ddp, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2):
@@ -192,20 +291,12 @@ class BucketAdamW:
         self.ddp = ddp
         self.rule = ShardedAdamW(lr, betas, eps, weight_decay)
         self.step_count = 0.0
+        flats = _mirror_parameters(ddp, symmetric=False)
         self.slots = []
-        with torch.no_grad():
-            for b in ddp.buckets:
-                first = b.params[0]
-                flat = torch.empty(b.flat.numel(), dtype=first.dtype, device=first.device)
-                at = 0
-                for p in b.params:
-                    view = flat[at:at + p.numel()].view_as(p)
-                    view.copy_(p)
-                    p.data = view
-                    at += p.numel()
-                master = flat if first.dtype == torch.float32 else flat.float()
-                self.slots.append({"bucket": b, "flat": flat, "master": master, "m": torch.zeros_like(master),
-                                   "v": torch.zeros_like(master)})
+        for span in ddp.buckets:
+            flat = flats[span.arena][span.lo:span.hi]
+            master = flat if flat.dtype == torch.float32 else flat.float()
+            self.slots.append({"bucket": span, "flat": flat, "master": master, "m": torch.zeros_like(master), "v": torch.zeros_like(master)})
         dev = ddp.params[0].device
         if dev.type == "cuda":  # step counter and per-step constants live on the device: the step is graph-capturable
             self._step_dev = torch.zeros(1, dtype=torch.float64, device=dev)
@@ -213,28 +304,104 @@ class BucketAdamW:
 
     @torch.no_grad()
     def step(self):
-        from ..ops import fused_adamw
-
-        if self.ddp._rebuild:
-            raise RuntimeError("the buckets are not final yet: create BucketAdamW after the first backward or use rebuild=False")
         self.step_count += 1.0
-        sc = self.rule.scalars(self.step_count)
-        on_gpu = self.slots[0]["bucket"].flat.is_cuda
+        on_gpu = self.slots[0]["flat"].is_cuda
         if on_gpu:
             from ..ops.elementwise import adam_prepare, adamw_step_dev
 
             adam_prepare(self._step_dev, (self.rule.lr, self.rule.betas, self.rule.eps, self.rule.weight_decay), self._scalars_dev)
         for s in self.slots:
-            b = s["bucket"]
+            grad = s["bucket"].flat
             shadow = None if s["master"] is s["flat"] else s["flat"]
             if on_gpu:
-                adamw_step_dev(s["master"], b.flat, s["m"], s["v"], self._scalars_dev, shadow)
+                adamw_step_dev(s["master"], grad, s["m"], s["v"], self._scalars_dev, shadow)
             else:
                 self.rule.state["b"] = [self.step_count - 1.0, s["m"], s["v"]]
-                self.rule.update("b", s["master"], b.flat.float(), shadow)
+                self.rule.update("b", s["master"], grad.float(), shadow)
 
     def zero_grad(self):
         self.ddp.zero_grad()
+
+    def state_bytes(self):
+        return sum(s[k].numel() * s[k].element_size() for s in self.slots for k in ("m", "v"))
+
+
+class ShardedBucketAdamW:
+    """AdamW for a DDP wrapper with the update sharded over the ranks, span by span, during backward.
+
+    Rank r owns chunk r (torch.tensor_split) of every span: it keeps fp32 master weights and moments for
+    that chunk only.  The wrapper's reducer becomes: reduce-scatter the span's gradients (average), apply
+    AdamW to the owned chunk -- inside the reduce-scatter kernel on GPU ranks, on the values it has just
+    reduced -- and all-gather the span's updated parameters.  The bytes on the wire equal the all-reduce's;
+    the optimizer reads and writes 1/n of what a replicated step does, and every rank ends with the same
+    parameters as `BucketAdamW` produces.  By the time backward returns the new parameters are in
+    place; `step()` only advances the step counter (and prepares the next step's bias corrections on the
+    device), so the whole step stays capturable as a CUDA graph.
+
+    Not compatible with accumulating gradients over several backward passes that each reduce (use
+    `no_sync()` for all but the last, as with any DDP).
+    """
+
+    def __init__(self, ddp, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2):
+        from .optim import ShardedAdamW
+        from .zero import split_sizes
+
+        self.ddp, self.g = ddp, ddp.g
+        self.rule = ShardedAdamW(lr, betas, eps, weight_decay)
+        self.step_count = 0.0
+        flats = _mirror_parameters(ddp, symmetric=True)
+        n, r = self.g.size, self.g.rank
+        self.slots = []
+        for span in ddp.buckets:
+            flat = flats[span.arena][span.lo:span.hi]
+            sizes = split_sizes(span.hi - span.lo, n)
+            lo = sum(sizes[:r])
+            mine = flat[lo:lo + sizes[r]]
+            master = mine if mine.dtype == torch.float32 else mine.float()  # fp32 parameters are their own master
+            self.slots.append({"bucket": span, "flat": flat, "sizes": sizes, "lo": lo, "master": master,
+                               "m": torch.zeros_like(master), "v": torch.zeros_like(master)})
+        self._slot_of = {id(s["bucket"]): s for s in self.slots}
+        dev = ddp.params[0].device
+        kinds = {p.dtype for p in ddp.params}
+        self._fused = bool(dev.type == "cuda" and getattr(self.g, "fused", False) and kinds <= {torch.float32, torch.bfloat16})
+        if self._fused:
+            from ..ops.elementwise import adam_prepare
+
+            self._step_dev = torch.zeros(1, dtype=torch.float64, device=dev)
+            self._scalars_dev = torch.zeros(8, dtype=torch.float32, device=dev)
+            self._prepare = lambda: adam_prepare(self._step_dev, (lr, betas, eps, weight_decay), self._scalars_dev)
+            self._prepare()  # the constants of step 1
+        ddp.reducer = self._reduce_update_gather
+
+    def _reduce_update_gather(self, span):
+        s = self._slot_of[id(span)]
+        count = s["sizes"][self.g.rank]
+        own = s["flat"][s["lo"]:s["lo"] + count]
+        if self._fused:
+            from .symm import AdamArgs
+
+            shadow = own if own.dtype == torch.bfloat16 else None  # fp32: the kernel updates the parameter chunk in place
+            args = AdamArgs.on_device(s["master"], s["m"], s["v"], self._scalars_dev, shadow)
+            self.g.reduce_scatter(span.flat, s["sizes"], op="avg", async_op=True, adam=args)
+        else:
+            mine = self.g.reduce_scatter(span.flat, s["sizes"], op="avg")
+            if count:
+                self.rule.state["s"] = [self.step_count, s["m"], s["v"]]
+                self.rule.update("s", s["master"], mine.to(s["master"].dtype))
+                if s["master"].data_ptr() != own.data_ptr():
+                    own.copy_(s["master"])
+        return self.g.all_gather(s["flat"], s["sizes"], async_op=True)
+
+    @torch.no_grad()
+    def step(self):
+        """The update ran during backward; this closes the step."""
+        self.step_count += 1.0
+        if self._fused:
+            self._prepare()  # bias corrections of the next step, computed on the device
+
+    def zero_grad(self):
+        for p in self.ddp.params:
+            p.grad = None
 
     def state_bytes(self):
         return sum(s[k].numel() * s[k].element_size() for s in self.slots for k in ("m", "v"))

@@ -35,10 +35,10 @@ class AdamArgs(ctypes.Structure):
     _fields_ = [("param", ctypes.c_void_p), ("exp_avg", ctypes.c_void_p), ("exp_avg_sq", ctypes.c_void_p),
                 ("shadow", ctypes.c_void_p), ("decay", ctypes.c_float), ("w1", ctypes.c_float), ("b2", ctypes.c_float),
                 ("w2", ctypes.c_float), ("inv_bias2_sqrt", ctypes.c_float), ("eps", ctypes.c_float),
-                ("neg_step", ctypes.c_float), ("do_decay", ctypes.c_int)]
+                ("neg_step", ctypes.c_float), ("do_decay", ctypes.c_int), ("scalars_dev", ctypes.c_void_p)]
 
-    @classmethod
-    def make(cls, param, exp_avg, exp_avg_sq, scalars, do_decay, shadow=None):
+    @staticmethod
+    def _check(param, exp_avg, exp_avg_sq, shadow):
         # The kernel addresses param / exp_avg / exp_avg_sq as float and shadow as bf16: anything else would make it
         # read and write past the arrays.
         for name, t in (("param", param), ("exp_avg", exp_avg), ("exp_avg_sq", exp_avg_sq)):
@@ -48,10 +48,24 @@ class AdamArgs(ctypes.Structure):
             raise TypeError(f"AdamArgs: shadow must be bfloat16 (got {shadow.dtype})")
         if not (param.numel() == exp_avg.numel() == exp_avg_sq.numel()) or (shadow is not None and shadow.numel() != param.numel()):
             raise ValueError("AdamArgs: param, moments and shadow must have the same number of elements")
+
+    @classmethod
+    def on_device(cls, param, exp_avg, exp_avg_sq, scalars_dev, shadow=None):
+        """The step's constants are read by the kernel from `scalars_dev` (eight floats written on the device by
+        ops.elementwise.adam_prepare) instead of being baked into the launch: for steps replayed as a CUDA graph."""
+        cls._check(param, exp_avg, exp_avg_sq, shadow)
+        if scalars_dev.dtype != torch.float32 or scalars_dev.numel() < 8 or not scalars_dev.is_cuda:
+            raise TypeError("AdamArgs.on_device: scalars_dev must be a CUDA float32 tensor of 8 elements")
+        return cls(param.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), shadow.data_ptr() if shadow is not None else None,
+                   0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0, scalars_dev.data_ptr())
+
+    @classmethod
+    def make(cls, param, exp_avg, exp_avg_sq, scalars, do_decay, shadow=None):
+        cls._check(param, exp_avg, exp_avg_sq, shadow)
         decay, w1, b2, w2, bias2_sqrt, eps, neg_step = scalars
         inv = float(np.float32(1.0) / np.float32(bias2_sqrt))
         return cls(param.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(),
-                   shadow.data_ptr() if shadow is not None else None, decay, w1, b2, w2, inv, eps, neg_step, int(do_decay))
+                   shadow.data_ptr() if shadow is not None else None, decay, w1, b2, w2, inv, eps, neg_step, int(do_decay), None)
 
 
 @functools.cache
