@@ -35,6 +35,7 @@ extern "C" void tb_note_launch(int n);
 namespace {
 
 int g_bwd_two_per_sm = 0;
+int g_bwd_variant = 1;  // 0: one kernel with fp32 atomics for dQ; 1: the two warp-specialised kernels
 int g_fwd_variant = 1;  // 0: two-pass kernel; 1: warp-specialised, P through shared memory; 2: warp-specialised, P in TMEM
 
 using namespace tc;
@@ -427,10 +428,17 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
           for (int e = 0; e < 32; ++e)
             if (c * 32 + e > r) raw[c][e] = 0xff800000u;  // -inf
       }
+      {
+        // eight independent running maxima: a single chain of 128 dependent FMNMX would cost ~5 cycles each
+        float part[8];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int e = 0; e < 8; ++e) part[e] = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(raw[c][e]));
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) part[e & 7] = fmaxf(part[e & 7], __uint_as_float(raw[c][e]));
+        mx = fmaxf(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])), fmaxf(fmaxf(part[4], part[5]), fmaxf(part[6], part[7])));
+      }
       if (j == 0) {
         m_used = mx;
       } else {
@@ -452,7 +460,7 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
         }
       }
       const float mc = m_used * scale_log2e;
-      float sum0 = 0.f, sum1 = 0.f;
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {  // 64 keys at a time: 32 registers of bf16 pairs
         uint32_t pk[32];
@@ -461,8 +469,8 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
           const int col = hh * 64 + 2 * e;
           const float p0 = ex2_approx(fmaf(__uint_as_float(raw[col >> 5][col & 31]), scale_log2e, -mc));
           const float p1 = ex2_approx(fmaf(__uint_as_float(raw[(col + 1) >> 5][(col + 1) & 31]), scale_log2e, -mc));
-          sum0 += p0;
-          sum1 += p1;
+          sums[(2 * e) & 3] += p0;
+          sums[(2 * e + 1) & 3] += p1;
           const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
           pk[e] = *reinterpret_cast<const uint32_t*>(&pp);
         }
@@ -474,7 +482,7 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
           for (int v = 0; v < 8; ++v) *reinterpret_cast<uint4*>(strip + swz(r, v)) = *reinterpret_cast<const uint4*>(&pk[4 * v]);
         }
       }
-      l += sum0 + sum1;
+      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
       if (P_TMEM) tmem_st_wait();
       else fence_async_smem();
       tc_fence_before();
@@ -927,6 +935,459 @@ k_attn_bwd64(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------ backward, warp-specialised
+// Two kernels, no atomics: k_attn_bwd_dq owns a tile of 128 queries and walks the key tiles at or below the
+// diagonal (dQ accumulates in TMEM); k_attn_bwd_dkv owns a tile of 128 keys and walks the query tiles at or above it
+// (dK and dV accumulate in TMEM).  Both recompute S and dP; results are deterministic.  Roles per CTA (320 threads):
+// warp 0 TMA producer, warp 1 MMA issuer (one thread), warps 2-9 element-wise work, two threads per TMEM lane (warps
+// w and w + 4 share a lane quarter and split the 128 columns).  Probabilities and dS never touch shared memory: they
+// are written back to TMEM as bf16 pairs and feed the next MMA as its A operand.
+
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src),
+               "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void named_barrier(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// ---- dQ.  Per key tile j <= qt:  S = Q.K_j^T, dP = dO.V_j^T (TMEM) -> dS = P * (dP - delta) * scale as bf16 in TMEM
+// (two buffers) -> dQ += dS.K_j.  The S / dP MMAs of tile j+1 are issued as soon as the element-wise warps have pulled
+// tile j into registers, so the tensor pipe works on j+1 while they compute dS(j).  The kernel also produces
+// delta[row] = sum_c dO[row, c] * O[row, c] for its queries (needed here and by the dK/dV kernel, which runs after it).
+// TMEM: S [0,128)  dP [128,256)  dQ [256,256+HD)  dS buffers [256+HD, +64) and [320+HD, +64).
+template <int HD>
+struct BwdDqSmem {
+  static constexpr int TILE_BYTES = (HD / 64) * STRIP;
+  static constexpr int Q = 0, DO = TILE_BYTES, RING = 2 * TILE_BYTES;
+  static constexpr int SLOTS_FIT = (223 * 1024 - RING) / TILE_BYTES;
+  static constexpr int SLOTS = SLOTS_FIT > 6 ? 6 : SLOTS_FIT;
+  static constexpr int DELTA = RING + SLOTS * TILE_BYTES;  // [2 halves][128 rows] floats
+  static constexpr int BARS = DELTA + 1024;
+  static constexpr int TOTAL = BARS + 256;
+  static_assert(SLOTS >= 4, "K_j, V_j, K_j+1 and V_j+1 are in flight together");
+};
+
+template <int HD>
+__global__ void __launch_bounds__(320, 1)
+k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const __nv_bfloat16* __restrict__ o,
+              const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse, float* __restrict__ delta_out,
+              __nv_bfloat16* __restrict__ dqkv, int B, int T, int H, int d, float scale, int* error) {
+  extern __shared__ __align__(1024) uint8_t dq_smem[];
+  uint8_t* smem = dq_smem;
+  if (smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0) {
+      *error = 1;
+      __threadfence_system();
+    }
+    return;
+  }
+  using L = BwdDqSmem<HD>;
+  constexpr int TILE_BYTES = L::TILE_BYTES, SLOTS = L::SLOTS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
+  uint64_t *qdo_full = bars, *sdp_full = bars + 1, *sdp_read = bars + 2, *ds_full = bars + 3 /* [2] */, *dq_full = bars + 5,
+           *kv_full = bars + 6, *kv_empty = bars + 6 + SLOTS;
+  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 6 + 2 * SLOTS);
+  float* delta_sm = reinterpret_cast<float*>(smem + L::DELTA);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_qt = T / TILE;
+  const int qt = n_qt - 1 - (int)blockIdx.x / (H * B);  // heaviest query tiles first
+  const int rest = (int)blockIdx.x % (H * B);
+  const int h = rest % H, b = rest / H;
+  const int n = qt + 1;  // key tiles
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t C_S = 0, C_DP = 128, C_DQ = 256, C_DS = 256 + HD;
+
+  if (tid == 0) {
+    mbar_init(qdo_full, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_read, 8);
+    mbar_init(&ds_full[0], 8);
+    mbar_init(&ds_full[1], 8);
+    mbar_init(dq_full, 1);
+    for (int s = 0; s < SLOTS; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tensormap(&map_qkv);
+    prefetch_tensormap(&map_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
+      load_tile<HD>(smem + L::Q, &map_qkv, qdo_full, h * HD, b * T + qt * TILE);
+      load_tile<HD>(smem + L::DO, &map_do, qdo_full, h * HD, b * T + qt * TILE);
+      bool ok = true;
+      for (int ld = 0; ld < 2 * n && ok; ++ld) {  // load 2j: K_j, load 2j+1: V_j
+        const int s = ld % SLOTS, j = ld >> 1, part = ld & 1;
+        if (!(ok = mbar_wait(&kv_empty[s], ((ld / SLOTS) & 1) ^ 1, error))) break;
+        mbar_expect_tx(&kv_full[s], TILE_BYTES);
+        load_tile<HD>(smem + L::RING + s * TILE_BYTES, &map_qkv, &kv_full[s], (1 + part) * d + h * HD, b * T + j * TILE);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc(128, 128, false, false);
+      constexpr uint32_t idesc_dq = instr_desc(128, HD, false, true);
+      auto slot_of = [&](int ld) { return smem + L::RING + (ld % SLOTS) * TILE_BYTES; };
+      auto wait_slot = [&](int ld) { return mbar_wait(&kv_full[ld % SLOTS], (ld / SLOTS) & 1, error); };
+      auto issue_scores = [&](int j) {
+        mma_kmajor<HD>(tmem + C_S, smem + L::Q, slot_of(2 * j), idesc_s, false);        // S  = Q . K_j^T
+        mma_kmajor<HD>(tmem + C_DP, smem + L::DO, slot_of(2 * j + 1), idesc_s, false);  // dP = dO . V_j^T
+        mma_commit(sdp_full);
+        mma_commit(&kv_empty[(2 * j + 1) % SLOTS]);  // V_j has no other reader
+      };
+      bool ok = mbar_wait(qdo_full, 0, error) && wait_slot(0) && wait_slot(1);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) {
+          if (!(ok = mbar_wait(sdp_read, j & 1, error))) break;  // tile j's S and dP are in registers
+          if (!(ok = wait_slot(2 * j + 2) && wait_slot(2 * j + 3))) break;
+          tc_fence_after();
+          issue_scores(j + 1);
+        }
+        if (!(ok = mbar_wait(&ds_full[j & 1], (j >> 1) & 1, error))) break;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(slot_of(2 * j));
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)  // dQ += dS . K_j: dS from TMEM (16 keys = 8 columns per step), K_j MN-major over the keys
+          mma_bf16_ts(tmem + C_DQ, tmem + C_DS + (j & 1) * 64 + kk * 8, smem_desc(k_addr + kk * 2048, STRIP, 1024), idesc_dq,
+                      (j > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(&kv_empty[(2 * j) % SLOTS]);
+      }
+      if (ok) mma_commit(dq_full);
+    }
+  } else {
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int q_idx = qt * TILE + r;
+    const size_t row = (size_t)b * T + q_idx;
+    // delta for this row: each of the row's two threads sums half of the head dimension
+    {
+      constexpr int COLS = HD / 2;
+      const __nv_bfloat16* a = o + row * d + h * HD + half * COLS;
+      const __nv_bfloat16* g = d_o + row * d + h * HD + half * COLS;
+      float acc = 0.f;
+#pragma unroll
+      for (int c = 0; c < COLS; c += 8) {
+        const uint4 av = *reinterpret_cast<const uint4*>(a + c), gv = *reinterpret_cast<const uint4*>(g + c);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __bfloat1622float2(a2[e]), y = __bfloat1622float2(g2[e]);
+          acc = fmaf(x.x, y.x, acc);
+          acc = fmaf(x.y, y.y, acc);
+        }
+      }
+      delta_sm[half * TILE + r] = acc;
+    }
+    named_barrier(1, 256);
+    const float delta = delta_sm[r] + delta_sm[TILE + r];
+    if (half == 0) delta_out[((size_t)b * H + h) * T + q_idx] = delta;
+    const float c2 = scale * 1.4426950408889634f;
+    const float neg_lse2 = -lse[((size_t)b * H + h) * T + q_idx] * 1.4426950408889634f;
+    bool ok = true;
+    for (int j = 0; j < n && ok; ++j) {
+      if (!(ok = mbar_wait_warp_spin(sdp_full, j & 1, error))) break;
+      tc_fence_after();
+      uint32_t s[2][32], dp[2][32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld32(tmem + C_S + lane_base + half * 64 + c * 32, s[c]);
+        tmem_ld32(tmem + C_DP + lane_base + half * 64 + c * 32, dp[c]);
+      }
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sdp_read);
+      uint32_t pk[32];
+      const bool diagonal = j == qt;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        float ds2[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int col = 2 * e + u;  // within this thread's 64 columns
+          float p = ex2_approx(fmaf(__uint_as_float(s[col >> 5][col & 31]), c2, neg_lse2));
+          if (diagonal && half * 64 + col > r) p = 0.f;
+          ds2[u] = p * (__uint_as_float(dp[col >> 5][col & 31]) - delta) * scale;
+        }
+        pk[e] = pack_bf16(ds2[0], ds2[1]);
+      }
+      tmem_st32(tmem + C_DS + (j & 1) * 64 + lane_base + half * 32, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_full[j & 1]);
+    }
+    if (ok) ok = mbar_wait_warp_spin(dq_full, 0, error);
+    if (ok) {
+      tc_fence_after();
+      constexpr int COLS = HD / 2;
+      __nv_bfloat16* dq_row = dqkv + row * 3 * d + h * HD + half * COLS;
+#pragma unroll 1
+      for (int c = 0; c < COLS / 32; ++c) {
+        uint32_t raw[32];
+        tmem_ld32(tmem + C_DQ + lane_base + half * COLS + c * 32, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint32_t y[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) y[e] = pack_bf16(__uint_as_float(raw[v * 8 + 2 * e]), __uint_as_float(raw[v * 8 + 2 * e + 1]));
+          *reinterpret_cast<uint4*>(dq_row + c * 32 + v * 8) = *reinterpret_cast<const uint4*>(y);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ---- dK, dV.  Transposed scores, so that the thread that owns a KEY row produces P^T and dS^T rows, which are the A
+// operands (M = keys) of the accumulating MMAs:  S^T = K.Q_i^T, dP^T = V.dO_i^T  ->  P^T = exp(S^T*scale - lse[q]) to
+// TMEM (bf16)  ->  dV += P^T.dO_i;  dS^T = P^T * (dP^T - delta[q]) * scale to TMEM  ->  dK += dS^T.Q_i.
+// lse and delta of the query tile travel with Q_i and dO_i in a stage (plain bulk copies onto the same barrier).
+// Each half-warp pair of a lane writes its bf16 result over the first 32 columns of ITS OWN half of the fp32 tile it
+// has just consumed (columns [0,32) and [64,96)), so no thread overwrites columns the other has yet to read.
+// TMEM: S^T [0,128)  dP^T [128,256)  dV [256,256+HD)  dK [256+HD, 256+2HD).
+template <int HD>
+struct BwdDkvSmem {
+  static constexpr int TILE_BYTES = (HD / 64) * STRIP;
+  static constexpr int K = 0, V = TILE_BYTES, STAGES_AT = 2 * TILE_BYTES;
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES + 1024;  // Q_i, dO_i, lse[128], delta[128]
+  static constexpr int STAGES_FIT = (223 * 1024 - STAGES_AT) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 4 ? 4 : STAGES_FIT;
+  static constexpr int BARS = STAGES_AT + STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BARS + 256;
+  static_assert(STAGES >= 2, "two query tiles must be in flight");
+};
+
+template <int HD>
+__global__ void __launch_bounds__(320, 1)
+k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const float* __restrict__ lse,
+               const float* __restrict__ delta, __nv_bfloat16* __restrict__ dqkv, int B, int T, int H, int d, float scale, int* error) {
+  extern __shared__ __align__(1024) uint8_t dkv_smem[];
+  uint8_t* smem = dkv_smem;
+  if (smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0) {
+      *error = 1;
+      __threadfence_system();
+    }
+    return;
+  }
+  using L = BwdDkvSmem<HD>;
+  constexpr int TILE_BYTES = L::TILE_BYTES, STAGES = L::STAGES, STAGE_BYTES = L::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
+  uint64_t *kv_full = bars, *s_full = bars + 1, *dp_full = bars + 2, *p_full = bars + 3, *ds_full = bars + 4, *acc_full = bars + 5,
+           *st_full = bars + 6, *st_empty = bars + 6 + STAGES;
+  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 6 + 2 * STAGES);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_tiles = T / TILE;
+  const int kt = (int)blockIdx.x / (H * B);  // key tile 0 visits every query tile: heaviest first
+  const int rest = (int)blockIdx.x % (H * B);
+  const int h = rest % H, b = rest / H;
+  const int nt = n_tiles - kt;  // query tiles kt .. n_tiles-1
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t C_S = 0, C_DP = 128, C_DV = 256, C_DK = 256 + HD;
+
+  if (tid == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_full, 8);
+    mbar_init(ds_full, 8);
+    mbar_init(acc_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&st_full[s], 1);
+      mbar_init(&st_empty[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tensormap(&map_qkv);
+    prefetch_tensormap(&map_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *holder;
+  auto stage_at = [&](int t) { return smem + L::STAGES_AT + (t % STAGES) * STAGE_BYTES; };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+      load_tile<HD>(smem + L::K, &map_qkv, kv_full, d + h * HD, b * T + kt * TILE);
+      load_tile<HD>(smem + L::V, &map_qkv, kv_full, 2 * d + h * HD, b * T + kt * TILE);
+      bool ok = true;
+      for (int t = 0; t < nt && ok; ++t) {
+        const int s = t % STAGES, i = kt + t;
+        if (!(ok = mbar_wait(&st_empty[s], ((t / STAGES) & 1) ^ 1, error))) break;
+        uint8_t* st = stage_at(t);
+        mbar_expect_tx(&st_full[s], STAGE_BYTES);
+        load_tile<HD>(st, &map_qkv, &st_full[s], h * HD, b * T + i * TILE);
+        load_tile<HD>(st + TILE_BYTES, &map_do, &st_full[s], h * HD, b * T + i * TILE);
+        const size_t stat0 = ((size_t)b * H + h) * T + (size_t)i * TILE;
+        bulk_load_1d(st + 2 * TILE_BYTES, lse + stat0, 512, &st_full[s]);
+        bulk_load_1d(st + 2 * TILE_BYTES + 512, delta + stat0, 512, &st_full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc(128, 128, false, false);
+      constexpr uint32_t idesc_acc = instr_desc(128, HD, false, true);
+      auto wait_stage = [&](int t) { return mbar_wait(&st_full[t % STAGES], (t / STAGES) & 1, error); };
+      // bf16 A operand written over an fp32 tile: keys k-step kk sits at columns (kk / 4) * 64 + (kk % 4) * 8
+      auto a_cols = [](int kk) { return (uint32_t)((kk >> 2) * 64 + (kk & 3) * 8); };
+      bool ok = mbar_wait(kv_full, 0, error) && wait_stage(0);
+      if (ok) {
+        tc_fence_after();
+        mma_kmajor<HD>(tmem + C_S, smem + L::K, stage_at(0), idesc_s, false);  // S^T = K . Q_i^T
+        mma_commit(s_full);
+        mma_kmajor<HD>(tmem + C_DP, smem + L::V, stage_at(0) + TILE_BYTES, idesc_s, false);  // dP^T = V . dO_i^T
+        mma_commit(dp_full);
+      }
+      for (int t = 0; t < nt && ok; ++t) {
+        const uint32_t q_addr = smem_u32(stage_at(t)), do_addr = q_addr + TILE_BYTES;
+        if (!(ok = mbar_wait(p_full, t & 1, error))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)  // dV += P^T . dO_i (16 queries per step; dO_i MN-major over the queries)
+          mma_bf16_ts(tmem + C_DV, tmem + C_S + a_cols(kk), smem_desc(do_addr + kk * 2048, STRIP, 1024), idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
+        if (t + 1 < nt) {
+          if (!(ok = wait_stage(t + 1))) break;
+          tc_fence_after();
+          mma_kmajor<HD>(tmem + C_S, smem + L::K, stage_at(t + 1), idesc_s, false);
+          mma_commit(s_full);
+        }
+        if (!(ok = mbar_wait(ds_full, t & 1, error))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)  // dK += dS^T . Q_i
+          mma_bf16_ts(tmem + C_DK, tmem + C_DP + a_cols(kk), smem_desc(q_addr + kk * 2048, STRIP, 1024), idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(&st_empty[t % STAGES]);  // Q_i, dO_i (and its lse / delta, read before ds_full) are done with
+        if (t + 1 < nt) {
+          mma_kmajor<HD>(tmem + C_DP, smem + L::V, stage_at(t + 1) + TILE_BYTES, idesc_s, false);
+          mma_commit(dp_full);
+        }
+      }
+      if (ok) mma_commit(acc_full);
+    }
+  } else {
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;  // key row within the tile
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float c2 = scale * 1.4426950408889634f;
+    bool ok = true;
+    for (int t = 0; t < nt && ok; ++t) {
+      const int i = kt + t;
+      const float* stat = reinterpret_cast<const float*>(stage_at(t) + 2 * TILE_BYTES) + half * 64;  // lse, then (+128) delta
+      if (!(ok = mbar_wait_warp_spin(&st_full[t % STAGES], (t / STAGES) & 1, error))) break;  // lse / delta have landed
+      if (!(ok = mbar_wait_warp_spin(s_full, t & 1, error))) break;
+      tc_fence_after();
+      float p[64];
+      {
+        uint32_t s[2][32];
+        tmem_ld32(tmem + C_S + lane_base + half * 64, s[0]);
+        tmem_ld32(tmem + C_S + lane_base + half * 64 + 32, s[1]);
+        tmem_ld_wait();
+        const bool diagonal = i == kt;
+#pragma unroll
+        for (int col = 0; col < 64; ++col) {
+          const float x = ex2_approx(fmaf(__uint_as_float(s[col >> 5][col & 31]), c2, -1.4426950408889634f * stat[col]));
+          p[col] = (diagonal && r > half * 64 + col) ? 0.f : x;  // key after the query
+        }
+      }
+      {
+        uint32_t pk[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) pk[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
+        tmem_st32(tmem + C_S + lane_base + half * 64, pk);
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      if (!(ok = mbar_wait_warp_spin(dp_full, t & 1, error))) break;
+      tc_fence_after();
+      {
+        uint32_t dp[2][32], pk[32];
+        tmem_ld32(tmem + C_DP + lane_base + half * 64, dp[0]);
+        tmem_ld32(tmem + C_DP + lane_base + half * 64 + 32, dp[1]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float a = p[2 * e] * (__uint_as_float(dp[(2 * e) >> 5][(2 * e) & 31]) - stat[128 + 2 * e]) * scale;
+          const float c = p[2 * e + 1] * (__uint_as_float(dp[(2 * e + 1) >> 5][(2 * e + 1) & 31]) - stat[128 + 2 * e + 1]) * scale;
+          pk[e] = pack_bf16(a, c);
+        }
+        tmem_st32(tmem + C_DP + lane_base + half * 64, pk);
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+    }
+    if (ok) ok = mbar_wait_warp_spin(acc_full, 0, error);
+    if (ok) {
+      tc_fence_after();
+      constexpr int COLS = HD / 2;
+      __nv_bfloat16* dk = dqkv + ((size_t)b * T + kt * TILE + r) * 3 * d + d + h * HD + half * COLS;
+      __nv_bfloat16* dv = dk + d;
+#pragma unroll 1
+      for (int part = 0; part < 2; ++part) {
+        __nv_bfloat16* dst = part == 0 ? dv : dk;
+        const uint32_t src = tmem + (part == 0 ? C_DV : C_DK) + lane_base + half * COLS;
+#pragma unroll 1
+        for (int c = 0; c < COLS / 32; ++c) {
+          uint32_t raw[32];
+          tmem_ld32(src + c * 32, raw);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t y[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[e] = pack_bf16(__uint_as_float(raw[v * 8 + 2 * e]), __uint_as_float(raw[v * 8 + 2 * e + 1]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = *reinterpret_cast<const uint4*>(y);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
 // dqkv[row, 0:d] = bf16(dq32[row, :])
 __global__ void __launch_bounds__(256) k_attn_dq_out(const float* __restrict__ dq32, __nv_bfloat16* __restrict__ dqkv, long long rows, int d) {
   const long long n8 = rows * (d / 8);
@@ -1032,6 +1493,8 @@ int tb_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int
 
 void tb_attn_fwd_variant(int v) { g_fwd_variant = v; }
 
+void tb_attn_bwd_kernels(int v) { g_bwd_variant = v; }
+
 // 1: the HD = 64 backward runs as k_attn_bwd64 (two CTAs per SM); 0: as k_attn_bwd<64>.  For measurements.
 void tb_attn_bwd_variant(int two_per_sm) { g_bwd_two_per_sm = two_per_sm; }
 
@@ -1048,6 +1511,28 @@ int tb_attn_bwd(const void* qkv, const void* out, const void* d_out, const float
   rc = make_map(&map_do, d_out, d, rows, d);
   if (rc) return rc;
   const float scale = 1.f / sqrtf((float)HD);
+  if (g_bwd_variant > 0) {
+    const unsigned ctas = (unsigned)((T / TILE) * H * B);
+    tb_note_launch(2);
+#define LAUNCH_BWD(HD_) \
+  do { \
+    static bool once = false; \
+    if (!once) { \
+      cudaError_t e = cudaFuncSetAttribute(k_attn_bwd_dq<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdDqSmem<HD_>::TOTAL); \
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_bwd_dkv<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdDkvSmem<HD_>::TOTAL); \
+      if (e != cudaSuccess) return (int)e; \
+      once = true; \
+    } \
+    k_attn_bwd_dq<HD_><<<ctas, 320, BwdDqSmem<HD_>::TOTAL, stream>>>(map_qkv, map_do, (const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, lse, \
+                                                                      delta, (__nv_bfloat16*)dqkv, B, T, H, d, scale, g_err_dev); \
+    k_attn_bwd_dkv<HD_><<<ctas, 320, BwdDkvSmem<HD_>::TOTAL, stream>>>(map_qkv, map_do, lse, delta, (__nv_bfloat16*)dqkv, B, T, H, d, scale, \
+                                                                        g_err_dev); \
+  } while (0)
+    if (HD == 64) LAUNCH_BWD(64);
+    else LAUNCH_BWD(128);
+#undef LAUNCH_BWD
+    return (int)cudaGetLastError();
+  }
   tb_note_launch(4);
   cudaMemsetAsync(dq32, 0, sizeof(float) * rows * d, stream);
   k_attn_delta<<<(unsigned)((rows * H + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, delta, T, H, HD, rows);

@@ -23,6 +23,8 @@ def _fns():
     L.tb_attn_bwd.restype = i
     L.tb_attn_bwd_variant.argtypes = [i]
     L.tb_attn_bwd_variant.restype = None
+    L.tb_attn_bwd_kernels.argtypes = [i]
+    L.tb_attn_bwd_kernels.restype = None
     L.tb_attn_fwd_variant.argtypes = [i]
     L.tb_attn_fwd_variant.restype = None
     L.tb_attn_error.argtypes = []
@@ -80,3 +82,8 @@ def backward_variant(two_per_sm):
 def forward_variant(which):
     """0: the two-pass kernel; 1: warp-specialised single pass, P through shared memory; 2: the same with P kept in TMEM."""
     _fns().tb_attn_fwd_variant(int(which))
+
+
+def backward_kernels(which):
+    """0: the single backward kernel that accumulates dQ with fp32 atomics; 1: the dQ kernel and the dK/dV kernel."""
+    _fns().tb_attn_bwd_kernels(int(which))

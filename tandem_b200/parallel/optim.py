@@ -28,6 +28,31 @@ class ShardedAdamW:
         self.state = {}
         self.master = {}  # key -> fp32 copy of a 16-bit shard
 
+    def ensure_state(self, key, param):
+        """[step, exp_avg, exp_avg_sq] of `key`, created (zero moments, fp32 master for a 16-bit shard) on first use."""
+        return self._state(key, param)
+
+    # ---- step constants on the device (for steps recorded as CUDA graphs)
+    def use_device_scalars(self, device):
+        """From now on the fused kernels read the step's constants from device memory: one counter and one set of
+        constants shared by every key, advanced by advance_on_device() once per optimizer step."""
+        if getattr(self, "_scalars_dev", None) is None:
+            self._step_dev = torch.zeros(1, dtype=torch.float64, device=device)
+            self._scalars_dev = torch.zeros(8, dtype=torch.float32, device=device)
+            self.advance_on_device()  # the constants of step 1
+
+    def device_scalars(self):
+        return getattr(self, "_scalars_dev", None)
+
+    def advance_on_device(self):
+        from ..ops.elementwise import adam_prepare
+
+        adam_prepare(self._step_dev, (self.lr, self.betas, self.eps, self.weight_decay), self._scalars_dev)
+
+    def steps_on_device(self):
+        """How many steps the device-side counter has prepared constants for, minus the one in preparation."""
+        return float(self._step_dev.item()) - 1.0
+
     def _state(self, key, param):
         if key not in self.state:
             like = param if param.dtype in (torch.float32, torch.float64) else param.float()
@@ -58,7 +83,12 @@ class ShardedAdamW:
                 from ..ops import fused_adamw
 
                 g = grad if grad.dtype in (torch.bfloat16, torch.float32) else grad.float()
-                fused_adamw(master, g, exp_avg, exp_avg_sq, self.scalars(step), self.weight_decay != 0, param)
+                if self.device_scalars() is not None:
+                    from ..ops.elementwise import adamw_step_dev
+
+                    adamw_step_dev(master, g, exp_avg, exp_avg_sq, self._scalars_dev, param)
+                else:
+                    fused_adamw(master, g, exp_avg, exp_avg_sq, self.scalars(step), self.weight_decay != 0, param)
             else:
                 self._torch_update(master, grad.float(), exp_avg, exp_avg_sq, step)
                 param.copy_(master)
@@ -69,7 +99,12 @@ class ShardedAdamW:
         if use_kernel:
             from ..ops import fused_adamw
 
-            fused_adamw(param, grad, exp_avg, exp_avg_sq, self.scalars(step), self.weight_decay != 0, shadow)
+            if self.device_scalars() is not None and param.is_cuda:
+                from ..ops.elementwise import adamw_step_dev
+
+                adamw_step_dev(param, grad, exp_avg, exp_avg_sq, self._scalars_dev, shadow)
+            else:
+                fused_adamw(param, grad, exp_avg, exp_avg_sq, self.scalars(step), self.weight_decay != 0, shadow)
             return
         self._torch_update(param, grad, exp_avg, exp_avg_sq, step)
         if shadow is not None:
