@@ -40,6 +40,9 @@ GLOBAL_BATCH = 16
 MODEL_LABEL, MODEL_DESC = "85.8M", "gpt-85.8M (L12 d768 h12 mlp3072 vocab65)"
 LR, WD = 3e-4, 0.1
 PUBLISHED_TOKENS_PER_S = 10265.0  # the reference's own "tandem DDP" row: 2x T4, fp32 (its README / bench/t4 results)
+# The unmodified reference (its stock fp32 path, Python engine) measured through `--impl reference` on this pool's B200s:
+# tokens/s of the flagship under DDP at 1, 2, 4 and 8 GPUs.  The same-hardware denominator beside the published T4 one.
+REFERENCE_ON_B200_TOKENS_PER_S = {1: 81494.0, 2: 123502.0, 4: 162418.0, 8: 187001.0}
 MICRO_BATCHES = 16  # pipeline strategies
 
 # The other training configurations of the benchmark plan (--model); the flagship above is the default.
@@ -169,7 +172,11 @@ def result_line(args, impl, strategy, dev_ms, e2e_ms, h2d, d2h, launches, clocks
     row = {
         "metric": f"gpt_{MODEL_LABEL}_{strategy}_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": value / PUBLISHED_TOKENS_PER_S if PUBLISHED_TOKENS_PER_S else None, "dtype": dtype, "data": "synthetic uniform-random token ids, random-init weights",
+        "vs_baseline": value / PUBLISHED_TOKENS_PER_S if PUBLISHED_TOKENS_PER_S else None,
+        "vs_baseline_is": "value / the reference's published tandem-DDP row (2x T4, fp32)" if PUBLISHED_TOKENS_PER_S else None,
+        "vs_reference_on_b200": (value / REFERENCE_ON_B200_TOKENS_PER_S[args.gpus]
+                                 if PUBLISHED_TOKENS_PER_S and strategy == "ddp" and args.gpus in REFERENCE_ON_B200_TOKENS_PER_S else None),
+        "dtype": dtype, "data": "synthetic uniform-random token ids, random-init weights",
         "impl": impl,
         "config": {"model": MODEL_DESC, "global_batch": GLOBAL_BATCH, "seq_len": MODEL["seq"],
                    "parallelism": f"{strategy}{args.gpus}", "optimizer": "AdamW lr 3e-4 wd 0.1",
@@ -188,7 +195,7 @@ def result_line(args, impl, strategy, dev_ms, e2e_ms, h2d, d2h, launches, clocks
 # ---------------------------------------------------------------------------------------------- ours
 def run_ours(args):
     import tandem_b200
-    from tandem_b200.ddp import DDP, BucketAdamW
+    from tandem_b200.ddp import DDP, BucketAdamW, ShardedBucketAdamW
     from tandem_b200.model import GPT, Config
     from tandem_b200.optim import ShardedAdamW
     from tandem_b200.parallel.symm import cuda_lib
@@ -215,23 +222,31 @@ def run_ours(args):
     pure_bf16 = kernels == "b200"
     if pure_bf16:
         model = model.bfloat16()  # fp32 master weights live in the optimizer
+    graphed = bool(args.graph) and args.strategy in ("ddp", "zero1", "zero2", "zero3")
+    sharded_opt = args.opt == "sharded" or (args.opt == "auto" and world >= 2)
     if args.strategy == "ddp":
         wrapped = DDP(model, g, rebuild=False)
-        opt = BucketAdamW(wrapped, lr=LR, weight_decay=WD)
-        finish = lambda: (opt.step(), opt.zero_grad())
+        # replicated: all-reduce + one AdamW kernel per bucket on every rank; sharded: reduce-scatter with the AdamW
+        # update in its epilogue + all-gather of the parameters (same values, 1/N of the optimizer traffic per rank)
+        opt = (ShardedBucketAdamW if sharded_opt else BucketAdamW)(wrapped, lr=LR, weight_decay=WD)
+        closer = opt
     elif args.strategy in ("zero1", "zero2"):
-        wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD), fused_step=True)
-        finish = lambda: (wrapped.step(), wrapped.zero_grad())
+        wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD), fused_step=True, capturable=graphed)
+        closer = wrapped
     elif args.strategy == "zero3":
-        wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD), fuse_gather_gemm=bool(args.fuse))
-        finish = lambda: (wrapped.step(), wrapped.zero_grad())
+        # the GEMM that gathers its own weight keeps a host-side epoch per call, so it is not recorded into graphs
+        wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD), fuse_gather_gemm=bool(args.fuse) and not graphed,
+                       capturable=graphed)
+        closer = wrapped
     elif args.strategy in ("gpipe", "1f1b"):
         from tandem_b200.pipeline import Pipeline
 
         wrapped = Pipeline(model, g, MICRO_BATCHES, args.strategy)  # one stage per GPU; stage traffic on NCCL p2p
         opt = torch.optim.AdamW(wrapped.parameters(), lr=LR, weight_decay=WD, fused=True)
+        closer = None
     else:
         raise SystemExit(f"unknown strategy {args.strategy}")
+    finish = (lambda: (closer.step(), closer.zero_grad())) if closer is not None else None
     pipelined = args.strategy in ("gpipe", "1f1b")
 
     def step_fn(x, y):
@@ -247,12 +262,11 @@ def run_ours(args):
         return loss
 
     per_rank = GLOBAL_BATCH if pipelined else GLOBAL_BATCH // world
-    graphed = args.graph and args.strategy == "ddp"
     if graphed:
         from tandem_b200.parallel.graph import GraphedStep
 
         ex = torch.zeros(per_rank, MODEL["seq"], dtype=torch.long, device=dev)
-        step_fn = GraphedStep(wrapped, opt, ex, ex.clone(), autocast=None if pure_bf16 else torch.bfloat16)
+        step_fn = GraphedStep(wrapped, closer, ex, ex.clone(), autocast=None if pure_bf16 else torch.bfloat16)
 
     def reduce_max(v):
         if world == 1:
@@ -279,7 +293,9 @@ def run_ours(args):
     g.close()
     if rank == 0:
         print(json.dumps(result_line(args, "ours", args.strategy, dev_ms, e2e_ms, h2d, d2h, int(launches), clocks, "bf16",
-                                     {"kernels": kernels, "final_loss": last, "cuda_graph": bool(graphed), "nvls": nvls})), flush=True)
+                                     {"kernels": kernels, "final_loss": last, "cuda_graph": bool(graphed), "nvls": nvls,
+                                      "optimizer": ("sharded over ranks, fused into the reduce-scatter" if sharded_opt else "replicated")
+                                      if args.strategy == "ddp" else "sharded"})), flush=True)
     if world > 1:
         import torch.distributed as dist
 
@@ -361,6 +377,7 @@ def reference_rank(g, steps, warmup, strategy):
     dev = g.device
     torch.manual_seed(0)
     model = GPT(Config(**MODEL)).to(dev)
+    pipelined = strategy in ("gpipe", "1f1b")
     if strategy == "ddp":
         wrapped = DDP(model, g)
         opt = torch.optim.AdamW(model.parameters(), lr=LR, weight_decay=WD, foreach=False)
@@ -368,17 +385,30 @@ def reference_rank(g, steps, warmup, strategy):
     elif strategy in ("zero1", "zero2"):
         wrapped = ZeRO(model, g, int(strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD))
         finish = lambda: (wrapped.step(), wrapped.zero_grad())
-    else:
+    elif strategy == "zero3":
         wrapped = FSDP(model, g, ShardedAdamW(lr=LR, weight_decay=WD))
         finish = lambda: (wrapped.step(), wrapped.zero_grad())
+    elif pipelined:
+        from tandem.pipeline import Pipeline
+
+        wrapped = Pipeline(model, g, MICRO_BATCHES, strategy)  # its own schedules over its own send / recv
+        opt = torch.optim.AdamW(wrapped.parameters(), lr=LR, weight_decay=WD, foreach=False)
+    else:
+        raise ValueError(f"the reference has no strategy {strategy!r}")
 
     def step_fn(x, y):
+        if pipelined:
+            loss = wrapped.train_step(x, y)
+            opt.step()
+            opt.zero_grad()
+            return loss if loss is not None else torch.zeros((), device=dev)
         loss = wrapped(x, y)
         loss.backward()
         finish()
         return loss
 
-    batches = token_batches(8, GLOBAL_BATCH // g.size, g.rank, g.size, MODEL["vocab"], MODEL["seq"])
+    per_rank = GLOBAL_BATCH if pipelined else GLOBAL_BATCH // g.size
+    batches = token_batches(8, per_rank, 0 if pipelined else g.rank, 1 if pipelined else g.size, MODEL["vocab"], MODEL["seq"])
     sampler = ClockSampler(dev.index)
     if g.rank == 0:
         sampler.start()
@@ -404,18 +434,27 @@ def run_reference(args):
             return
         sys.path.insert(0, ref)
         os.environ["PYTHONPATH"] = ref + os.pathsep + ROOT + os.pathsep + os.environ.get("PYTHONPATH", "")
-        try:
-            import tandem
+        import tandem
 
-            out = tandem.launch(reference_rank, args.gpus, args.steps, args.warmup, args.strategy, device="cuda",
-                                backend=args.ref_backend)
-        except Exception as e:
-            print(json.dumps({"impl": "reference", "unavailable": f"the reference failed to run: {repr(e)[:300]}"}), flush=True)
+        # "auto": the reference's C++ engine (its faster one, selected with backend="cpp" and built by the reference
+        # itself on first use) when there is communication to do, its Python engine if that build or run fails.
+        engines = {"auto": ["cpp", "python"] if args.gpus > 1 else ["python"], "cpp": ["cpp"], "python": ["python"]}[args.ref_backend]
+        out, engine, notes = None, None, []
+        for engine in engines:
+            try:
+                out = tandem.launch(reference_rank, args.gpus, args.steps, args.warmup, args.strategy, device="cuda", backend=engine)
+                break
+            except Exception as e:
+                notes.append(f"{engine}: {repr(e)[:200]}")
+        if out is None:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference failed to run: " + " | ".join(notes)}), flush=True)
             return
+        args.ref_backend = engine
+        ref_notes = notes
         dev_ms = max(o["dev_ms"] for o in out)
         e2e_ms = max(o["e2e_ms"] for o in out)
         print(json.dumps(result_line(args, "reference", args.strategy, dev_ms, e2e_ms, out[0]["h2d"], out[0]["d2h"], 0,
-                                     out[0]["clocks"], "fp32", {"engine": args.ref_backend, "final_loss": out[0]["loss"]})),
+                                     out[0]["clocks"], "fp32", {"engine": args.ref_backend, "engine_fallbacks": ref_notes, "final_loss": out[0]["loss"]})),
               flush=True)
     finally:
         if world > 1:
@@ -432,9 +471,12 @@ def main():
     ap.add_argument("--model", default="85.8m", choices=["85.8m", "1.3b", "pp24"],
                     help="85.8m: the flagship; 1.3b: the ZeRO-3 configuration; pp24: the 24-layer pipeline configuration")
     ap.add_argument("--kernels", default=os.environ.get("TANDEM_BENCH_KERNELS", "b200"), choices=["torch", "b200"])
-    ap.add_argument("--ref-backend", default="python", choices=["python", "cpp"])
+    ap.add_argument("--ref-backend", default=os.environ.get("TANDEM_REF_BACKEND", "python"), choices=["auto", "python", "cpp"],
+                    help="the reference's engine: its Python engine, its C++ engine, or auto (C++ with a fall-back to Python)")
+    ap.add_argument("--opt", default="auto", choices=["auto", "replicated", "sharded"],
+                    help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: sharded from 2 GPUs)")
     ap.add_argument("--fuse", type=int, default=1, help="zero3: gather each block's qkv weight inside its GEMM kernel")
-    ap.add_argument("--graph", type=int, default=1, help="replay the ddp step as a CUDA graph (ours, ddp only)")
+    ap.add_argument("--graph", type=int, default=1, help="record the step once as a CUDA graph and replay it (ours: ddp, zero1, zero2, zero3)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     select_model(args.model)

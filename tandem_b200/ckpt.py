@@ -96,7 +96,8 @@ def optimizer_state(wrapped, opt):
             if key not in opt.state:
                 continue
             step, m, v = opt.state[key]
-            out["step"] = step
+            # with step constants kept on the device (graph replay) the host-side count only saw the recorded step
+            out["step"] = opt.steps_on_device() if opt.device_scalars() is not None else step
             parts = {"exp_avg": _gather_flat(g, m, layout.numel, g.size).cpu(),
                      "exp_avg_sq": _gather_flat(g, v, layout.numel, g.size).cpu()}
             if key in opt.master:  # 16-bit parameters: the fp32 master weights are optimizer state too
@@ -107,6 +108,26 @@ def optimizer_state(wrapped, opt):
                 b = offs[offs.index(a) + 1]
                 for kind, flat in parts.items():
                     out[kind][names[id(p)]] = flat[a:b].clone()
+        return out
+    if hasattr(opt, "slots") and opt.slots and "sizes" in opt.slots[0]:  # ShardedBucketAdamW: each rank holds chunk r of every span
+        names = {id(p): n for n, p in _named(wrapped)}
+        out = {"kind": "adamw", "hyper": {"lr": opt.rule.lr, "betas": tuple(opt.rule.betas), "eps": opt.rule.eps,
+                                          "weight_decay": opt.rule.weight_decay},
+               "step": opt.step_count, "exp_avg": {}, "exp_avg_sq": {}, "master": {}}
+        for s in opt.slots:
+            span = s["bucket"]
+            parts = {}
+            for kind, key in (("exp_avg", "m"), ("exp_avg_sq", "v"), ("master", "master")):
+                full = torch.zeros(span.hi - span.lo, dtype=s[key].dtype, device=s[key].device)
+                full[s["lo"]:s["lo"] + s[key].numel()].copy_(s[key])
+                g.all_gather(full, s["sizes"])
+                parts[kind] = full.cpu()
+            at = 0
+            for p in span.params:
+                n = p.numel()
+                for kind, full in parts.items():
+                    out[kind][names[id(p)]] = full[at:at + n].clone()
+                at += n
         return out
     if hasattr(opt, "slots"):  # BucketAdamW: replicated state, bucket-major
         names = {id(p): n for n, p in _named(wrapped)}
@@ -163,20 +184,41 @@ def load_optimizer_state(wrapped, opt, state):
                 opt.master[key] = fw[layout.lo:layout.hi].to(dev).clone() if have_master else shard.detach().to(wide).clone()
             else:
                 opt.master.pop(key, None)
+        if opt.device_scalars() is not None:
+            opt._step_dev.fill_(float(state["step"]))
+            opt.advance_on_device()  # the constants of the step that comes next
         return
     opt.step_count = float(state["step"])
+    sharded = bool(opt.slots) and "sizes" in opt.slots[0]
     if hasattr(opt, "_step_dev"):
         opt._step_dev.fill_(opt.step_count)
+        if sharded:
+            opt._prepare()  # the sharded optimizer keeps the NEXT step's constants ready on the device
     for s in opt.slots:
+        span = s["bucket"]
+        if sharded:
+            full = {k: torch.zeros(span.hi - span.lo, dtype=s["m"].dtype) for k in ("m", "v", "master")}
         at = 0
-        for p in s["bucket"].params:
+        for p in span.params:
             n = p.numel()
             name = names[id(p)]
-            s["m"][at:at + n].copy_(state["exp_avg"][name])
-            s["v"][at:at + n].copy_(state["exp_avg_sq"][name])
-            if s["master"] is not s["flat"] and "master" in state:
-                s["master"][at:at + n].copy_(state["master"][name])
+            if sharded:
+                full["m"][at:at + n].copy_(state["exp_avg"][name].reshape(-1))
+                full["v"][at:at + n].copy_(state["exp_avg_sq"][name].reshape(-1))
+                source = state["master"][name] if name in (state.get("master") or {}) else p.detach().cpu().to(s["m"].dtype)
+                full["master"][at:at + n].copy_(source.reshape(-1))
+            else:
+                s["m"][at:at + n].copy_(state["exp_avg"][name])
+                s["v"][at:at + n].copy_(state["exp_avg_sq"][name])
+                if s["master"] is not s["flat"] and "master" in state:
+                    s["master"][at:at + n].copy_(state["master"][name])
             at += n
+        if sharded:
+            lo, count = s["lo"], s["m"].numel()
+            s["m"].copy_(full["m"][lo:lo + count])
+            s["v"].copy_(full["v"][lo:lo + count])
+            if s["master"].data_ptr() != s["flat"][lo:lo + count].data_ptr():
+                s["master"].copy_(full["master"][lo:lo + count])
 
 
 def save(path, wrapped, opt=None, extra=None):

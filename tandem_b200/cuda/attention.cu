@@ -36,7 +36,7 @@ namespace {
 
 int g_bwd_two_per_sm = 0;
 int g_bwd_variant = 1;  // 0: one kernel with fp32 atomics for dQ; 1: the two warp-specialised kernels
-int g_fwd_variant = 1;  // 0: two-pass kernel; 1: warp-specialised, P through shared memory; 2: warp-specialised, P in TMEM
+int g_fwd_variant = 2;  // 0: two-pass kernel; 1: warp-specialised, P through shared memory; 2: warp-specialised, P in TMEM
 
 using namespace tc;
 
@@ -300,10 +300,10 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
   uint64_t *q_full = bars, *s_full = bars + 2, *p_full = bars + 4, *o_full = bars + 6, *kv_full = bars + 8, *kv_empty = bars + 8 + SLOTS;
   uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 8 + 2 * SLOTS);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // heaviest pairs (most key tiles) first over the whole grid
   const int n_qt = T / TILE, n_pairs = (n_qt + 1) / 2;
-  const int pair = n_pairs - 1 - (int)blockIdx.x / (H * B);
-  const int rest = (int)blockIdx.x % (H * B);
+  // consecutive CTAs share one head's K and V (they stay in L2), longest pair first within the head
+  const int pair = n_pairs - 1 - (int)blockIdx.x % n_pairs;
+  const int rest = (int)blockIdx.x / n_pairs;
   const int h = rest % H, b = rest / H;
   const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
   const int n0 = qt0 + 1, n1 = qt1 < n_qt ? qt1 + 1 : 0;  // key tiles each query tile visits
@@ -965,7 +965,7 @@ template <int HD>
 struct BwdDqSmem {
   static constexpr int TILE_BYTES = (HD / 64) * STRIP;
   static constexpr int Q = 0, DO = TILE_BYTES, RING = 2 * TILE_BYTES;
-  static constexpr int SLOTS_FIT = (223 * 1024 - RING) / TILE_BYTES;
+  static constexpr int SLOTS_FIT = (225 * 1024 - RING) / TILE_BYTES;
   static constexpr int SLOTS = SLOTS_FIT > 6 ? 6 : SLOTS_FIT;
   static constexpr int DELTA = RING + SLOTS * TILE_BYTES;  // [2 halves][128 rows] floats
   static constexpr int BARS = DELTA + 1024;
@@ -996,8 +996,8 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant
   float* delta_sm = reinterpret_cast<float*>(smem + L::DELTA);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_qt = T / TILE;
-  const int qt = n_qt - 1 - (int)blockIdx.x / (H * B);  // heaviest query tiles first
-  const int rest = (int)blockIdx.x % (H * B);
+  const int qt = n_qt - 1 - (int)blockIdx.x % n_qt;  // consecutive CTAs share a head (its K, V stay in L2); longest first
+  const int rest = (int)blockIdx.x / n_qt;
   const int h = rest % H, b = rest / H;
   const int n = qt + 1;  // key tiles
   constexpr uint32_t TMEM_COLS = 512;
@@ -1208,8 +1208,8 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
   uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 6 + 2 * STAGES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = T / TILE;
-  const int kt = (int)blockIdx.x / (H * B);  // key tile 0 visits every query tile: heaviest first
-  const int rest = (int)blockIdx.x % (H * B);
+  const int kt = (int)blockIdx.x % n_tiles;  // consecutive CTAs share a head; key tile 0 visits every query tile: longest first
+  const int rest = (int)blockIdx.x / n_tiles;
   const int h = rest % H, b = rest / H;
   const int nt = n_tiles - kt;  // query tiles kt .. n_tiles-1
   constexpr uint32_t TMEM_COLS = 512;

@@ -41,6 +41,37 @@ class NcclP2P:
                                     device_id=group.device)
             self._own = True
 
+    # ---- lanes for pipeline stages
+    # Activations travel down the pipeline on one communicator, gradients travel up on another.  Each (pair of
+    # stages, lane) then carries one direction only, so a receive can be posted long before its data exists without
+    # ever standing in front of a send to the same peer on the same NCCL stream (which is how early receives
+    # deadlock when both directions share a communicator).
+    def lane(self, name):
+        if not hasattr(self, "_lanes"):
+            self._lanes = {"act": None}  # None: the default process group
+            self._lanes["grad"] = self.dist.new_group(list(range(self.g.size)), backend="nccl")  # collective: every rank calls it
+            self._side = torch.cuda.Stream(self.g.device)
+        return self._lanes[name]
+
+    def post_recv(self, shape, dtype, src, lane):
+        """Starts a receive into a fresh buffer, independent of whatever is queued on the caller's stream.
+        Returns (work, buffer); the buffer is usable on the caller's stream after work.wait()."""
+        group = self.lane(lane)
+        with torch.cuda.stream(self._side):
+            buf = torch.empty(shape, device=self.g.device, dtype=dtype)
+            work = self.dist.irecv(buf, src, group=group)
+        return work, buf
+
+    def claim(self, work, buf):
+        """Orders the caller's stream after a posted receive and hands the buffer over to it."""
+        work.wait()
+        buf.record_stream(torch.cuda.current_stream(self.g.device))
+        return buf
+
+    def post_send(self, tensor, dst, lane):
+        """Starts a send ordered after the caller's stream; the caller keeps (work, tensor) until the step ends."""
+        return self.dist.isend(tensor, dst, group=self.lane(lane)), tensor
+
     def _done(self, name, works, result, nbytes, async_op, keep):
         work = _NcclWork(name, self.g, works, result, nbytes, keep)
         return work if async_op else work.wait()

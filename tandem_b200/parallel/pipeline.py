@@ -104,7 +104,10 @@ class Pipeline:
         def fresh():
             return torch.empty(shape, device=dev, dtype=dtype)
 
-        for a in plan(self.schedule, g.size, g.rank, self.m):
+        actions = plan(self.schedule, g.size, g.rank, self.m)
+        if dev.type == "cuda" and getattr(g, "transport", "device") == "device" and g.size > 1:
+            return self._run_on_lanes(actions, xs, ys, dev, dtype, shape)
+        for a in actions:
             kind = a[0]
             if kind == "F":
                 i = a[1]
@@ -146,4 +149,69 @@ class Pipeline:
                 if not self.first:
                     act = fresh()
                     g.sendrecv(grad.contiguous(), up, act, up)
+        return sum(losses) if self.last else None
+
+    def _run_on_lanes(self, actions, xs, ys, dev, dtype, shape):
+        """GPU stages.  Transfers use two NCCL lanes (activations down, gradients up), so paired actions fall
+        apart into an asynchronous send and a receive that was posted ahead of time: as soon as one receive
+        has been claimed the next one of its kind is posted, before this stage computes anything on what it just
+        received.  Sends never hold up the compute stream; they are collected and awaited when the step ends."""
+        g, up, down = self.g, self.g.rank - 1, self.g.rank + 1
+        wire = g._p2p()
+        takes_act = {"recv_act", "send_grad_recv_act"}
+        takes_grad = {"recv_grad", "send_act_recv_grad"}
+        acts_due = 0 if self.first else sum(a[0] in takes_act for a in actions)
+        grads_due = 0 if self.last else sum(a[0] in takes_grad for a in actions)
+        posted = {"act": None, "grad": None}
+
+        def post(kind):
+            nonlocal acts_due, grads_due
+            if kind == "act" and acts_due:
+                acts_due -= 1
+                posted["act"] = wire.post_recv(shape, dtype, up, "act")
+            elif kind == "grad" and grads_due:
+                grads_due -= 1
+                posted["grad"] = wire.post_recv(shape, dtype, down, "grad")
+
+        def claim(kind):
+            handle, posted[kind] = posted[kind], None
+            tensor = wire.claim(*handle)
+            post(kind)  # the next one starts arriving while this one is being used
+            return tensor
+
+        post("act")
+        post("grad")
+        saved, losses, in_flight = {}, [], []
+        act = grad = out = None
+        for a in actions:
+            kind = a[0]
+            if kind == "F":
+                i = a[1]
+                with self.timeline.span(f"F{i}"):
+                    inp = xs[i].to(dev) if self.first else act.requires_grad_()
+                    out = self._run_units(inp)
+                    if self.last:
+                        out = loss_fn(out, ys[i].to(dev), self.kernels) / self.m
+                        losses.append(out.detach())
+                    saved[i] = (inp, out)
+            elif kind == "B":
+                i = a[1]
+                with self.timeline.span(f"B{i}"):
+                    inp, res = saved.pop(i)
+                    if self.last:
+                        res.backward()
+                    else:
+                        res.backward(grad)
+                    grad = None if self.first else inp.grad
+            else:
+                if kind in ("send_act", "send_act_recv_grad") and not self.last:
+                    in_flight.append(wire.post_send(out.detach().contiguous(), down, "act"))
+                if kind in ("send_grad", "send_grad_recv_act") and not self.first:
+                    in_flight.append(wire.post_send(grad.contiguous(), up, "grad"))
+                if kind in takes_act and not self.first:
+                    act = claim("act")
+                if kind in takes_grad and not self.last:
+                    grad = claim("grad")
+        for work, _tensor in in_flight:
+            work.wait()
         return sum(losses) if self.last else None
