@@ -28,6 +28,7 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "launch.cuh"
 #include "tcgen05.cuh"
 
 extern "C" void tb_note_launch(int n);
@@ -328,10 +329,12 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
     tmem_alloc(holder, TMEM_COLS);
     tmem_relinquish();
   }
+  tb::pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *holder;
+  tb::pdl_wait();  // set-up is done; everything below reads what earlier kernels wrote
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -1022,10 +1025,12 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant
     tmem_alloc(holder, TMEM_COLS);
     tmem_relinquish();
   }
+  tb::pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *holder;
+  tb::pdl_wait();  // set-up is done; everything below reads what earlier kernels wrote
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1234,10 +1239,12 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     tmem_alloc(holder, TMEM_COLS);
     tmem_relinquish();
   }
+  tb::pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *holder;
+  tb::pdl_wait();  // set-up is done; everything below reads what earlier kernels wrote
   auto stage_at = [&](int t) { return smem + L::STAGES_AT + (t % STAGES) * STAGE_BYTES; };
 
   if (warp == 0) {
@@ -1466,7 +1473,7 @@ int tb_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int
       if (e != cudaSuccess) return (int)e; \
       once = true; \
     } \
-    k_attn_fwd_ws<HD_, PT_><<<ctas, 320, Fwd2Smem<HD_, PT_>::TOTAL, stream>>>(map, (__nv_bfloat16*)out, lse, B, T, H, d, scale_log2e, g_err_dev); \
+    tb::launch(k_attn_fwd_ws<HD_, PT_>, dim3(ctas), dim3(320), Fwd2Smem<HD_, PT_>::TOTAL, stream, map, (__nv_bfloat16*)out, lse, B, T, H, d, scale_log2e, g_err_dev); \
   } while (0)
     if (HD == 64 && g_fwd_variant == 1) LAUNCH_WS(64, false);
     else if (HD == 64) LAUNCH_WS(64, true);
@@ -1523,10 +1530,10 @@ int tb_attn_bwd(const void* qkv, const void* out, const void* d_out, const float
       if (e != cudaSuccess) return (int)e; \
       once = true; \
     } \
-    k_attn_bwd_dq<HD_><<<ctas, 320, BwdDqSmem<HD_>::TOTAL, stream>>>(map_qkv, map_do, (const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, lse, \
-                                                                      delta, (__nv_bfloat16*)dqkv, B, T, H, d, scale, g_err_dev); \
-    k_attn_bwd_dkv<HD_><<<ctas, 320, BwdDkvSmem<HD_>::TOTAL, stream>>>(map_qkv, map_do, lse, delta, (__nv_bfloat16*)dqkv, B, T, H, d, scale, \
-                                                                        g_err_dev); \
+    tb::launch(k_attn_bwd_dq<HD_>, dim3(ctas), dim3(320), BwdDqSmem<HD_>::TOTAL, stream, map_qkv, map_do, (const __nv_bfloat16*)out, \
+               (const __nv_bfloat16*)d_out, lse, delta, (__nv_bfloat16*)dqkv, B, T, H, d, scale, g_err_dev); \
+    tb::launch(k_attn_bwd_dkv<HD_>, dim3(ctas), dim3(320), BwdDkvSmem<HD_>::TOTAL, stream, map_qkv, map_do, lse, (const float*)delta, \
+               (__nv_bfloat16*)dqkv, B, T, H, d, scale, g_err_dev); \
   } while (0)
     if (HD == 64) LAUNCH_BWD(64);
     else LAUNCH_BWD(128);

@@ -10,6 +10,7 @@
 #include <stdint.h>
 
 #include "adam.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -24,6 +25,7 @@ template <typename G>
 __global__ void __launch_bounds__(256)
 k_adamw(float* __restrict__ param, const G* __restrict__ grad, float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
         __nv_bfloat16* __restrict__ shadow, long long n, AdamScalars s, float grad_scale) {
+  tb::pdl_enter();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     float g = grad_of<G>(grad[i]);
@@ -43,6 +45,7 @@ template <typename G>
 __global__ void __launch_bounds__(256)
 k_adamw_dev(float* __restrict__ param, const G* __restrict__ grad, float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
             __nv_bfloat16* __restrict__ shadow, long long n, const AdamScalars* __restrict__ scalars) {
+  tb::pdl_enter();
   const AdamScalars s = *scalars;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -58,6 +61,7 @@ k_adamw_dev(float* __restrict__ param, const G* __restrict__ grad, float* __rest
 
 // One thread: step += 1, then the scalars of that step, in double precision as the host would.
 __global__ void k_adam_prepare(double* step, double lr, double beta1, double beta2, double eps, double wd, AdamScalars* out) {
+  tb::pdl_enter();
   const double t = *step + 1.0;
   *step = t;
   const double bc1 = 1.0 - pow(beta1, t), bc2 = 1.0 - pow(beta2, t);
@@ -84,6 +88,7 @@ struct CopyTable {
 
 // blockIdx.y picks the tensor, blockIdx.x strides over it.
 __global__ void __launch_bounds__(256) k_multi_copy(CopyTable t) {
+  tb::pdl_enter();
   const int k = blockIdx.y;
   const char* s = t.src[k];
   char* d = t.dst[k];
@@ -102,6 +107,9 @@ extern "C" void tb_note_launch(int n);
 
 extern "C" {
 
+// 1 (default): kernels are launched with programmatic dependent launch; 0: plain launches (for A/B measurements).
+void tb_set_pdl(int on) { tb::pdl_enabled() = on ? 1 : 0; }
+
 // scalars: {1-lr*wd, 1-beta1, beta2, 1-beta2, sqrt(bias_correction2), eps, -lr/bias_correction1}
 int tb_adamw(void* param, const void* grad, int grad_is_bf16, void* exp_avg, void* exp_avg_sq, void* shadow_bf16, long long n,
              const float* scalars, int do_decay, float grad_scale, cudaStream_t stream) {
@@ -111,11 +119,11 @@ int tb_adamw(void* param, const void* grad, int grad_is_bf16, void* exp_avg, voi
   int blocks = (int)(want > 148 * 8 ? 148 * 8 : want);
   tb_note_launch(1);
   if (grad_is_bf16)
-    k_adamw<__nv_bfloat16><<<blocks, 256, 0, stream>>>((float*)param, (const __nv_bfloat16*)grad, (float*)exp_avg,
-                                                        (float*)exp_avg_sq, (__nv_bfloat16*)shadow_bf16, n, s, grad_scale);
+    tb::launch(k_adamw<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (float*)param, (const __nv_bfloat16*)grad, (float*)exp_avg,
+               (float*)exp_avg_sq, (__nv_bfloat16*)shadow_bf16, n, s, grad_scale);
   else
-    k_adamw<float><<<blocks, 256, 0, stream>>>((float*)param, (const float*)grad, (float*)exp_avg, (float*)exp_avg_sq,
-                                                (__nv_bfloat16*)shadow_bf16, n, s, grad_scale);
+    tb::launch(k_adamw<float>, dim3(blocks), dim3(256), 0, stream, (float*)param, (const float*)grad, (float*)exp_avg, (float*)exp_avg_sq,
+               (__nv_bfloat16*)shadow_bf16, n, s, grad_scale);
   return (int)cudaGetLastError();
 }
 
@@ -123,7 +131,7 @@ int tb_adamw(void* param, const void* grad, int grad_is_bf16, void* exp_avg, voi
 int tb_adam_prepare(void* step_counter, double lr, double beta1, double beta2, double eps, double wd, void* scalars,
                     cudaStream_t stream) {
   tb_note_launch(1);
-  k_adam_prepare<<<1, 1, 0, stream>>>((double*)step_counter, lr, beta1, beta2, eps, wd, (AdamScalars*)scalars);
+  tb::launch(k_adam_prepare, dim3(1), dim3(1), 0, stream, (double*)step_counter, lr, beta1, beta2, eps, wd, (AdamScalars*)scalars);
   return (int)cudaGetLastError();
 }
 
@@ -135,11 +143,11 @@ int tb_adamw_dev(void* param, const void* grad, int grad_is_bf16, void* exp_avg,
   int blocks = (int)(want > 148 * 8 ? 148 * 8 : want);
   tb_note_launch(1);
   if (grad_is_bf16)
-    k_adamw_dev<__nv_bfloat16><<<blocks, 256, 0, stream>>>((float*)param, (const __nv_bfloat16*)grad, (float*)exp_avg,
-                                                            (float*)exp_avg_sq, (__nv_bfloat16*)shadow_bf16, n, (const AdamScalars*)scalars);
+    tb::launch(k_adamw_dev<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (float*)param, (const __nv_bfloat16*)grad, (float*)exp_avg,
+               (float*)exp_avg_sq, (__nv_bfloat16*)shadow_bf16, n, (const AdamScalars*)scalars);
   else
-    k_adamw_dev<float><<<blocks, 256, 0, stream>>>((float*)param, (const float*)grad, (float*)exp_avg, (float*)exp_avg_sq,
-                                                    (__nv_bfloat16*)shadow_bf16, n, (const AdamScalars*)scalars);
+    tb::launch(k_adamw_dev<float>, dim3(blocks), dim3(256), 0, stream, (float*)param, (const float*)grad, (float*)exp_avg, (float*)exp_avg_sq,
+               (__nv_bfloat16*)shadow_bf16, n, (const AdamScalars*)scalars);
   return (int)cudaGetLastError();
 }
 
@@ -158,7 +166,7 @@ int tb_multi_copy(const void* const* src, void* const* dst, const long long* byt
     long long want = (most + 256 * 16 * 4 - 1) / (256 * 16 * 4);
     dim3 grid((unsigned)(want < 1 ? 1 : (want > 64 ? 64 : want)), t.count);
     tb_note_launch(1);
-    k_multi_copy<<<grid, 256, 0, stream>>>(t);
+    tb::launch(k_multi_copy, grid, dim3(256), 0, stream, t);
   }
   return (int)cudaGetLastError();
 }

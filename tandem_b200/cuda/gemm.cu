@@ -36,6 +36,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include "launch.cuh"
 #include "tcgen05.cuh"
 
 namespace {
@@ -453,10 +454,12 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
     tmem_alloc(tmem_holder, TMEM_COLS);
     tmem_relinquish();
   }
+  tb::pdl_launch_dependents();  // the next kernel may set itself up while this one computes
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  tb::pdl_wait();  // barriers and TMEM are ready; from here on global memory written by earlier kernels is read
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -725,10 +728,12 @@ k_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     tmem_alloc_pair(tmem_holder, TMEM_COLS);
     tmem_relinquish_pair();
   }
+  tb::pdl_launch_dependents();
   tc_fence_before();
   cluster_sync_all();  // both CTAs' barriers are initialised before either one signals the other's
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  tb::pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -866,6 +871,7 @@ k_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 // Sums split-K partial tiles (fp32, fixed order) into the bf16 output, four columns per thread.
 __global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__ partials, int splits, long long stride, long long quads,
                                                         int N, int ldc, __nv_bfloat16* __restrict__ out, bool accumulate) {
+  tb::pdl_enter();
   const int per_row = ldc / 4;
   for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (long long)gridDim.x * blockDim.x) {
     const int col = (int)(q % per_row) * 4;
@@ -962,8 +968,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * g.splits;
   int ctas = tiles < g_sm_count ? tiles : g_sm_count;
   if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
-  kernel<<<ctas, L::THREADS, L::TOTAL, stream>>>(ma, mb, mo, mp, g, GatherArgs{});
-  return (int)cudaGetLastError();
+  return (int)tb::launch(kernel, dim3(ctas), dim3(L::THREADS), L::TOTAL, stream, ma, mb, mo, mp, g, GatherArgs{});
 }
 
 
@@ -1158,9 +1163,8 @@ int tb_splitk_reduce(const void* partials, int splits, int M, int N, int ldc, vo
   long long blocks = (quads + threads - 1) / threads;
   if (blocks > 148 * 8) blocks = 148 * 8;
   tb_note_launch(1);
-  k_splitk_reduce<<<(int)blocks, threads, 0, stream>>>((const float*)partials, splits, (long long)M * ldc, quads, N, ldc,
-                                                     (__nv_bfloat16*)out, (flags & EPI_ACCUMULATE) != 0);
-  return (int)cudaGetLastError();
+  return (int)tb::launch(k_splitk_reduce, dim3((int)blocks), dim3(threads), 0, stream, (const float*)partials, splits, (long long)M * ldc, quads, N,
+                         ldc, (__nv_bfloat16*)out, (flags & EPI_ACCUMULATE) != 0);
 }
 
 // out[M, N] = A[M, K] . W[N, K]^T (+ epilogue) where W is gathered by the kernel itself: rank q's shard (peer

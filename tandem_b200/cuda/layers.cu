@@ -8,6 +8,7 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include "launch.cuh"
 #include "noalloc.h"
 
 extern "C" void tb_note_launch(int n);
@@ -51,6 +52,7 @@ template <int MAXV>
 __global__ void __launch_bounds__(256)
 k_ln_fwd(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
          __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int D, float eps) {
+  tb::pdl_enter();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= M) return;
@@ -107,6 +109,7 @@ __global__ void __launch_bounds__(256, MAXV <= 4 ? 2 : 1)  // two blocks per SM 
 k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
          const float* __restrict__ mean_in, const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ add,
          __nv_bfloat16* __restrict__ dx, float* __restrict__ part, int M, int D) {
+  tb::pdl_enter();
   extern __shared__ float sh[];  // [warps][2][D]
   const int warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,6 +185,7 @@ k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__
 __global__ void __launch_bounds__(256)
 k_reduce_partials(const float* __restrict__ part, int parts, int width, __nv_bfloat16* __restrict__ out0,
                   __nv_bfloat16* __restrict__ out1, int split) {
+  tb::pdl_enter();
   __shared__ float sh[8][33];
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
@@ -211,6 +215,7 @@ __device__ unsigned g_col_sum_tickets[8192];
 __global__ void __launch_bounds__(1024)
 k_col_sum(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __restrict__ part, unsigned* tickets,
           __nv_bfloat16* __restrict__ out) {
+  tb::pdl_enter();
   __shared__ float sh[32][33];
   __shared__ int is_last;
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
@@ -253,6 +258,7 @@ k_col_sum(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __re
 __global__ void __launch_bounds__(256)
 k_xent_fwd(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets, float* __restrict__ lse_out,
            float* __restrict__ loss_out, int V, int ld) {
+  tb::pdl_enter();
   __shared__ float red[8];
   const int row = blockIdx.x;
   const __nv_bfloat16* z = logits + (size_t)row * ld;
@@ -284,6 +290,7 @@ k_xent_fwd(const __nv_bfloat16* __restrict__ logits, const long long* __restrict
 __global__ void __launch_bounds__(256)
 k_xent_bwd(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets, const float* __restrict__ lse,
            const float* __restrict__ grad_scale, float inv_rows, int V, int ld, int width) {
+  tb::pdl_enter();
   const int row = blockIdx.x;
   __nv_bfloat16* z = logits + (size_t)row * ld;
   const float l = lse[row];
@@ -298,6 +305,7 @@ k_xent_bwd(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ tar
 
 // loss = mean(per_row) in a fixed order (one block).
 __global__ void __launch_bounds__(1024) k_mean(const float* __restrict__ v, int n, float* __restrict__ out) {
+  tb::pdl_enter();
   __shared__ float red[32];
   float acc = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) acc += v[i];
@@ -315,6 +323,7 @@ __global__ void __launch_bounds__(1024) k_mean(const float* __restrict__ v, int 
 __global__ void __launch_bounds__(256)
 k_embed_fwd(const long long* __restrict__ idx, const __nv_bfloat16* __restrict__ tok, const __nv_bfloat16* __restrict__ pos,
             __nv_bfloat16* __restrict__ out, int rows, int T, int D) {
+  tb::pdl_enter();
   const int nvec = D >> 3;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * nvec; i += (long long)gridDim.x * blockDim.x) {
     const int row = (int)(i / nvec), v = (int)(i % nvec);
@@ -330,6 +339,7 @@ k_embed_fwd(const long long* __restrict__ idx, const __nv_bfloat16* __restrict__
 // dtok32[idx[row]] += dy[row] (fp32 atomics); dpos[t] = sum over batch of dy[b, t] (fixed order).
 __global__ void __launch_bounds__(256)
 k_embed_bwd_tok(const long long* __restrict__ idx, const __nv_bfloat16* __restrict__ dy, float* __restrict__ dtok32, int rows, int D) {
+  tb::pdl_enter();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * D; i += (long long)gridDim.x * blockDim.x) {
     const int row = (int)(i / D), c = (int)(i % D);
     atomicAdd(dtok32 + (size_t)idx[row] * D + c, __bfloat162float(dy[i]));
@@ -338,6 +348,7 @@ k_embed_bwd_tok(const long long* __restrict__ idx, const __nv_bfloat16* __restri
 
 __global__ void __launch_bounds__(256)
 k_embed_bwd_pos(const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dpos, int B, int T, int D) {
+  tb::pdl_enter();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)T * D; i += (long long)gridDim.x * blockDim.x) {
     float acc = 0.f;
     for (int b = 0; b < B; ++b) acc += __bfloat162float(dy[(size_t)b * T * D + i]);
@@ -346,6 +357,7 @@ k_embed_bwd_pos(const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict_
 }
 
 __global__ void __launch_bounds__(256) k_f32_to_bf16(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n) {
+  tb::pdl_enter();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     out[i] = __float2bfloat16_rn(in[i]);
 }
@@ -364,7 +376,7 @@ int tb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float
   if (D % 8 || D > 32 * 8 * 8) return -20;
   const int blocks = (M + 7) / 8;
   tb_note_launch(1);
-#define LN(V) k_ln_fwd<V><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, mean, rstd, M, D, eps)
+#define LN(V) tb::launch(k_ln_fwd<V>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, mean, rstd, M, D, eps)
   if (D <= 256 * 1) LN(1);
   else if (D <= 256 * 2) LN(2);
   else if (D <= 256 * 4) LN(4);
@@ -394,15 +406,15 @@ int tb_layernorm_bwd_add(const void* dy, const void* x, const void* w, const flo
 #define LN(V)                                                                                                          \
   do {                                                                                                                 \
     if (smem > 48 * 1024) cudaFuncSetAttribute(k_ln_bwd<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-    k_ln_bwd<V><<<blocks, 256, smem, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,  \
-                                          mean, rstd, (const __nv_bfloat16*)add, (__nv_bfloat16*)dx, scratch, M, D);   \
+    tb::launch(k_ln_bwd<V>, dim3(blocks), dim3(256), smem, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,          \
+               (const __nv_bfloat16*)w, mean, rstd, (const __nv_bfloat16*)add, (__nv_bfloat16*)dx, scratch, M, D);          \
   } while (0)
   if (D <= 256 * 1) LN(1);
   else if (D <= 256 * 2) LN(2);
   else if (D <= 256 * 4) LN(4);
   else LN(8);
 #undef LN
-  k_reduce_partials<<<(2 * D + 31) / 32, 256, 0, s>>>(scratch, blocks, 2 * D, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, D);
+  tb::launch(k_reduce_partials, dim3((2 * D + 31) / 32), dim3(256), 0, s, (const float*)scratch, blocks, 2 * D, (__nv_bfloat16*)dw, (__nv_bfloat16*)db, D);
   return (int)cudaGetLastError();
 }
 
@@ -427,12 +439,13 @@ int tb_col_sum(const void* x, int M, int N, int ld, void* out_bf16, float* scrat
     unsigned* tickets = pool + next;
     next += grid.x;
     tb_note_launch(1);
-    k_col_sum<<<grid, 1024, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, scratch, tickets, (__nv_bfloat16*)out_bf16);
+    tb::launch(k_col_sum, grid, dim3(1024), 0, s, (const __nv_bfloat16*)x, M, N, ld, scratch, tickets, (__nv_bfloat16*)out_bf16);
     return (int)cudaGetLastError();
   }
   tb_note_launch(2);
-  k_col_sum<<<grid, 1024, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, scratch, nullptr, nullptr);
-  k_reduce_partials<<<(N + 31) / 32, 256, 0, s>>>(scratch, slices, N, (__nv_bfloat16*)out_bf16, nullptr, N);
+  tb::launch(k_col_sum, grid, dim3(1024), 0, s, (const __nv_bfloat16*)x, M, N, ld, scratch, (unsigned*)nullptr, (__nv_bfloat16*)nullptr);
+  tb::launch(k_reduce_partials, dim3((N + 31) / 32), dim3(256), 0, s, (const float*)scratch, slices, N, (__nv_bfloat16*)out_bf16,
+             (__nv_bfloat16*)nullptr, N);
   return (int)cudaGetLastError();
 }
 
@@ -440,8 +453,8 @@ int tb_xent_fwd(const void* logits, const long long* targets, float* lse, float*
                 cudaStream_t s) {
   const int threads = V <= 128 ? 32 : (V <= 2048 ? 128 : 256);
   tb_note_launch(2);
-  k_xent_fwd<<<rows, threads, 0, s>>>((const __nv_bfloat16*)logits, targets, lse, row_loss, V, ld);
-  k_mean<<<1, 1024, 0, s>>>(row_loss, rows, loss);
+  tb::launch(k_xent_fwd, dim3(rows), dim3(threads), 0, s, (const __nv_bfloat16*)logits, targets, lse, row_loss, V, ld);
+  tb::launch(k_mean, dim3(1), dim3(1024), 0, s, (const float*)row_loss, rows, loss);
   return (int)cudaGetLastError();
 }
 
@@ -449,15 +462,15 @@ int tb_xent_bwd(void* logits, const long long* targets, const float* lse, const 
                 int width, cudaStream_t s) {
   const int threads = ld <= 128 ? 32 : (ld <= 2048 ? 128 : 256);
   tb_note_launch(1);
-  k_xent_bwd<<<rows, threads, 0, s>>>((__nv_bfloat16*)logits, targets, lse, grad_scale, 1.f / rows, V, ld, width);
+  tb::launch(k_xent_bwd, dim3(rows), dim3(threads), 0, s, (__nv_bfloat16*)logits, targets, lse, grad_scale, 1.f / rows, V, ld, width);
   return (int)cudaGetLastError();
 }
 
 int tb_embed_fwd(const long long* idx, const void* tok, const void* pos, void* out, int rows, int T, int D, cudaStream_t s) {
   if (D % 8) return -20;
   tb_note_launch(1);
-  k_embed_fwd<<<grid_for((long long)rows * (D / 8), 256, 148 * 8), 256, 0, s>>>(idx, (const __nv_bfloat16*)tok, (const __nv_bfloat16*)pos,
-                                                                              (__nv_bfloat16*)out, rows, T, D);
+  tb::launch(k_embed_fwd, dim3(grid_for((long long)rows * (D / 8), 256, 148 * 8)), dim3(256), 0, s, idx, (const __nv_bfloat16*)tok,
+             (const __nv_bfloat16*)pos, (__nv_bfloat16*)out, rows, T, D);
   return (int)cudaGetLastError();
 }
 
@@ -465,9 +478,9 @@ int tb_embed_fwd(const long long* idx, const void* tok, const void* pos, void* o
 int tb_embed_bwd(const long long* idx, const void* dy, float* dtok32, void* dtok, void* dpos, int B, int T, int D, int V,
                  cudaStream_t s) {
   tb_note_launch(3);
-  k_embed_bwd_tok<<<grid_for((long long)B * T * D, 256, 148 * 8), 256, 0, s>>>(idx, (const __nv_bfloat16*)dy, dtok32, B * T, D);
-  k_f32_to_bf16<<<grid_for((long long)V * D, 256, 148 * 8), 256, 0, s>>>(dtok32, (__nv_bfloat16*)dtok, (long long)V * D);
-  k_embed_bwd_pos<<<grid_for((long long)T * D, 256, 148 * 8), 256, 0, s>>>((const __nv_bfloat16*)dy, (__nv_bfloat16*)dpos, B, T, D);
+  tb::launch(k_embed_bwd_tok, dim3(grid_for((long long)B * T * D, 256, 148 * 8)), dim3(256), 0, s, idx, (const __nv_bfloat16*)dy, dtok32, B * T, D);
+  tb::launch(k_f32_to_bf16, dim3(grid_for((long long)V * D, 256, 148 * 8)), dim3(256), 0, s, (const float*)dtok32, (__nv_bfloat16*)dtok, (long long)V * D);
+  tb::launch(k_embed_bwd_pos, dim3(grid_for((long long)T * D, 256, 148 * 8)), dim3(256), 0, s, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dpos, B, T, D);
   return (int)cudaGetLastError();
 }
 

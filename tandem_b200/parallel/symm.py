@@ -114,6 +114,9 @@ def cuda_lib():
     for name, (argtypes, restype) in sig.items():
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = argtypes, restype
+    # TANDEM_PDL=0: launch the compute kernels without programmatic dependent launch (for A/B measurements)
+    lib.tb_set_pdl.argtypes, lib.tb_set_pdl.restype = [i], None
+    lib.tb_set_pdl(0 if os.environ.get("TANDEM_PDL", "1") == "0" else 1)
     return lib
 
 
