@@ -1,7 +1,7 @@
 """All-gather -> GEMM, fused in one kernel versus done in sequence, on a ZeRO-3 style sharded weight.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        -m tandem_b200.ops.bench_ag_gemm [--tokens 16384] [--dim 2048] [--out-features 6144]
+        bench/bench_ag_gemm.py [--tokens 16384] [--dim 2048] [--out-features 6144]
 
 Each rank owns 1/N of a flat bf16 buffer that contains the weight W[out, dim] (symmetric memory).
   fused     GatheredLinear: the GEMM kernel's fetch warps pull W from the owners while its tensor-core
@@ -12,11 +12,16 @@ Device time from CUDA events, max over ranks, L2 flushed between repetitions.  T
 of flops / measured bf16 peak and bytes that must cross NVLink / 770 GB/s.
 """
 
+import os as _os
+import sys as _sys
+
+_sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+
 import argparse
 import json
 import os
 
-import torch
+import torch  # noqa: E402
 import torch.distributed as dist
 
 

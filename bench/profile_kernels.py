@@ -1,6 +1,6 @@
 """Runs ONE kernel of this library a few times on a small, fixed case, so that a profiler can capture it:
 
-    python -m tandem_b200.ops.profile_kernels gemm_fwd | gemm_dx | gemm_dw | attn | adamw | layernorm |
+    python bench/profile_kernels.py gemm_fwd | gemm_dx | gemm_dw | attn | adamw | layernorm |
                                                allreduce | reduce_scatter_adam | gather_gemm
 
 Inputs are larger than the 126 MB L2 where the kernel is memory-bound, and at most a few hundred MB in
@@ -9,10 +9,15 @@ total.  The multi-rank kernels run with all ranks' buffers on this one GPU under
 CUDA-event time of the last repetition and the algorithmic bytes / flops of the case.
 """
 
+import os as _os
+import sys as _sys
+
+_sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+
 import json
 import sys
 
-import torch
+import torch  # noqa: E402
 
 
 def run(which, reps=3):
@@ -24,7 +29,7 @@ def run(which, reps=3):
 
     info = {}
     if which in ("gemm_fwd", "gemm_dx", "gemm_dw"):
-        from .gemm import BIAS, gemm
+        from tandem_b200.ops.gemm import BIAS, gemm
 
         M, N, K = 8192, 3072, 768
         if which == "gemm_fwd":
@@ -40,7 +45,7 @@ def run(which, reps=3):
             fn = lambda: gemm(a, b, M, N, K, M, N, True, True)
         info = {"flops": 2.0 * M * N * K, "bytes": 2.0 * (M * K + N * K + M * N)}
     elif which == "attn":
-        from . import causal_attention
+        from tandem_b200.ops import causal_attention
 
         B, T, H, hd = 16, 512, 12, 64
         qkv = rnd(B, T, 3 * H * hd).requires_grad_()
@@ -52,7 +57,7 @@ def run(which, reps=3):
 
         info = {"flops": 3.5 * 4.0 * B * H * T * T * hd / 2, "bytes": 2.0 * B * T * H * hd * (3 + 1 + 1 + 3)}
     elif which == "adamw":
-        from . import fused_adamw
+        from tandem_b200.ops import fused_adamw
 
         n = 64 << 20
         p, m, v = torch.randn(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
@@ -61,7 +66,7 @@ def run(which, reps=3):
         fn = lambda: fused_adamw(p, gr, m, v, sc, True, sh)
         info = {"bytes": n * (4 * 3 * 2 + 2 + 2)}
     elif which == "layernorm":
-        from . import layer_norm
+        from tandem_b200.ops import layer_norm
 
         M, D = 65536, 768
         x, w, b = rnd(M, D).requires_grad_(), rnd(D).requires_grad_(), rnd(D).requires_grad_()
@@ -73,7 +78,7 @@ def run(which, reps=3):
 
         info = {"bytes": 2.0 * M * D * (2 + 3)}
     elif which in ("allreduce", "reduce_scatter_adam"):
-        from ..parallel.symm import AdamArgs, EmulatedRanks
+        from tandem_b200.parallel.symm import AdamArgs, EmulatedRanks
 
         n, numel = 4, 16 << 20
         e = EmulatedRanks(n, timeout_s=5.0, max_blocks=32)
@@ -91,8 +96,8 @@ def run(which, reps=3):
             fn = lambda: e.reduce_scatter(bufs, [per] * n, average=True, adam=args)
             info = {"bytes": 4.0 * numel * (n + 1) + 4.0 * numel * 6}
     elif which == "gather_gemm":
-        from ..parallel.symm import split_offsets
-        from .gemm import GatheredLinear
+        from tandem_b200.parallel.symm import split_offsets
+        from tandem_b200.ops.gemm import GatheredLinear
 
         n, M, N, K = 4, 8192, 6144, 2048
         flat = rnd(N * K, scale=0.1)

@@ -6,19 +6,13 @@
 // operand when the reduction runs over the head dimension (Q.K^T, dO.V^T) and, with the same bytes,
 // an MN-major operand when it runs over the rows (P.V, P^T.dO, dS^T.Q, dS.K).
 //
-// Forward (one CTA per 128 queries of one head; 256 threads, two per query row = TMEM lane):
-//   pass 1  for every key tile:  S = Q.K^T (tcgen05.mma into TMEM) -> running row max
-//   pass 2  for every key tile:  S again -> P = exp2(S*c - max) written to shared memory as bf16
-//           in the swizzled K-major layout (summed on the way) -> O += P.V (accumulator stays in TMEM)
-//   end     O / sum -> bf16, and the row's log-sum-exp for backward
-// Two passes trade one extra Q.K^T (attention is ~5 % of this model's flops) for never having to
-// rescale an accumulator that lives in TMEM.
-//
-// Backward (one CTA per 128 keys of one head; loops over the query tiles at or below the diagonal):
-//   S = Q.K^T,  dP = dO.V^T   (TMEM)      P = exp(S*scale - lse),  dS = P * (dP - D) * scale
-//   dV += P^T.dO,  dK += dS^T.Q            (accumulated in TMEM across query tiles)
-//   dQ_tile = dS.K                          (TMEM) -> fp32 atomic adds into a dQ scratch
-// D = rowsum(dO * O) comes from a small pre-kernel; a post-kernel converts dQ to bf16.
+// Three warp-specialised kernels (one TMA producer warp, one MMA-issuing thread, eight element-wise warps):
+//   k_attn_fwd_ws    two 128-query tiles per CTA alternate on the tensor pipe; single pass, online softmax with a lazy
+//                    rescale of the accumulator in TMEM; P stays in TMEM as the A operand of P.V
+//   k_attn_bwd_dq    per query tile: S, dP -> dS (TMEM) -> dQ += dS.K; also produces delta = rowsum(dO * O)
+//   k_attn_bwd_dkv   per key tile, transposed scores: P^T, dS^T (TMEM) -> dV += P^T.dO, dK += dS^T.Q
+// Probabilities and score gradients never pass through shared memory, nothing is accumulated with atomics, and
+// the results do not depend on scheduling.  Consecutive CTAs work on the same head so its K and V stay in L2.
 //
 // Every wait is bounded (tcgen05.cuh); on expiry the CTA raises the host-visible error word, frees its
 // TMEM and returns.  The reference calls torch's scaled_dot_product_attention (tandem/model.py:43).
@@ -35,32 +29,10 @@ extern "C" void tb_note_launch(int n);
 
 namespace {
 
-int g_bwd_two_per_sm = 0;
-int g_bwd_variant = 1;  // 0: one kernel with fp32 atomics for dQ; 1: the two warp-specialised kernels
-int g_fwd_variant = 2;  // 0: two-pass kernel; 1: warp-specialised, P through shared memory; 2: warp-specialised, P in TMEM
-
 using namespace tc;
 
 constexpr int TILE = 128;           // queries per CTA, keys per step
 constexpr int STRIP = TILE * 128;   // bytes of one 128-row x 64-column bf16 strip (128-byte rows)
-
-// Byte offset of the 16-byte slot holding elements [8*slot, 8*slot+8) of row r in a swizzled strip.
-__device__ __forceinline__ int swz(int r, int slot) { return r * 128 + ((slot ^ (r & 7)) << 4); }
-
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-struct Waiter {
-  uint64_t* bar;
-  uint32_t phase;
-  int* error;
-  // Called by every thread of the CTA.  The verdict is made uniform, so that after a wait that ran out all
-  // threads leave the loops together and meet at the same __syncthreads on the way out.
-  __device__ __forceinline__ bool wait() {
-    bool ok = mbar_wait(bar, phase, error);
-    phase ^= 1;
-    return __syncthreads_and(ok);
-  }
-};
 
 // Loads one [128 rows x HD cols] operand tile (HD/64 strips) whose first element is (row, col) of qkv.
 template <int HD>
@@ -80,179 +52,6 @@ __device__ __forceinline__ void mma_kmajor(uint32_t d_tmem, const uint8_t* a, co
                idesc, (accumulate || s > 0 || k > 0) ? 1u : 0u);
 }
 
-// ------------------------------------------------------------------------------------------ forward
-// 256 threads: thread t owns query row t % 128 and the key columns [64*(t/128), 64*(t/128)+64) of every key
-// tile (warps w and w+4 share TMEM lanes 32*(w%4)..).  K (and V) tiles are double-buffered: thread 0 issues
-// the loads of the next step before it issues this step's MMAs.
-template <int HD>
-struct FwdSmem {
-  static constexpr int TILE_BYTES = (HD / 64) * STRIP;
-  // STATS (the two column halves' row maxima / sums, 1 KB) shares P's bytes: it is written at the end of pass 0 and
-  // after the last step, read at the start of pass 1 and at the very end, never while P is live.  With HD = 64 the
-  // total stays under 113 KB, so that two CTAs fit one SM (each also holds 256 TMEM columns): one computes its
-  // softmax while the other's MMAs run.  The buffer is declared 1024-byte aligned instead of being rounded up.
-  static constexpr int Q = 0, KV = Q + TILE_BYTES /* [2 buffers][K, V] */, P = KV + 4 * TILE_BYTES, STATS = P,
-                       BARS = P + 2 * STRIP;
-  static constexpr int TOTAL = BARS + 64;
-};
-
-template <int HD>
-__global__ void __launch_bounds__(256, HD == 64 ? 2 : 1)
-k_attn_fwd(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int T, int H, int d,
-           float scale_log2e, int* error) {
-  extern __shared__ __align__(1024) uint8_t fwd_smem[];
-  uint8_t* smem = fwd_smem;
-  if (smem_u32(smem) & 1023) {  // the swizzled tiles need 1024-byte alignment; nothing is allocated yet
-    if (threadIdx.x == 0) {
-      *error = 1;
-      __threadfence_system();
-    }
-    return;
-  }
-  using L = FwdSmem<HD>;
-  constexpr int TILE_BYTES = L::TILE_BYTES;
-  uint8_t *sQ = smem + L::Q, *sKV = smem + L::KV, *sP = smem + L::P;
-  float* stats = reinterpret_cast<float*>(smem + L::STATS);  // [2 halves][128 rows]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);  // 0: Q, 1-2: K/V buffers, 3: MMA
-  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 4);
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int r = tid & 127, half = tid >> 7;
-  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int row0 = b * T + qt * TILE;
-  constexpr uint32_t TMEM_COLS = 256;  // S: [0,128), O: [128, 128+HD)
-
-  if (tid == 0) {
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) {
-    tmem_alloc(holder, TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *holder;
-  const uint32_t tS = tmem, tO = tmem + 128;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  Waiter wq{&bars[0], 0, error}, wkv[2] = {{&bars[1], 0, error}, {&bars[2], 0, error}}, mm{&bars[3], 0, error};
-  constexpr uint32_t idesc_s = instr_desc(128, 128, false, false);
-  constexpr uint32_t idesc_o = instr_desc(128, HD, false, true);
-  const int steps = 2 * (qt + 1);  // pass 0 over key tiles 0..qt (row maxima), then pass 1 (P and O)
-
-  auto issue_loads = [&](int it) {  // thread 0 only
-    const int pass = it > qt, j = pass ? it - (qt + 1) : it, buf = it & 1;
-    uint8_t* k_dst = sKV + buf * 2 * TILE_BYTES;
-    mbar_expect_tx(&bars[1 + buf], TILE_BYTES * (pass ? 2 : 1));
-    load_tile<HD>(k_dst, &map, &bars[1 + buf], d + h * HD, b * T + j * TILE);
-    if (pass) load_tile<HD>(k_dst + TILE_BYTES, &map, &bars[1 + buf], 2 * d + h * HD, b * T + j * TILE);
-  };
-
-  if (tid == 0) {
-    mbar_expect_tx(&bars[0], TILE_BYTES);
-    load_tile<HD>(sQ, &map, &bars[0], h * HD, row0);
-    issue_loads(0);
-  }
-  bool ok = wq.wait();
-
-  float m2 = -INFINITY, l = 0.f;
-  const int q_idx = qt * TILE + r;
-  for (int it = 0; it < steps && ok; ++it) {
-    const int pass = it > qt, j = pass ? it - (qt + 1) : it, buf = it & 1;
-    const uint8_t* sK = sKV + buf * 2 * TILE_BYTES;
-    const uint8_t* sV = sK + TILE_BYTES;
-    if (tid == 0 && it + 1 < steps) issue_loads(it + 1);  // the other buffer was released by the previous step's last wait
-    if (!(ok = wkv[buf].wait())) break;
-    tc_fence_after();
-    if (tid == 0) {
-      mma_kmajor<HD>(tS, sQ, sK, idesc_s, false);
-      mma_commit(&bars[3]);
-    }
-    if (!(ok = mm.wait())) break;
-    tc_fence_after();
-    if (it == qt + 1) {  // first step of pass 1: combine the two halves' row maxima
-      m2 = fmaxf(stats[r], stats[TILE + r]);
-      __syncthreads();  // everyone has read the maxima before P (the same bytes) is written
-    }
-    const bool diagonal = j == qt;
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      const int col0 = half * 64 + c * 32;
-      uint32_t raw[32];
-      tmem_ld32(tS + lane_base + col0, raw);
-      tmem_ld_wait();
-      float x[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        x[i] = __uint_as_float(raw[i]) * scale_log2e;
-        if (diagonal && (j * TILE + col0 + i) > q_idx) x[i] = -INFINITY;
-      }
-      if (!pass) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) m2 = fmaxf(m2, x[i]);
-      } else {
-        uint8_t* strip = sP + half * STRIP;
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          __nv_bfloat162 p2[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float p0 = exp2f(x[v * 8 + 2 * i] - m2), p1 = exp2f(x[v * 8 + 2 * i + 1] - m2);
-            l += p0 + p1;
-            p2[i] = __floats2bfloat162_rn(p0, p1);
-          }
-          *reinterpret_cast<uint4*>(strip + swz(r, c * 4 + v)) = *reinterpret_cast<const uint4*>(p2);
-        }
-      }
-    }
-    if (it == qt) stats[half * TILE + r] = m2;  // end of pass 0
-    tc_fence_before();
-    if (pass) fence_async_smem();
-    __syncthreads();  // every row of S has been read (and P written) before the next MMA touches them
-    if (pass) {
-      if (tid == 0) {
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)  // 8 steps of 16 keys: P strip kk/4 (K-major), V rows 16*kk.. (MN-major, strips 16 KB apart)
-          mma_bf16(tO, smem_desc(smem_u32(sP + (kk >> 2) * STRIP) + (kk & 3) * 32, 16, 1024),
-                   smem_desc(smem_u32(sV) + kk * 2048, STRIP, 1024), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(&bars[3]);
-      }
-      if (!(ok = mm.wait())) break;  // P, this K/V buffer and S may be reused
-      tc_fence_after();
-    }
-  }
-  if (ok) {
-    stats[half * TILE + r] = l;
-    __syncthreads();
-    l = stats[r] + stats[TILE + r];
-    const float inv_l = 1.f / l;
-    constexpr int COLS = HD / 2;  // this thread's share of the row
-    __nv_bfloat16* o = out + (size_t)(row0 + r) * d + h * HD + half * COLS;
-#pragma unroll 1
-    for (int c = 0; c < COLS / 32; ++c) {
-      uint32_t raw[32];
-      tmem_ld32(tO + lane_base + half * COLS + c * 32, raw);
-      tmem_ld_wait();
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        __nv_bfloat162 y[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          y[i] = __floats2bfloat162_rn(__uint_as_float(raw[v * 8 + 2 * i]) * inv_l, __uint_as_float(raw[v * 8 + 2 * i + 1]) * inv_l);
-        *reinterpret_cast<uint4*>(o + c * 32 + v * 8) = *reinterpret_cast<const uint4*>(y);
-      }
-    }
-    if (half == 0) lse[((size_t)b * H + h) * T + q_idx] = (m2 + log2f(l)) * 0.69314718055994530942f;  // natural log
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after();
-    tmem_dealloc(tmem, TMEM_COLS);
-  }
-}
-
 // ------------------------------------------------------------------------------------------ forward, warp-specialised
 // One CTA per PAIR of 128-query tiles of one head, 320 threads in four roles:
 //   warp 0       TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring of tile slots
@@ -265,15 +64,14 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict__ 
 // barrier of its own: S_i(j) is committed after O_i += P.V of step j-1 on the in-order tensor pipe, and the next one is
 // only issued after this row's thread has arrived on p_full.
 // The two tiles alternate on the tensor pipe: while the softmax threads of one tile work on S_i(j) (exponentials), the
-// MMAs of the other tile run.  P goes to the MMA either through shared memory (bf16, swizzled K-major strips) or, with
-// P_TMEM, stays in TMEM over the first 64 columns of S (bf16 pairs) and is the A operand of a TMEM-sourced MMA.
+// MMAs of the other tile run.  P stays in TMEM: it is written as bf16 pairs over the first 64 columns of S and is the
+// A operand of a TMEM-sourced MMA (measured against staging P in shared memory: 198 vs 223 us at T = 2048, head dim 128).
 // TMEM: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+HD)  O_1 [256+HD, 256+2HD).
-template <int HD, bool P_TMEM>
+template <int HD>
 struct Fwd2Smem {
   static constexpr int TILE_BYTES = (HD / 64) * STRIP;
   static constexpr int Q = 0;                                       // two query tiles
-  static constexpr int P = Q + 2 * TILE_BYTES;                      // two P tiles of 2 strips (absent with P_TMEM)
-  static constexpr int RING = P + (P_TMEM ? 0 : 4 * STRIP);
+  static constexpr int RING = Q + 2 * TILE_BYTES;
   static constexpr int BUDGET = 224 * 1024;
   static constexpr int SLOTS_FIT = (BUDGET - RING) / TILE_BYTES;
   static constexpr int SLOTS = SLOTS_FIT > 6 ? 6 : SLOTS_FIT;       // K and V tiles in flight
@@ -282,7 +80,7 @@ struct Fwd2Smem {
   static_assert(SLOTS >= 3, "the K/V ring needs at least three slots");
 };
 
-template <int HD, bool P_TMEM>
+template <int HD>
 __global__ void __launch_bounds__(320, 1)
 k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int B, int T, int H,
               int d, float scale_log2e, int* error) {
@@ -295,7 +93,7 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
     }
     return;
   }
-  using L = Fwd2Smem<HD, P_TMEM>;
+  using L = Fwd2Smem<HD>;
   constexpr int TILE_BYTES = L::TILE_BYTES, SLOTS = L::SLOTS;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
   uint64_t *q_full = bars, *s_full = bars + 2, *p_full = bars + 4, *o_full = bars + 6, *kv_full = bars + 8, *kv_empty = bars + 8 + SLOTS;
@@ -370,12 +168,7 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint64_t v_desc = smem_desc(v_addr + kk * 2048, STRIP, 1024);
-          if (P_TMEM) {
-            mma_bf16_ts(tO, tmem + i * 128 + kk * 8, v_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-          } else {
-            const uint8_t* sP = smem + L::P + i * 2 * STRIP;
-            mma_bf16(tO, smem_desc(smem_u32(sP + (kk >> 2) * STRIP) + (kk & 3) * 32, 16, 1024), v_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-          }
+          mma_bf16_ts(tO, tmem + i * 128 + kk * 8, v_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);  // 16 keys = 8 TMEM columns of P
         }
       };
       bool ok = mbar_wait(&q_full[0], 0, error) && (!n1 || mbar_wait(&q_full[1], 0, error)) && wait_slot(0);
@@ -413,7 +206,6 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem + i * 128 + lane_base;
     const uint32_t tO = tmem + 256 + i * HD + lane_base;
-    uint8_t* sP = smem + L::P + i * 2 * STRIP;
     float m_used = -INFINITY, l = 0.f;  // m_used in raw score units
     bool ok = true;
     for (int j = 0; j < n_i && ok; ++j) {
@@ -477,17 +269,10 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
           const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
           pk[e] = *reinterpret_cast<const uint32_t*>(&pp);
         }
-        if (P_TMEM) {
-          tmem_st32(tS + hh * 32, pk);  // P over the first 64 columns of S: keys 2c, 2c+1 in column c
-        } else {
-          uint8_t* strip = sP + hh * STRIP;
-#pragma unroll
-          for (int v = 0; v < 8; ++v) *reinterpret_cast<uint4*>(strip + swz(r, v)) = *reinterpret_cast<const uint4*>(&pk[4 * v]);
-        }
+        tmem_st32(tS + hh * 32, pk);  // P over the first 64 columns of S: keys 2c, 2c+1 in column c
       }
       l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-      if (P_TMEM) tmem_st_wait();
-      else fence_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[i]);
@@ -518,421 +303,6 @@ k_attn_fwd_ws(const __grid_constant__ CUtensorMap map, __nv_bfloat16* __restrict
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem, TMEM_COLS);
-  }
-}
-
-// ------------------------------------------------------------------------------------------ backward
-// delta[b, h, t] = sum_c dO[b, t, h*HD + c] * O[b, t, h*HD + c]
-__global__ void __launch_bounds__(256)
-k_attn_delta(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta, int T, int H, int HD,
-             long long rows) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (row, head)
-  if (idx >= rows * H) return;
-  const long long row = idx / H;
-  const int h = (int)(idx % H);
-  const __nv_bfloat16* a = o + row * (long long)H * HD + h * HD;
-  const __nv_bfloat16* g = d_o + row * (long long)H * HD + h * HD;
-  float acc = 0.f;
-  for (int c = 0; c < HD; c += 8) {
-    uint4 av = *reinterpret_cast<const uint4*>(a + c), gv = *reinterpret_cast<const uint4*>(g + c);
-    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
-    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(g2[i]);
-      acc += x.x * y.x + x.y * y.y;
-    }
-  }
-  delta[((row / T) * H + h) * T + row % T] = acc;
-}
-
-// 256 threads, same row / column-half split as the forward.  Q and dO tiles are double-buffered when they fit
-// (HD = 64).  TMEM: [0,128) S, then dQ;  [128,256) dP;  [256, 256+HD) dV;  [256+HD, 256+2HD) dK.
-template <int HD>
-struct BwdSmem {
-  static constexpr int TILE_BYTES = (HD / 64) * STRIP;
-  static constexpr int NBUF = HD == 64 ? 2 : 1;
-  static constexpr int K = 0, V = K + TILE_BYTES, QDO = V + TILE_BYTES /* [NBUF][Q, dO] */, P = QDO + NBUF * 2 * TILE_BYTES,
-                       DS = P + 2 * STRIP, BARS = DS + 2 * STRIP;
-  static constexpr int TOTAL = BARS + 64 + 1024;
-};
-
-template <int HD>
-__global__ void __launch_bounds__(256)
-k_attn_bwd(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const float* __restrict__ lse,
-           const float* __restrict__ delta, float* __restrict__ dq32, __nv_bfloat16* __restrict__ dqkv, int T, int H, int d,
-           float scale, int* error) {
-  extern __shared__ uint8_t raw_smem[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
-  using L = BwdSmem<HD>;
-  constexpr int TILE_BYTES = L::TILE_BYTES, NBUF = L::NBUF;
-  uint8_t *sK = smem + L::K, *sV = smem + L::V, *sQDO = smem + L::QDO, *sP = smem + L::P, *sDS = smem + L::DS;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);  // 0: K/V, 1-2: Q/dO buffers, 3: MMA
-  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 4);
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int r = tid & 127, half = tid >> 7;
-  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int n_tiles = T / TILE;
-  constexpr uint32_t TMEM_COLS = 512;
-
-  if (tid == 0) {
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) {
-    tmem_alloc(holder, TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *holder;
-  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 256 + HD, tDQ = tmem;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  Waiter wkv{&bars[0], 0, error}, wq[2] = {{&bars[1], 0, error}, {&bars[2], 0, error}}, mm{&bars[3], 0, error};
-  constexpr uint32_t idesc_s = instr_desc(128, 128, false, false);   // S, dP: K-major x K-major over HD
-  constexpr uint32_t idesc_kv = instr_desc(128, HD, true, true);     // dV = P^T.dO, dK = dS^T.Q: both MN-major over queries
-  constexpr uint32_t idesc_dq = instr_desc(128, HD, false, true);    // dQ = dS.K: A K-major over keys, B MN-major
-
-  auto issue_q = [&](int i) {  // thread 0 only
-    const int buf = NBUF == 2 ? (i - kt) & 1 : 0;
-    uint8_t* q_dst = sQDO + buf * 2 * TILE_BYTES;
-    mbar_expect_tx(&bars[1 + buf], 2 * TILE_BYTES);
-    load_tile<HD>(q_dst, &map_qkv, &bars[1 + buf], h * HD, b * T + i * TILE);
-    load_tile<HD>(q_dst + TILE_BYTES, &map_do, &bars[1 + buf], h * HD, b * T + i * TILE);
-  };
-
-  if (tid == 0) {
-    mbar_expect_tx(&bars[0], 2 * TILE_BYTES);
-    load_tile<HD>(sK, &map_qkv, &bars[0], d + h * HD, b * T + kt * TILE);
-    load_tile<HD>(sV, &map_qkv, &bars[0], 2 * d + h * HD, b * T + kt * TILE);
-    issue_q(kt);
-  }
-  bool ok = wkv.wait();
-
-  for (int i = kt; i < n_tiles && ok; ++i) {
-    const int buf = NBUF == 2 ? (i - kt) & 1 : 0;
-    const uint8_t* sQ = sQDO + buf * 2 * TILE_BYTES;
-    const uint8_t* sDO = sQ + TILE_BYTES;
-    const int qrow0 = b * T + i * TILE;
-    if (NBUF == 2 && tid == 0 && i + 1 < n_tiles) issue_q(i + 1);
-    if (!(ok = wq[buf].wait())) break;
-    tc_fence_after();
-    if (tid == 0) {
-      mma_kmajor<HD>(tS, sQ, sK, idesc_s, false);     // S[q, k]
-      mma_kmajor<HD>(tDP, sDO, sV, idesc_s, false);   // dP[q, k]
-      mma_commit(&bars[3]);
-    }
-    if (!(ok = mm.wait())) break;
-    tc_fence_after();
-    const int q_idx = i * TILE + r;
-    const float row_lse = lse[((size_t)b * H + h) * T + q_idx];
-    const float row_delta = delta[((size_t)b * H + h) * T + q_idx];
-    const bool diagonal = i == kt;
-    uint8_t* p_strip = sP + half * STRIP;
-    uint8_t* ds_strip = sDS + half * STRIP;
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      const int col0 = half * 64 + c * 32;
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tS + lane_base + col0, rs);
-      tmem_ld32(tDP + lane_base + col0, rp);
-      tmem_ld_wait();
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        __nv_bfloat162 p2[4], s2[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = col0 + v * 8 + 2 * e + u;
-            float p = __expf(__uint_as_float(rs[v * 8 + 2 * e + u]) * scale - row_lse);
-            if (diagonal && kt * TILE + col > q_idx) p = 0.f;
-            pv[u] = p;
-            dv[u] = p * (__uint_as_float(rp[v * 8 + 2 * e + u]) - row_delta) * scale;
-          }
-          p2[e] = __floats2bfloat162_rn(pv[0], pv[1]);
-          s2[e] = __floats2bfloat162_rn(dv[0], dv[1]);
-        }
-        *reinterpret_cast<uint4*>(p_strip + swz(r, c * 4 + v)) = *reinterpret_cast<const uint4*>(p2);
-        *reinterpret_cast<uint4*>(ds_strip + swz(r, c * 4 + v)) = *reinterpret_cast<const uint4*>(s2);
-      }
-    }
-    tc_fence_before();
-    fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      // P and dS are stored [query row][key]: as A operands over the queries they are MN-major (M = keys):
-      // key strips 16 KB apart (LBO), 8-query groups 1024 B apart (SBO), 16 queries per step = 2048 B.
-      // dO and Q are [query row][head dim]: MN-major B operands (N = head dim) with the same geometry.
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        mma_bf16(tDV, smem_desc(smem_u32(sP) + kk * 2048, STRIP, 1024), smem_desc(smem_u32(sDO) + kk * 2048, STRIP, 1024), idesc_kv,
-                 (i > kt || kk > 0) ? 1u : 0u);
-        mma_bf16(tDK, smem_desc(smem_u32(sDS) + kk * 2048, STRIP, 1024), smem_desc(smem_u32(sQ) + kk * 2048, STRIP, 1024), idesc_kv,
-                 (i > kt || kk > 0) ? 1u : 0u);
-      }
-      // dQ[q, hd] = dS[q, keys] . K[keys, hd]: dS K-major over keys (strip kk/4, 32 B per step), K MN-major over keys.
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        mma_bf16(tDQ, smem_desc(smem_u32(sDS + (kk >> 2) * STRIP) + (kk & 3) * 32, 16, 1024), smem_desc(smem_u32(sK) + kk * 2048, STRIP, 1024),
-                 idesc_dq, kk > 0 ? 1u : 0u);
-      mma_commit(&bars[3]);
-    }
-    if (!(ok = mm.wait())) break;
-    tc_fence_after();
-    if (NBUF == 1 && tid == 0 && i + 1 < n_tiles) issue_q(i + 1);  // single buffer: Q and dO are free only now
-    constexpr int COLS = HD / 2;
-    float* dq_row = dq32 + (size_t)(qrow0 + r) * d + h * HD + half * COLS;
-#pragma unroll 1
-    for (int c = 0; c < COLS / 32; ++c) {
-      uint32_t raw[32];
-      tmem_ld32(tDQ + lane_base + half * COLS + c * 32, raw);
-      tmem_ld_wait();
-#pragma unroll
-      for (int e = 0; e < 8; ++e)
-        atomicAdd(reinterpret_cast<float4*>(dq_row + c * 32 + e * 4),
-                  make_float4(__uint_as_float(raw[4 * e]), __uint_as_float(raw[4 * e + 1]), __uint_as_float(raw[4 * e + 2]),
-                              __uint_as_float(raw[4 * e + 3])));
-    }
-    tc_fence_before();
-    __syncthreads();  // dQ has left TMEM, and P / dS may be overwritten
-  }
-  if (ok) {
-    // dK and dV rows (this CTA's keys) into the k and v parts of dqkv; each thread writes half of its row
-    constexpr int COLS = HD / 2;
-    __nv_bfloat16* dk = dqkv + (size_t)(b * T + kt * TILE + r) * 3 * d + d + h * HD + half * COLS;
-    __nv_bfloat16* dv = dk + d;
-#pragma unroll 1
-    for (int part = 0; part < 2; ++part) {
-      __nv_bfloat16* dst = part == 0 ? dv : dk;
-      const uint32_t src = (part == 0 ? tDV : tDK) + half * COLS;
-#pragma unroll 1
-      for (int c = 0; c < COLS / 32; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(src + lane_base + c * 32, raw);
-        tmem_ld_wait();
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          __nv_bfloat162 y[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) y[e] = __floats2bfloat162_rn(__uint_as_float(raw[v * 8 + 2 * e]), __uint_as_float(raw[v * 8 + 2 * e + 1]));
-          *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = *reinterpret_cast<const uint4*>(y);
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after();
-    tmem_dealloc(tmem, TMEM_COLS);
-  }
-}
-
-
-// Backward for HD = 64 shaped so that TWO CTAs share an SM (256 TMEM columns and under 113 KB of shared memory
-// each): while one CTA computes its exponentials the other's MMAs run.  S and dP take turns in the same 128 TMEM
-// columns (P stays packed in registers between them), dQ follows in the first 64 of those; P and dS take turns in
-// one shared-memory buffer; Q and dO are single-buffered.  Per query tile:
-//   S = Q.K^T                     -> P = exp(S*scale - lse) to registers (bf16 pairs) and shared memory
-//   dV += P^T.dO ;  dP = dO.V^T   -> dS = P * (dP - D) * scale over P's bytes in shared memory
-//   dK += dS^T.Q ;  dQ = dS.K     -> fp32 atomic adds into the dQ scratch
-// TMEM: [0,128) S / dP / dQ;  [128,192) dV;  [192,256) dK.
-struct Bwd64Smem {
-  static constexpr int K = 0, V = K + STRIP, Q = V + STRIP, DO = Q + STRIP, PS = DO + STRIP, BARS = PS + 2 * STRIP;
-  static constexpr int TOTAL = BARS + 64;
-};
-
-__global__ void __launch_bounds__(256, 2)
-k_attn_bwd64(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const float* __restrict__ lse,
-             const float* __restrict__ delta, float* __restrict__ dq32, __nv_bfloat16* __restrict__ dqkv, int T, int H, int d, float scale,
-             int* error) {
-  constexpr int HD = 64;
-  extern __shared__ __align__(1024) uint8_t bwd_smem[];
-  uint8_t* smem = bwd_smem;
-  if (smem_u32(smem) & 1023) {  // the swizzled tiles need 1024-byte alignment; nothing is allocated yet
-    if (threadIdx.x == 0) {
-      *error = 1;
-      __threadfence_system();
-    }
-    return;
-  }
-  using L = Bwd64Smem;
-  uint8_t *sK = smem + L::K, *sV = smem + L::V, *sQ = smem + L::Q, *sDO = smem + L::DO, *sPS = smem + L::PS;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);  // 0: K/V, 1: Q/dO, 2: MMA
-  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 4);
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int r = tid & 127, half = tid >> 7;
-  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int n_tiles = T / TILE;
-  constexpr uint32_t TMEM_COLS = 256;
-
-  if (tid == 0) {
-    for (int i = 0; i < 3; ++i) mbar_init(&bars[i], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) {
-    tmem_alloc(holder, TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *holder;
-  const uint32_t tSP = tmem, tDQ = tmem, tDV = tmem + 128, tDK = tmem + 192;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  Waiter wkv{&bars[0], 0, error}, wq{&bars[1], 0, error}, mm{&bars[2], 0, error};
-  constexpr uint32_t idesc_s = instr_desc(128, 128, false, false);
-  constexpr uint32_t idesc_kv = instr_desc(128, HD, true, true);
-  constexpr uint32_t idesc_dq = instr_desc(128, HD, false, true);
-
-  auto issue_q = [&](int i) {  // thread 0 only
-    mbar_expect_tx(&bars[1], 2 * STRIP);
-    load_tile<HD>(sQ, &map_qkv, &bars[1], h * HD, b * T + i * TILE);
-    load_tile<HD>(sDO, &map_do, &bars[1], h * HD, b * T + i * TILE);
-  };
-
-  if (tid == 0) {
-    mbar_expect_tx(&bars[0], 2 * STRIP);
-    load_tile<HD>(sK, &map_qkv, &bars[0], d + h * HD, b * T + kt * TILE);
-    load_tile<HD>(sV, &map_qkv, &bars[0], 2 * d + h * HD, b * T + kt * TILE);
-    issue_q(kt);
-  }
-  bool ok = wkv.wait();
-  uint8_t* my_strip = sPS + half * STRIP;
-
-  for (int i = kt; i < n_tiles && ok; ++i) {
-    const int qrow0 = b * T + i * TILE;
-    if (!(ok = wq.wait())) break;
-    tc_fence_after();
-    if (tid == 0) {
-      mma_kmajor<HD>(tSP, sQ, sK, idesc_s, false);  // S[q, k]
-      mma_commit(&bars[2]);
-    }
-    if (!(ok = mm.wait())) break;
-    tc_fence_after();
-    const int q_idx = i * TILE + r;
-    const float row_lse = lse[((size_t)b * H + h) * T + q_idx];
-    const float row_delta = delta[((size_t)b * H + h) * T + q_idx];
-    const bool diagonal = i == kt;
-    uint4 packed[8];  // this thread's 64 probabilities as bf16 pairs
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const int col0 = half * 64 + c * 32;
-      uint32_t rs[32];
-      tmem_ld32(tSP + lane_base + col0, rs);
-      tmem_ld_wait();
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed[c * 4 + v]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float pv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = col0 + v * 8 + 2 * e + u;
-            float p = __expf(__uint_as_float(rs[v * 8 + 2 * e + u]) * scale - row_lse);
-            if (diagonal && kt * TILE + col > q_idx) p = 0.f;
-            pv[u] = p;
-          }
-          p2[e] = __floats2bfloat162_rn(pv[0], pv[1]);
-        }
-        *reinterpret_cast<uint4*>(my_strip + swz(r, c * 4 + v)) = packed[c * 4 + v];
-      }
-    }
-    tc_fence_before();
-    fence_async_smem();
-    __syncthreads();  // S has been read everywhere (dP may overwrite it) and P is complete
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)  // dV += P^T.dO: P and dO MN-major over the queries
-        mma_bf16(tDV, smem_desc(smem_u32(sPS) + kk * 2048, STRIP, 1024), smem_desc(smem_u32(sDO) + kk * 2048, STRIP, 1024), idesc_kv,
-                 (i > kt || kk > 0) ? 1u : 0u);
-      mma_kmajor<HD>(tSP, sDO, sV, idesc_s, false);  // dP[q, k]
-      mma_commit(&bars[2]);
-    }
-    if (!(ok = mm.wait())) break;  // P's bytes may be overwritten: the dV MMAs have read them
-    tc_fence_after();
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const int col0 = half * 64 + c * 32;
-      uint32_t rp[32];
-      tmem_ld32(tSP + lane_base + col0, rp);
-      tmem_ld_wait();
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&packed[c * 4 + v]);
-        __nv_bfloat162 s2[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 p = __bfloat1622float2(p2[e]);
-          s2[e] = __floats2bfloat162_rn(p.x * (__uint_as_float(rp[v * 8 + 2 * e]) - row_delta) * scale,
-                                        p.y * (__uint_as_float(rp[v * 8 + 2 * e + 1]) - row_delta) * scale);
-        }
-        *reinterpret_cast<uint4*>(my_strip + swz(r, c * 4 + v)) = *reinterpret_cast<const uint4*>(s2);
-      }
-    }
-    tc_fence_before();
-    fence_async_smem();
-    __syncthreads();  // dP has been read everywhere (dQ may overwrite it) and dS is complete
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)  // dK += dS^T.Q
-        mma_bf16(tDK, smem_desc(smem_u32(sPS) + kk * 2048, STRIP, 1024), smem_desc(smem_u32(sQ) + kk * 2048, STRIP, 1024), idesc_kv,
-                 (i > kt || kk > 0) ? 1u : 0u);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)  // dQ = dS.K: dS K-major over the keys, K MN-major over the keys
-        mma_bf16(tDQ, smem_desc(smem_u32(sPS + (kk >> 2) * STRIP) + (kk & 3) * 32, 16, 1024), smem_desc(smem_u32(sK) + kk * 2048, STRIP, 1024),
-                 idesc_dq, kk > 0 ? 1u : 0u);
-      mma_commit(&bars[2]);
-    }
-    if (!(ok = mm.wait())) break;
-    tc_fence_after();
-    if (tid == 0 && i + 1 < n_tiles) issue_q(i + 1);  // Q and dO are free only now
-    constexpr int COLS = HD / 2;
-    float* dq_row = dq32 + (size_t)(qrow0 + r) * d + h * HD + half * COLS;
-    {
-      uint32_t raw[32];
-      tmem_ld32(tDQ + lane_base + half * COLS, raw);
-      tmem_ld_wait();
-#pragma unroll
-      for (int e = 0; e < 8; ++e)
-        atomicAdd(reinterpret_cast<float4*>(dq_row + e * 4),
-                  make_float4(__uint_as_float(raw[4 * e]), __uint_as_float(raw[4 * e + 1]), __uint_as_float(raw[4 * e + 2]),
-                              __uint_as_float(raw[4 * e + 3])));
-    }
-    tc_fence_before();
-    __syncthreads();  // dQ has left TMEM before the next tile's S lands there
-  }
-  if (ok) {
-    constexpr int COLS = HD / 2;
-    __nv_bfloat16* dk = dqkv + (size_t)(b * T + kt * TILE + r) * 3 * d + d + h * HD + half * COLS;
-    __nv_bfloat16* dv = dk + d;
-#pragma unroll 1
-    for (int part = 0; part < 2; ++part) {
-      __nv_bfloat16* dst = part == 0 ? dv : dk;
-      uint32_t raw[32];
-      tmem_ld32((part == 0 ? tDV : tDK) + half * COLS + lane_base, raw);
-      tmem_ld_wait();
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        __nv_bfloat162 y[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) y[e] = __floats2bfloat162_rn(__uint_as_float(raw[v * 8 + 2 * e]), __uint_as_float(raw[v * 8 + 2 * e + 1]));
-        *reinterpret_cast<uint4*>(dst + v * 8) = *reinterpret_cast<const uint4*>(y);
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -1395,19 +765,6 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
   }
 }
 
-// dqkv[row, 0:d] = bf16(dq32[row, :])
-__global__ void __launch_bounds__(256) k_attn_dq_out(const float* __restrict__ dq32, __nv_bfloat16* __restrict__ dqkv, long long rows, int d) {
-  const long long n8 = rows * (d / 8);
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
-    const long long row = i / (d / 8);
-    const int c = (int)(i % (d / 8)) * 8;
-    const float4 a = *reinterpret_cast<const float4*>(dq32 + row * d + c), bq = *reinterpret_cast<const float4*>(dq32 + row * d + c + 4);
-    __nv_bfloat162 y[4] = {__floats2bfloat162_rn(a.x, a.y), __floats2bfloat162_rn(a.z, a.w), __floats2bfloat162_rn(bq.x, bq.y),
-                           __floats2bfloat162_rn(bq.z, bq.w)};
-    *reinterpret_cast<uint4*>(dqkv + row * 3 * d + c) = *reinterpret_cast<const uint4*>(y);
-  }
-}
-
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1460,54 +817,28 @@ int tb_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int
   int rc = make_map(&map, qkv, 3LL * d, (long long)B * T, 3LL * d);
   if (rc) return rc;
   const float scale_log2e = 1.4426950408889634f / sqrtf((float)HD);
-  dim3 grid(T / TILE, H, B);
+  const int n_pairs = (T / TILE + 1) / 2;
+  const unsigned ctas = (unsigned)(n_pairs * H * B);
   tb_note_launch(1);
-  if (g_fwd_variant > 0) {
-    const int n_pairs = (T / TILE + 1) / 2;
-    const unsigned ctas = (unsigned)(n_pairs * H * B);
-#define LAUNCH_WS(HD_, PT_) \
+#define LAUNCH_FWD(HD_) \
   do { \
     static bool once = false; \
     if (!once) { \
-      cudaError_t e = cudaFuncSetAttribute(k_attn_fwd_ws<HD_, PT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<HD_, PT_>::TOTAL); \
+      cudaError_t e = cudaFuncSetAttribute(k_attn_fwd_ws<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<HD_>::TOTAL); \
       if (e != cudaSuccess) return (int)e; \
       once = true; \
     } \
-    tb::launch(k_attn_fwd_ws<HD_, PT_>, dim3(ctas), dim3(320), Fwd2Smem<HD_, PT_>::TOTAL, stream, map, (__nv_bfloat16*)out, lse, B, T, H, d, scale_log2e, g_err_dev); \
+    return (int)tb::launch(k_attn_fwd_ws<HD_>, dim3(ctas), dim3(320), Fwd2Smem<HD_>::TOTAL, stream, map, (__nv_bfloat16*)out, lse, B, T, H, d, \
+                           scale_log2e, g_err_dev); \
   } while (0)
-    if (HD == 64 && g_fwd_variant == 1) LAUNCH_WS(64, false);
-    else if (HD == 64) LAUNCH_WS(64, true);
-    else if (g_fwd_variant == 1) LAUNCH_WS(128, false);
-    else LAUNCH_WS(128, true);
-#undef LAUNCH_WS
-    return (int)cudaGetLastError();
-  }
-  if (HD == 64) {
-    static bool once = false;
-    if (!once) {
-      cudaFuncSetAttribute(k_attn_fwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL);
-      cudaFuncSetAttribute(k_attn_fwd<64>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);  // two CTAs per SM
-      once = true;
-    }
-    k_attn_fwd<64><<<grid, 256, FwdSmem<64>::TOTAL, stream>>>(map, (__nv_bfloat16*)out, lse, T, H, d, scale_log2e, g_err_dev);
-  } else {
-    static bool once = false;
-    if (!once) { cudaFuncSetAttribute(k_attn_fwd<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::TOTAL); once = true; }
-    k_attn_fwd<128><<<grid, 256, FwdSmem<128>::TOTAL, stream>>>(map, (__nv_bfloat16*)out, lse, T, H, d, scale_log2e, g_err_dev);
-  }
-  return (int)cudaGetLastError();
+  if (HD == 64) LAUNCH_FWD(64);
+  LAUNCH_FWD(128);
+#undef LAUNCH_FWD
 }
 
-void tb_attn_fwd_variant(int v) { g_fwd_variant = v; }
-
-void tb_attn_bwd_kernels(int v) { g_bwd_variant = v; }
-
-// 1: the HD = 64 backward runs as k_attn_bwd64 (two CTAs per SM); 0: as k_attn_bwd<64>.  For measurements.
-void tb_attn_bwd_variant(int two_per_sm) { g_bwd_two_per_sm = two_per_sm; }
-
-// dqkv[B*T, 3d] from qkv, out, d_out, lse.  delta: fp32 [B*H*T] scratch; dq32: fp32 [B*T*d] scratch (zeroed here).
-int tb_attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, void* dqkv, float* delta, float* dq32, int B, int T,
-                int H, int HD, cudaStream_t stream) {
+// dqkv[B*T, 3d] from qkv, out, d_out, lse.  delta: fp32 [B*H*T], written by the dQ kernel and read by the dK/dV kernel.
+int tb_attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, void* dqkv, float* delta, int B, int T, int H, int HD,
+                cudaStream_t stream) {
   if (T % TILE || (HD != 64 && HD != 128)) return -21;
   if (ensure_error_word()) return -13;
   const int d = H * HD;
@@ -1518,9 +849,8 @@ int tb_attn_bwd(const void* qkv, const void* out, const void* d_out, const float
   rc = make_map(&map_do, d_out, d, rows, d);
   if (rc) return rc;
   const float scale = 1.f / sqrtf((float)HD);
-  if (g_bwd_variant > 0) {
-    const unsigned ctas = (unsigned)((T / TILE) * H * B);
-    tb_note_launch(2);
+  const unsigned ctas = (unsigned)((T / TILE) * H * B);
+  tb_note_launch(2);
 #define LAUNCH_BWD(HD_) \
   do { \
     static bool once = false; \
@@ -1530,39 +860,15 @@ int tb_attn_bwd(const void* qkv, const void* out, const void* d_out, const float
       if (e != cudaSuccess) return (int)e; \
       once = true; \
     } \
-    tb::launch(k_attn_bwd_dq<HD_>, dim3(ctas), dim3(320), BwdDqSmem<HD_>::TOTAL, stream, map_qkv, map_do, (const __nv_bfloat16*)out, \
-               (const __nv_bfloat16*)d_out, lse, delta, (__nv_bfloat16*)dqkv, B, T, H, d, scale, g_err_dev); \
-    tb::launch(k_attn_bwd_dkv<HD_>, dim3(ctas), dim3(320), BwdDkvSmem<HD_>::TOTAL, stream, map_qkv, map_do, lse, (const float*)delta, \
-               (__nv_bfloat16*)dqkv, B, T, H, d, scale, g_err_dev); \
+    cudaError_t e = tb::launch(k_attn_bwd_dq<HD_>, dim3(ctas), dim3(320), BwdDqSmem<HD_>::TOTAL, stream, map_qkv, map_do, (const __nv_bfloat16*)out, \
+                               (const __nv_bfloat16*)d_out, lse, delta, (__nv_bfloat16*)dqkv, B, T, H, d, scale, g_err_dev); \
+    if (e != cudaSuccess) return (int)e; \
+    return (int)tb::launch(k_attn_bwd_dkv<HD_>, dim3(ctas), dim3(320), BwdDkvSmem<HD_>::TOTAL, stream, map_qkv, map_do, lse, (const float*)delta, \
+                           (__nv_bfloat16*)dqkv, B, T, H, d, scale, g_err_dev); \
   } while (0)
-    if (HD == 64) LAUNCH_BWD(64);
-    else LAUNCH_BWD(128);
+  if (HD == 64) LAUNCH_BWD(64);
+  LAUNCH_BWD(128);
 #undef LAUNCH_BWD
-    return (int)cudaGetLastError();
-  }
-  tb_note_launch(4);
-  cudaMemsetAsync(dq32, 0, sizeof(float) * rows * d, stream);
-  k_attn_delta<<<(unsigned)((rows * H + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, delta, T, H, HD, rows);
-  dim3 grid(T / TILE, H, B);
-  if (HD == 64 && g_bwd_two_per_sm) {
-    static bool once = false;
-    if (!once) {
-      cudaFuncSetAttribute(k_attn_bwd64, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::TOTAL);
-      cudaFuncSetAttribute(k_attn_bwd64, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-      once = true;
-    }
-    k_attn_bwd64<<<grid, 256, Bwd64Smem::TOTAL, stream>>>(map_qkv, map_do, lse, delta, dq32, (__nv_bfloat16*)dqkv, T, H, d, scale, g_err_dev);
-  } else if (HD == 64) {
-    static bool once = false;
-    if (!once) { cudaFuncSetAttribute(k_attn_bwd<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::TOTAL); once = true; }
-    k_attn_bwd<64><<<grid, 256, BwdSmem<64>::TOTAL, stream>>>(map_qkv, map_do, lse, delta, dq32, (__nv_bfloat16*)dqkv, T, H, d, scale, g_err_dev);
-  } else {
-    static bool once = false;
-    if (!once) { cudaFuncSetAttribute(k_attn_bwd<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::TOTAL); once = true; }
-    k_attn_bwd<128><<<grid, 256, BwdSmem<128>::TOTAL, stream>>>(map_qkv, map_do, lse, delta, dq32, (__nv_bfloat16*)dqkv, T, H, d, scale, g_err_dev);
-  }
-  k_attn_dq_out<<<592, 256, 0, stream>>>(dq32, (__nv_bfloat16*)dqkv, rows, d);
-  return (int)cudaGetLastError();
 }
 
 }  // extern "C"

@@ -47,14 +47,11 @@ constexpr int EPI_STAGING = 8 * 4096;     // per epilogue warp: a 32-row x 128-b
 
 enum EpilogueFlags {
   EPI_BIAS = 1,        // + bias[col]
-  EPI_GELU = 2,        // out = gelu(v); with aux_out: also write v (pre-activation) there
+  EPI_GELU = 2,        // out = gelu(v); with aux_out: also write gelu'(v) there (what backward multiplies by)
   EPI_RESIDUAL = 4,    // + aux_in[row, col]
-  EPI_DGELU = 8,       // out = v * gelu'(aux_in[row, col])
+  EPI_DGELU = 8,       // out = v * aux_in[row, col]  (aux_in = the gelu'(.) that the forward GEMM saved)
   EPI_ACCUMULATE = 16, // out += v  (gradient accumulation)
   EPI_OUT_F32 = 32,    // out is fp32 (else bf16)
-  EPI_DISCARD = 64,    // measurement aid: drain the accumulator but compute and store nothing
-  EPI_NO_STORE = 128,  // measurement aid: everything except the final global stores
-  EPI_LOAD_ONLY = 256, // measurement aid: read the accumulator from TMEM and do nothing with it
 };
 
 struct GemmArgs {
@@ -63,16 +60,19 @@ struct GemmArgs {
   int flags;
   void* out;
   const __nv_bfloat16* bias;
-  const __nv_bfloat16* aux_in;   // residual or pre-activation, [M, ldc]
-  __nv_bfloat16* aux_out;        // pre-activation out for EPI_GELU, [M, ldc]
+  const __nv_bfloat16* aux_in;   // residual, or the saved gelu' factors, [M, ldc]
+  __nv_bfloat16* aux_out;        // gelu'(pre-activation) out for EPI_GELU, [M, ldc]
   int* error;                    // host-mapped; set to 1 when a wait runs out
   int tma_store;                 // map_out (and map_pre) are valid: bf16 output blocks leave through TMA stores
-  // Split-K (splits > 1): the reduction range is cut into `splits` parts, each (tile, part) is one work item, and part
-  // p stores its fp32 partial tile to partials + p * partial_stride (same [M, ldc] layout as out) with no epilogue;
-  // tb_splitk_reduce() then sums the parts in a fixed order and applies the output conversion.
+  // Split-K (splits > 1): the reduction range is cut into `splits` parts and each (tile, part) is one work item.  Parts
+  // 1 .. splits-1 ("producers") park their raw fp32 accumulator tile in `partials` and raise one flag per epilogue warp;
+  // part 0 ("consumer") adds the parked tiles to its own accumulator, in part order, and runs the ordinary epilogue
+  // (bias, GELU, residual, TMA store ...).  Every CTA works through producer items before consumer items and a
+  // producer never waits, so the scheme cannot deadlock whatever the grid; one kernel, no reduction pass, and the
+  // result does not depend on scheduling.
   int splits;
-  float* partials;
-  long long partial_stride;
+  float* partials;        // [tiles][splits - 1][BM * BN] floats
+  unsigned* split_flags;  // [tiles][splits - 1][8 epilogue warps], zero between launches (the consumer resets them)
 };
 
 // All-gather fused into the GEMM (B operand = a weight whose flat bytes are sharded over the ranks).
@@ -122,12 +122,21 @@ __device__ __forceinline__ bool wait_chunks(const uint32_t* ready, int c_lo, int
   return true;
 }
 
-__device__ __forceinline__ float gelu_exact(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f)); }
-
-__device__ __forceinline__ float gelu_grad(float x) {
-  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752440f));
-  const float pdf = 0.39894228040143267794f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+// Exact (erf) GELU and its derivative from one evaluation:  erf through Abramowitz & Stegun 7.1.26 (absolute error
+// below 1.5e-7, far inside a bf16 rounding), whose exp(-z^2) with z = |x| / sqrt(2) is the very exp(-x^2 / 2) that the
+// density needs.  One ex2 and one reciprocal on the special-function unit plus a dozen FMAs, against erff + expf before;
+// the element-wise epilogue is what bounds the K = 768 GEMMs.
+//   gelu(x)  = x * Phi(x)          Phi(x) = (1 + erf(x / sqrt 2)) / 2
+//   gelu'(x) = Phi(x) + x * phi(x)  phi(x) = exp(-x^2 / 2) / sqrt(2 pi)
+__device__ __forceinline__ void gelu_and_grad(float x, float* g, float* dg) {
+  const float z = fabsf(x) * 0.70710678118654752440f;
+  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
+  const float e = ex2_approx(-0.72134752044448170368f * x * x);  // exp(-x^2 / 2)
+  const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f), 0.254829592f);
+  const float erf_abs = fmaf(-poly, e, 1.f);
+  const float cdf = 0.5f * (1.f + copysignf(erf_abs, x));
+  *g = x * cdf;
+  *dg = fmaf(x * 0.39894228040143267794f, e, cdf);
 }
 
 // ------------------------------------------------------------------------------------------ kernel
@@ -159,14 +168,17 @@ __device__ __forceinline__ void epilogue_chunk_generic(const uint32_t (&raw)[32]
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float a = __bfloat162float(aux[j]);
-          x[j] = (g.flags & EPI_RESIDUAL) ? x[j] + a : x[j] * gelu_grad(a);
+          x[j] = (g.flags & EPI_RESIDUAL) ? x[j] + a : x[j] * a;
         }
       }
       if (g.flags & EPI_GELU) {
+        float dg[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gelu_and_grad(x[j], &x[j], &dg[j]);
         if (g.aux_out != nullptr) {
           __nv_bfloat16 pre[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) pre[j] = __float2bfloat16_rn(x[j]);
+          for (int j = 0; j < 8; ++j) pre[j] = __float2bfloat16_rn(dg[j]);
           if (full8) {
             *reinterpret_cast<uint4*>(g.aux_out + base + v8 * 8) = *reinterpret_cast<const uint4*>(pre);
           } else {
@@ -174,8 +186,6 @@ __device__ __forceinline__ void epilogue_chunk_generic(const uint32_t (&raw)[32]
               if (col + j < g.N) g.aux_out[base + v8 * 8 + j] = pre[j];
           }
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
       }
       if (out_f32) {
         float* o = reinterpret_cast<float*>(out) + base + v8 * 8;
@@ -244,18 +254,19 @@ __device__ __forceinline__ void epilogue_chunk_interior(const uint32_t (&raw)[32
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float a = __bfloat162float(aux[j]);
-        x[j] = (g.flags & EPI_RESIDUAL) ? x[j] + a : x[j] * gelu_grad(a);
+        x[j] = (g.flags & EPI_RESIDUAL) ? x[j] + a : x[j] * a;
       }
     }
     if (g.flags & EPI_GELU) {
+      float dg[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gelu_and_grad(x[j], &x[j], &dg[j]);
       if (g.aux_out != nullptr) {
         __nv_bfloat162 pre[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) pre[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+        for (int j = 0; j < 4; ++j) pre[j] = __floats2bfloat162_rn(dg[2 * j], dg[2 * j + 1]);
         *reinterpret_cast<uint4*>(g.aux_out + base + v8 * 8) = *reinterpret_cast<const uint4*>(pre);
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
     }
     if (out_f32) {
       float* o = reinterpret_cast<float*>(out) + base + v8 * 8;
@@ -293,7 +304,7 @@ __device__ __forceinline__ void epilogue_chunk_interior(const uint32_t (&raw)[32
 //     MMA/TMA traffic of the main loop several times more than their size would suggest.
 //   map == nullptr: the warp reads the block back and stores complete 128-byte lines itself.
 __device__ __forceinline__ void store_block(uint8_t* stage, const uint4 (&v)[8], const CUtensorMap* map, __nv_bfloat16* out, size_t ldc,
-                                            int row0, int rows_valid, int col0, int lane, bool skip) {
+                                            int row0, int rows_valid, int col0, int lane) {
   if (map != nullptr) {
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous store has read the block
     __syncwarp();
@@ -301,7 +312,7 @@ __device__ __forceinline__ void store_block(uint8_t* stage, const uint4 (&v)[8],
     for (int sgm = 0; sgm < 8; ++sgm) *reinterpret_cast<uint4*>(stage + lane * 128 + ((sgm ^ (lane & 7)) << 4)) = v[sgm];
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, then the async proxy's read
     __syncwarp();
-    if (lane == 0 && !skip) {
+    if (lane == 0) {
       asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_u32(stage)),
                    "r"(col0), "r"(row0)
                    : "memory");
@@ -318,8 +329,7 @@ __device__ __forceinline__ void store_block(uint8_t* stage, const uint4 (&v)[8],
   for (int i = 0; i < 8; ++i) {
     const int r = (lane >> 3) + 4 * i;
     const uint4 x = *reinterpret_cast<const uint4*>(stage + r * 128 + ((sgm ^ (r & 7)) << 4));
-    if (r < rows_valid && !skip) *reinterpret_cast<uint4*>(out + (size_t)(row0 + r) * ldc + col0 + sgm * 8) = x;
-    if (skip && x.x == 0x7fc0dead) stage[0] = 1;  // keeps the loads alive when stores are skipped
+    if (r < rows_valid) *reinterpret_cast<uint4*>(out + (size_t)(row0 + r) * ldc + col0 + sgm * 8) = x;
   }
 }
 
@@ -363,23 +373,23 @@ __device__ __forceinline__ void epilogue_pair_interior(const uint32_t (&ra)[32],
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float a = __bfloat162float(aux[j]);
-        x[j] = (g.flags & EPI_DGELU) ? x[j] * gelu_grad(a) : x[j] + a;
+        x[j] = (g.flags & EPI_DGELU) ? x[j] * a : x[j] + a;
       }
     }
     if (g.flags & EPI_GELU) {
+      float dg[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gelu_and_grad(x[j], &x[j], &dg[j]);
       __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&prev[v8]);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) pp[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = gelu_exact(x[j]);
+      for (int j = 0; j < 4; ++j) pp[j] = __floats2bfloat162_rn(dg[2 * j], dg[2 * j + 1]);
     }
     __nv_bfloat162* oo = reinterpret_cast<__nv_bfloat162*>(&outv[v8]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) oo[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
   }
-  const bool skip = g.flags & EPI_NO_STORE;
-  store_block(stage, outv, map_out, reinterpret_cast<__nv_bfloat16*>(out), g.ldc, row0, rows_valid, col0, lane, skip);
-  if (keep_pre) store_block(stage, prev, map_pre, g.aux_out, g.ldc, row0, rows_valid, col0, lane, skip);
+  store_block(stage, outv, map_out, reinterpret_cast<__nv_bfloat16*>(out), g.ldc, row0, rows_valid, col0, lane);
+  if (keep_pre) store_block(stage, prev, map_pre, g.aux_out, g.ldc, row0, rows_valid, col0, lane);
 }
 
 // Tile shapes.  BM = 128: one 128-row accumulator per tile, two of them in TMEM so the next tile's
@@ -416,11 +426,14 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
   const int splits = g.splits > 1 ? g.splits : 1;
-  const int num_tiles = tiles_m * tiles_n * splits;  // work items: item -> output tile (item % tiles), k-part (item / tiles)
+  const int out_tiles = tiles_m * tiles_n;
+  const int num_tiles = out_tiles * splits;  // work items: item -> output tile (item % out_tiles) and k-part
   const int k_blocks_all = (g.K + BK - 1) / BK;
   const int k_per = (k_blocks_all + splits - 1) / splits;
+  // producers (parts 1 .. splits-1) come first in the item order, consumers (part 0) last
+  auto part_of = [&](int item) { return splits == 1 ? 0 : (item < out_tiles * (splits - 1) ? 1 + item / out_tiles : 0); };
   auto k_range = [&](int item, int* kb0, int* kb1) {
-    const int part = item / (tiles_m * tiles_n);
+    const int part = part_of(item);
     *kb0 = part * k_per;
     *kb1 = (part + 1) * k_per < k_blocks_all ? (part + 1) * k_per : k_blocks_all;
   };
@@ -429,7 +442,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
   // Tile t -> (m0, n0).  m runs fastest, so the CTAs sweep one weight panel at a time; with GATHER the panels
   // are visited starting from the one this rank's own shard feeds, the order in which the chunks arrive.
   auto tile_origin = [&](int item, int* m0, int* n0) {
-    const int tile = item % (tiles_m * tiles_n);
+    const int tile = item % out_tiles;
     int n_idx = tile / tiles_m;
     if (GATHER) n_idx = (n_idx + ga.n_start) % tiles_n;
     *m0 = (tile % tiles_m) * BM;
@@ -604,7 +617,29 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       int m0, n0;
       tile_origin(tile, &m0, &n0);
-      void* out = splits > 1 ? (void*)(g.partials + (long long)(tile / (tiles_m * tiles_n)) * g.partial_stride) : g.out;
+      void* out = g.out;
+      const int part = part_of(tile), out_tile = tile % out_tiles;
+      // this warp's share of the parked partial tiles of `out_tile`: [part - 1][chunk][column][row]
+      float* parked = splits > 1 ? g.partials + (size_t)out_tile * (splits - 1) * (BM * BN) : nullptr;
+      unsigned* my_flags = splits > 1 ? g.split_flags + ((size_t)out_tile * (splits - 1)) * 8 + (warp - 2) : nullptr;
+      const int tile_row = half * 128 + quarter * 32 + lane;
+      if (splits > 1 && part == 0) {  // consumer: every producer's matching warp must have parked its share
+        for (int p = 0; p < splits - 1 && ok; ++p) {
+          bool seen = true;
+          if (lane == 0) {
+            const long long start = clock64();
+            while (ld_acquire_gpu(my_flags + p * 8) == 0u) {
+              if (clock64() - start > (1ll << WAIT_LIMIT_CYCLES_SHIFT)) {
+                *g.error = 1;
+                __threadfence_system();
+                seen = false;
+                break;
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, seen ? 1 : 0, 0) != 0;
+        }
+      }
       const uint32_t buf = BM == 128 ? (local_tile & 1) : half;
       const uint32_t acc_phase = BM == 128 ? ((local_tile >> 1) & 1) : (local_tile & 1);
       ok = mbar_wait_warp(&acc_full[buf], acc_phase, g.error);
@@ -620,7 +655,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
       const int c_split = BN == 192 ? 4 : CHUNKS / 2;
       const int c_begin = BM == 128 ? group * c_split : 0;
       const int c_end = BM == 128 ? (group == 0 ? c_split : CHUNKS) : CHUNKS;
-      if (!(g.flags & EPI_DISCARD)) {
+      {
         uint32_t ra[32], rb[32];
         uint8_t* stage = staging + (warp - 2) * 4096;
         const int row0 = m0 + half * 128 + quarter * 32;           // first row of this warp's block
@@ -635,9 +670,25 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
           tmem_ld32(taddr + (c + 1) * 32, rb);
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
-          if (g.flags & EPI_LOAD_ONLY) {
-            if (ra[0] == 0x7fc0dead && rb[31] == 0x7fc0dead) stage[0] = 1;  // keeps the loads alive
-            continue;
+          if (splits > 1) {
+            if (part > 0) {  // producer: park the raw accumulator, column by column (lanes = consecutive rows: coalesced)
+              float* dst = parked + (size_t)(part - 1) * (BM * BN) + (size_t)c * 32 * BM + tile_row;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                __stcg(dst + (size_t)e * BM, __uint_as_float(ra[e]));
+                __stcg(dst + (size_t)(32 + e) * BM, __uint_as_float(rb[e]));
+              }
+              continue;
+            }
+            if (!ok) continue;
+            for (int p = 0; p < splits - 1; ++p) {  // consumer: fold the parked tiles in, in part order
+              const float* src = parked + (size_t)p * (BM * BN) + (size_t)c * 32 * BM + tile_row;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                ra[e] = __float_as_uint(__uint_as_float(ra[e]) + __ldcg(src + (size_t)e * BM));
+                rb[e] = __float_as_uint(__uint_as_float(rb[e]) + __ldcg(src + (size_t)(32 + e) * BM));
+              }
+            }
           }
           if (pair_ok && col0 + 64 <= g.N) {
             epilogue_pair_interior(ra, rb, stage, row, row0, rows_valid, col0, g, out, bias_vec, lane, out_map, pre_map);
@@ -647,6 +698,16 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
             if (interior_rows && col0 + 64 <= g.N) epilogue_chunk_interior(rb, row, col0 + 32, g, out, out_f32, bias_vec);
             else epilogue_chunk_generic(rb, row, col0 + 32, g, out, out_f32);
           }
+        }
+      }
+      if (splits > 1) {
+        if (part > 0) {  // the parked share is complete: publish it
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) st_release_gpu(my_flags + (part - 1) * 8, 1u);
+        } else {         // leave the flags at zero for the next launch that is handed these words
+          __syncwarp();
+          if (lane < splits - 1) my_flags[lane * 8] = 0u;
         }
       }
       tc_fence_before();
@@ -822,7 +883,7 @@ k_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const bool bias_vec = (g.flags & EPI_BIAS) && (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0;
       constexpr int CHUNKS = BN / 32;
       const int c_begin = group * (CHUNKS / 2), c_end = c_begin + CHUNKS / 2;
-      if (!(g.flags & EPI_DISCARD)) {
+      {
         uint32_t ra[32], rb[32];
         uint8_t* stage = staging + (warp - 2) * 4096;
         const int row0 = m0 + quarter * 32;
@@ -835,10 +896,6 @@ k_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           tmem_ld32(taddr + (c + 1) * 32, rb);
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
-          if (g.flags & EPI_LOAD_ONLY) {
-            if (ra[0] == 0x7fc0dead && rb[31] == 0x7fc0dead) stage[0] = 1;
-            continue;
-          }
           if (pair_ok && col0 + 64 <= g.N) {
             epilogue_pair_interior(ra, rb, stage, row, row0, rows_valid, col0, g, g.out, bias_vec, lane, out_map, pre_map);
           } else {
@@ -867,31 +924,6 @@ k_gemm_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
 }
 
-
-// Sums split-K partial tiles (fp32, fixed order) into the bf16 output, four columns per thread.
-__global__ void __launch_bounds__(256) k_splitk_reduce(const float* __restrict__ partials, int splits, long long stride, long long quads,
-                                                        int N, int ldc, __nv_bfloat16* __restrict__ out, bool accumulate) {
-  tb::pdl_enter();
-  const int per_row = ldc / 4;
-  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (long long)gridDim.x * blockDim.x) {
-    const int col = (int)(q % per_row) * 4;
-    if (col >= N) continue;  // row padding
-    float4 acc = *reinterpret_cast<const float4*>(partials + q * 4);
-    for (int p = 1; p < splits; ++p) {
-      const float4 v = *reinterpret_cast<const float4*>(partials + p * stride + q * 4);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    __nv_bfloat16* o = out + q * 4;
-    float r[4] = {acc.x, acc.y, acc.z, acc.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (col + j < N) {
-        if (accumulate) r[j] += __bfloat162float(o[j]);
-        o[j] = __float2bfloat16_rn(r[j]);
-      }
-    }
-  }
-}
 
 // ------------------------------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -1006,45 +1038,60 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   return (int)cudaGetLastError();
 }
 
-// Picks the tile shape with the least estimated time: rounds of tiles over the SMs times the relative
-// cost of one tile.  Measured on B200 (tandem_b200/ops/bench_gemm.py --tile): with a short reduction
-// (K <= 1024) the epilogue sets the pace and the double-buffered 128x256 tile wins; with a long one the
-// 256x256 tile wins (a third less operand traffic per flop) unless it leaves most SMs idle, and the
-// weight-gradient shapes (few output tiles, K = tokens) want 128x128 tiles to fill the machine.
-void choose_tile(int M, int N, int K, int sms, int forced, int* bm, int* bn) {
-  struct Shape { int bm, bn; double cost; };  // cost: relative time of one tile at equal K
-  const Shape shapes[4] = {{256, 256, K <= 1024 ? 5.0 : 4.0}, {128, 256, 2.3}, {128, 128, 1.5}, {128, 192, 2.15}};
-  if (forced >= 0 && forced < 3) {
-    *bm = shapes[forced].bm;
-    *bn = shapes[forced].bn;
-    return;
-  }
-  if (forced == 3 || forced == 4) {  // CTA-pair kernel (bm = 512 marks it): 256 x 256 or 256 x 128 per pair
+// Tile shape and split count with the least estimated time.  A work item is (output tile, k-part); items are dealt
+// round-robin to one CTA per SM, so the time is about  rounds x (k-blocks per part x cost of a k-block + fixed cost of
+// an item [+ cost of parking / folding partial tiles])  with rounds = ceil(items / SMs).  Costs are in units of one
+// 128 x 256 x 64 k-block and were fitted to measurements on B200 (tandem_b200 bench/bench_gemm.py --sweep): the
+// 256 x 256 tile moves a third less operand data per flop, the 128 x 128 tile is bound by shared-memory bandwidth,
+// and an item's fixed cost (pipeline fill, epilogue tail) is worth about five k-blocks.  Splitting is what lets the
+// weight-gradient shapes (few output tiles, K = tokens) and small-batch shapes (few rows per rank) use every SM.
+struct TileShape { int bm, bn; double per_kblock, fixed; };
+constexpr TileShape SHAPES[4] = {{256, 256, 1.75, 9.0}, {128, 256, 1.0, 5.0}, {128, 128, 0.62, 3.5}, {128, 192, 0.8, 4.5}};
+constexpr int MAX_SPLITS = 8;
+
+int g_forced_tile = -1;   // 0: 256x256, 1: 128x256, 2: 128x128, 3 / 4: CTA pair 256x256 / 256x128, 5: 128x192; -1: planned
+int g_forced_splits = 0;  // > 0: that many k-parts (where the reduction is long enough); 0: planned
+
+void plan_gemm(int M, int N, int K, int sms, int* bm, int* bn, int* splits) {
+  const int k_blocks = (K + BK - 1) / BK;
+  auto valid_splits = [&](int s) {  // every part gets at least two k-blocks and none is empty
+    const int per = (k_blocks + s - 1) / s;
+    return s == 1 || (per >= 2 && (s - 1) * per < k_blocks);
+  };
+  if (g_forced_tile == 3 || g_forced_tile == 4) {  // CTA-pair kernel (bm = 512 marks it): no split-K
     *bm = 512;
-    *bn = forced == 3 ? 256 : 128;
+    *bn = g_forced_tile == 3 ? 256 : 128;
+    *splits = 1;
     return;
   }
-  if (forced == 5) {
-    *bm = 128;
-    *bn = 192;
-    return;
-  }
-  double best = 1e30;
-  for (const Shape& s : shapes) {
-    if (s.bn > 128 && N <= 128) continue;
-    const long long tiles = (long long)((M + s.bm - 1) / s.bm) * ((N + s.bn - 1) / s.bn);
-    const long long rounds = (tiles + sms - 1) / sms;
-    const double t = rounds * s.cost;
-    if (t < best - 1e-9) {
-      best = t;
-      *bm = s.bm;
-      *bn = s.bn;
+  double best = 1e300;
+  for (int k = 0; k < 4; ++k) {
+    const TileShape& t = SHAPES[k];
+    const int id = k == 3 ? 5 : k;
+    if (g_forced_tile >= 0 && g_forced_tile != id) continue;
+    if (g_forced_tile < 0 && t.bn > 128 && N <= 128) continue;
+    const long long tiles = (long long)((M + t.bm - 1) / t.bm) * ((N + t.bn - 1) / t.bn);
+    for (int sp = 1; sp <= MAX_SPLITS; ++sp) {
+      if (g_forced_splits > 0 && sp != g_forced_splits && valid_splits(g_forced_splits)) continue;
+      if (!valid_splits(sp)) continue;
+      const long long rounds = (tiles * sp + sms - 1) / sms;
+      const int per = (k_blocks + sp - 1) / sp;
+      const double park = sp > 1 ? 1.5 * t.per_kblock * (sp - 1) : 0.0;  // a parked tile is written once and read once
+      const double cost = rounds * (per * t.per_kblock + t.fixed * t.per_kblock + park);
+      if (cost < best - 1e-9) {
+        best = cost;
+        *bm = t.bm;
+        *bn = t.bn;
+        *splits = sp;
+      }
     }
   }
 }
 
-int g_forced_tile = -1;
-int g_forced_splits = 0;
+// Flag words for split-K, handed out round-robin to launches (a launch that is handed words still in use by an earlier
+// one would need a pool's worth of launches in flight at once); all zero between launches.
+constexpr int SPLIT_FLAG_POOL = 1 << 16;
+__device__ unsigned g_split_flags[SPLIT_FLAG_POOL];
 
 }  // namespace
 
@@ -1059,14 +1106,10 @@ int tb_gemm_error() { return g_error_host != nullptr ? *g_error_host : 0; }
 //   a_mn == 0: A is [M, K] with leading dimension lda (K contiguous); a_mn == 1: A is [K, M], lda (M contiguous).
 //   b_mn == 0: B is [N, K] with leading dimension ldb (K contiguous); b_mn == 1: B is [K, N], ldb (N contiguous).
 // Leading dimensions must be multiples of 8 elements and base pointers 16-byte aligned (TMA).
-int tb_gemm_bf16_splitk(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
-                        int flags, const void* bias, const void* aux_in, void* aux_out, int max_ctas, int splits, void* partials,
-                        cudaStream_t stream) {
+int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int flags,
+                 const void* bias, const void* aux_in, void* aux_out, int max_ctas, void* workspace, long long workspace_bytes,
+                 cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (splits > 1) {
-    const int k_blocks = (K + 63) / 64, k_per = (k_blocks + splits - 1) / splits;
-    if (partials == nullptr || ((uintptr_t)partials & 15) || (ldc & 3) || (splits - 1) * k_per >= k_blocks) return -14;  // no empty part
-  }
   if ((lda & 7) || (ldb & 7) || (((uintptr_t)A | (uintptr_t)B) & 15)) return -12;
   if (g_error_host == nullptr) {
     if (cudaHostAlloc((void**)&g_error_host, 64, cudaHostAllocMapped) != cudaSuccess) return -13;
@@ -1076,14 +1119,30 @@ int tb_gemm_bf16_splitk(const void* A, const void* B, void* out, int M, int N, i
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  int BM = 128, BN = 128;
-  choose_tile(M, N, K, g_sm_count, g_forced_tile, &BM, &BN);
-  if (splits > 1 && (BM == 512 || BN == 192 || g_forced_tile < 0)) {
-    // few output tiles and a long reduction: large single-CTA tiles, the parts fill the machine
-    BM = 128;
-    BN = N > 128 ? 256 : 128;
-  }
+  int BM = 128, BN = 128, splits = 1;
+  plan_gemm(M, N, K, max_ctas > 0 && max_ctas < g_sm_count ? max_ctas : g_sm_count, &BM, &BN, &splits);
   const bool paired = BM == 512;  // a 256 x BN tile shared by a CTA pair: per CTA 128 rows of A, BN/2 rows of B
+  unsigned* split_flags = nullptr;
+  if (splits > 1) {
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const long long need = tiles * (splits - 1) * BM * BN * 4, words = tiles * (splits - 1) * 8;
+    if (workspace == nullptr || workspace_bytes < need || ((uintptr_t)workspace & 15) || words > SPLIT_FLAG_POOL) {
+      splits = 1;  // no room to park partial tiles: compute unsplit (same result up to summation order)
+    } else {
+      static unsigned* pool = nullptr;
+      static int pool_device = -1;
+      static long long next = 0;
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (pool == nullptr || pool_device != dev) {
+        if (cudaGetSymbolAddress((void**)&pool, g_split_flags) != cudaSuccess) return (int)cudaGetLastError();
+        pool_device = dev;
+      }
+      if (next + words > SPLIT_FLAG_POOL) next = 0;
+      split_flags = pool + next;
+      next += words;
+    }
+  }
   CUtensorMap ma, mb;
   int rc;
   if (!a_mn) rc = make_map(&ma, A, K, M, lda, 64, paired ? 128 : BM);
@@ -1093,15 +1152,9 @@ int tb_gemm_bf16_splitk(const void* A, const void* B, void* out, int M, int N, i
   else rc = make_map(&mb, B, N, K, ldb, 64, 64);
   if (rc) return rc;
   CUtensorMap mo, mp;
-  const int tma_store = splits > 1 ? 0 : make_store_maps(&mo, &mp, out, aux_out, M, N, ldc, flags);
-  if (splits > 1) {
-    memset(&mo, 0, sizeof(mo));
-    memset(&mp, 0, sizeof(mp));
-  }
-  // with split-K each part only stores its fp32 partial tile; tb_splitk_reduce applies the rest
-  const int kflags = splits > 1 ? (EPI_OUT_F32 | (flags & (EPI_DISCARD | EPI_NO_STORE | EPI_LOAD_ONLY))) : flags;
-  GemmArgs g{M, N, K, ldc, kflags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev, tma_store,
-             splits > 1 ? splits : 1, (float*)partials, (long long)M * ldc};
+  const int tma_store = make_store_maps(&mo, &mp, out, aux_out, M, N, ldc, flags);
+  GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev, tma_store,
+             splits, (float*)workspace, split_flags};
   tb_note_launch(1);
 #define GO2(BN_) \
   do { \
@@ -1127,45 +1180,36 @@ int tb_gemm_bf16_splitk(const void* A, const void* B, void* out, int M, int N, i
 #undef GO
 }
 
-int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
-                 int flags, const void* bias, const void* aux_in, void* aux_out, int max_ctas, cudaStream_t stream) {
-  return tb_gemm_bf16_splitk(A, B, out, M, N, K, lda, ldb, ldc, a_mn, b_mn, flags, bias, aux_in, aux_out, max_ctas, 1, nullptr, stream);
-}
-
-// How many parts to cut the reduction into (1: do not split).  Splitting pays when the output has too few 128 x 256
-// tiles to occupy even a quarter of the SMs and the reduction is long -- the square weight gradients, whose K is the
-// token count (measured on B200: 768 x 768 x 8192 goes from 52 to 34 us; at 72 tiles the split no longer pays).
-int tb_gemm_splits(int M, int N, int K) {
+// Bytes of workspace tb_gemm_bf16 wants for this problem (0: it will not split the reduction).  The caller allocates
+// at least that much (any stream-ordered allocator will do: the kernel is done with it when it completes) and passes it.
+long long tb_gemm_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (g_sm_count == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  if (g_forced_splits > 0) return g_forced_splits;
-  const int tiles = ((M + 127) / 128) * ((N + (N > 128 ? 255 : 127)) / (N > 128 ? 256 : 128));
-  const int k_blocks = (K + 63) / 64;
-  if (tiles * 4 > g_sm_count || k_blocks < 32) return 1;
-  int s = g_sm_count / tiles;
-  if (s > k_blocks / 16) s = k_blocks / 16;
-  if (s > 8) s = 8;
-  while (s > 1 && (s - 1) * ((k_blocks + s - 1) / s) >= k_blocks) --s;  // no empty part
-  return s < 1 ? 1 : s;
+  int BM = 128, BN = 128, splits = 1;
+  plan_gemm(M, N, K, g_sm_count, &BM, &BN, &splits);
+  if (splits <= 1) return 0;
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return tiles * (splits - 1) * BM * BN * 4;
 }
 
+// What the planner picks: writes {BM (512: CTA pair), BN, splits}.
+void tb_gemm_plan(int M, int N, int K, int* out3) {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  out3[0] = out3[1] = 128;
+  out3[2] = 1;
+  plan_gemm(M, N, K, g_sm_count, &out3[0], &out3[1], &out3[2]);
+}
+
+// Pins the number of k-parts (0: planned) / the tile shape (-1: planned) for every later call.  For tuning and tests.
 void tb_gemm_force_splits(int n) { g_forced_splits = n; }
-
-// out[M, N] (bf16, row stride ldc) = sum over the parts, in order, of partials[p][M, ldc] (fp32); with
-// EPI_ACCUMULATE in `flags`, added to what out holds.
-int tb_splitk_reduce(const void* partials, int splits, int M, int N, int ldc, void* out, int flags, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  const long long quads = (long long)M * (ldc / 4);
-  const int threads = 256;
-  long long blocks = (quads + threads - 1) / threads;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  tb_note_launch(1);
-  return (int)tb::launch(k_splitk_reduce, dim3((int)blocks), dim3(threads), 0, stream, (const float*)partials, splits, (long long)M * ldc, quads, N,
-                         ldc, (__nv_bfloat16*)out, (flags & EPI_ACCUMULATE) != 0);
-}
 
 // out[M, N] = A[M, K] . W[N, K]^T (+ epilogue) where W is gathered by the kernel itself: rank q's shard (peer
 // address shards[q]) holds bytes [shard_lo[q], shard_hi[q]) of the unit's flat buffer; W is the byte range
@@ -1196,7 +1240,7 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
   CUtensorMap mo, mp;
   const int tma_store = make_store_maps(&mo, &mp, out, aux_out, M, N, ldc, flags);
   GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev, tma_store,
-             1, nullptr, 0};
+             1, nullptr, nullptr};
   GatherArgs ga{};
   for (int q = 0; q < n_ranks; ++q) {
     ga.shard[q] = (const char*)shards[q];
@@ -1228,7 +1272,6 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
   return (int)cudaLaunchCooperativeKernel((const void*)kernel, dim3(ctas), dim3(384), params, L::TOTAL, stream);
 }
 
-// Forces a tile shape for every later call (0: 256x256, 1: 128x256, 2: 128x128; -1: automatic).  For tuning.
 void tb_gemm_force_tile(int which) { g_forced_tile = which; }
 
 // 1 (default): bf16 outputs leave through TMA stores; 0: the epilogue warps store them.  For measurements.

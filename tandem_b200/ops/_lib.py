@@ -19,11 +19,10 @@ def lib():
         "tb_gemm_tma_store": ([i], None),
         "tb_gemm_gathered": ([vp, vp, i, i, i, i, i, i, vp, vp, vp, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_longlong),
                               ctypes.POINTER(ctypes.c_longlong), i, vp, ctypes.c_longlong, ctypes.c_longlong, vp, ctypes.c_uint, i, i, vp], i),
-        "tb_gemm_bf16": ([vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp, vp, i, vp], i),
-        "tb_gemm_bf16_splitk": ([vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp, vp, i, i, vp, vp], i),
-        "tb_gemm_splits": ([i, i, i], i),
+        "tb_gemm_bf16": ([vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp, vp, i, vp, ctypes.c_longlong, vp], i),
+        "tb_gemm_workspace_bytes": ([i, i, i], ctypes.c_longlong),
+        "tb_gemm_plan": ([i, i, i, ctypes.POINTER(ctypes.c_int)], None),
         "tb_gemm_force_splits": ([i], None),
-        "tb_splitk_reduce": ([vp, i, i, i, i, vp, i, vp], i),
         "tb_layernorm_fwd": ([vp, vp, vp, vp, vp, vp, i, i, f, vp], i),
         "tb_layernorm_bwd_blocks": ([i], i),
         "tb_layernorm_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp], i),

@@ -1,6 +1,7 @@
 """Causal self-attention over a packed qkv tensor [B, T, 3*dim], on the hand-written
 tcgen05 kernels (tandem_b200/cuda/attention.cu): forward keeps only the output and one
-log-sum-exp per row; backward recomputes the probabilities tile by tile.  Shapes the
+log-sum-exp per row; backward recomputes the probabilities tile by tile in two kernels
+(dQ, then dK and dV), deterministically and without scratch beyond one float per row.  Shapes the
 kernels do not cover (T not a multiple of 128, head dim other than 64 / 128, non-bf16)
 raise rather than fall back silently.  The reference calls torch's
 scaled_dot_product_attention (tandem/model.py:43)."""
@@ -19,14 +20,8 @@ def _fns():
     vp, i = ctypes.c_void_p, ctypes.c_int
     L.tb_attn_fwd.argtypes = [vp, vp, vp, i, i, i, i, vp]
     L.tb_attn_fwd.restype = i
-    L.tb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, vp]
+    L.tb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, vp]
     L.tb_attn_bwd.restype = i
-    L.tb_attn_bwd_variant.argtypes = [i]
-    L.tb_attn_bwd_variant.restype = None
-    L.tb_attn_bwd_kernels.argtypes = [i]
-    L.tb_attn_bwd_kernels.restype = None
-    L.tb_attn_fwd_variant.argtypes = [i]
-    L.tb_attn_fwd_variant.restype = None
     L.tb_attn_error.argtypes = []
     L.tb_attn_error.restype = i
     return L
@@ -58,9 +53,8 @@ class _CausalAttention(torch.autograd.Function):
         d_out = d_out.contiguous()
         dqkv = torch.empty_like(qkv)
         delta = torch.empty(B * heads * T, dtype=torch.float32, device=qkv.device)
-        dq32 = torch.empty(B * T * d, dtype=torch.float32, device=qkv.device)
         check_rc(_fns().tb_attn_bwd(qkv.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr(), dqkv.data_ptr(), delta.data_ptr(),
-                                    dq32.data_ptr(), B, T, heads, d // heads, stream(qkv)), "attention backward")
+                                    B, T, heads, d // heads, stream(qkv)), "attention backward")
         return dqkv, None
 
 
@@ -72,18 +66,3 @@ def causal_attention(qkv, heads):
 def attention_error():
     """True once any attention kernel gave up on a wait (results since then are invalid)."""
     return bool(_fns().tb_attn_error())
-
-
-def backward_variant(two_per_sm):
-    """HD = 64 backward: True runs the kernel shaped for two CTAs per SM, False the one-CTA-per-SM kernel."""
-    _fns().tb_attn_bwd_variant(int(bool(two_per_sm)))
-
-
-def forward_variant(which):
-    """0: the two-pass kernel; 1: warp-specialised single pass, P through shared memory; 2: the same with P kept in TMEM."""
-    _fns().tb_attn_fwd_variant(int(which))
-
-
-def backward_kernels(which):
-    """0: the single backward kernel that accumulates dQ with fp32 atomics; 1: the dQ kernel and the dK/dV kernel."""
-    _fns().tb_attn_bwd_kernels(int(which))

@@ -3,8 +3,8 @@
 `linear` and `mlp` are autograd functions whose forward and both backward
 products (dX, dW) run on the same kernel with different operand layouts, and
 whose element-wise work rides in the GEMM epilogues: bias add, exact GELU
-(with the pre-activation saved for backward), the residual add that follows
-the projection, and GELU's derivative applied to the incoming gradient.
+(which also saves GELU's derivative at each pre-activation, so that backward
+only multiplies by it), and the residual add that follows the projection.
 The reference computes these with nn.Linear / F.gelu / `+` (tandem/model.py:36-58)."""
 
 import torch
@@ -37,20 +37,15 @@ def gemm(a, b, M, N, K, lda, ldb, a_mn, b_mn, flags=0, bias=None, aux_in=None, a
         raise ValueError("aux_in must share the output's row stride")
     if out.dtype == torch.float32:
         flags |= OUT_F32
-    splits = lib().tb_gemm_splits(M, N, K) if flags in (0, ACCUMULATE) and ldc % 4 == 0 else 1
-    if splits > 1:
-        # few output tiles, long reduction (the weight gradients): the reduction is cut into parts that fill the SMs,
-        # each part leaves an fp32 partial product, and one pass sums them in a fixed order into the bf16 output
-        partials = torch.empty((splits, M, ldc), dtype=torch.float32, device=a.device)
-        rc = lib().tb_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), flags,
-                                       None, None, None, 0, splits, partials.data_ptr(), stream(a))
-        if rc == 0:
-            rc = lib().tb_splitk_reduce(partials.data_ptr(), splits, M, N, ldc, out.data_ptr(), flags, stream(a))
-    else:
-        rc = lib().tb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), flags,
-                                bias.data_ptr() if bias is not None else None,
-                                aux_in.data_ptr() if aux_in is not None else None,
-                                aux_out.data_ptr() if aux_out is not None else None, 0, stream(a))
+    # Problems with too few output tiles for the SMs (weight gradients, small per-rank batches) are computed with the
+    # reduction cut into parts inside the one kernel; it parks partial tiles in this workspace.
+    need = lib().tb_gemm_workspace_bytes(M, N, K)
+    workspace = torch.empty(need, dtype=torch.uint8, device=a.device) if need else None
+    rc = lib().tb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), flags,
+                            bias.data_ptr() if bias is not None else None,
+                            aux_in.data_ptr() if aux_in is not None else None,
+                            aux_out.data_ptr() if aux_out is not None else None, 0,
+                            workspace.data_ptr() if workspace is not None else None, need, stream(a))
     if rc in (-11, -12):
         raise RuntimeError(f"gemm: operand not addressable by TMA (M={M} N={N} K={K} lda={lda} ldb={ldb} a_mn={a_mn} b_mn={b_mn} "
                            f"a={a.data_ptr():#x} b={b.data_ptr():#x}): {lib().tb_gemm_last_error().decode()}")
@@ -142,28 +137,36 @@ class _MLP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w1, b1, w2, b2, residual):
         need_bf16(x, w1, b1, w2, b2, residual)
+        if residual is None:
+            raise ValueError("ops.mlp adds its input stream: pass the residual tensor")
+        if w1.shape[0] % 8 or w2.shape[0] % 8:
+            raise ValueError("ops.mlp needs hidden and output widths that are multiples of 8 (16-byte rows)")
         x2, ldx = _rows(x)
         M = x2.shape[0]
-        pre = empty_padded(M, w1.shape[0], torch.bfloat16, x.device)
-        h = _forward(x2, ldx, w1, b1, GELU, None, pre)
+        slope = empty_padded(M, w1.shape[0], torch.bfloat16, x.device)  # gelu'(W1 . x + b1), written by the same epilogue
+        h = _forward(x2, ldx, w1, b1, GELU, None, slope)
         res2 = residual.reshape(-1, residual.shape[-1])
         y = _forward(h, h.stride(0), w2, b2, RESIDUAL, res2)
-        ctx.save_for_backward(x2, w1, w2, pre, h)
+        ctx.save_for_backward(x2, w1, w2, slope, h)
         ctx.ldx, ctx.in_shape = ldx, x.shape
-        return y.view(*x.shape[:-1], w2.shape[0])
+        return y.view(*x.shape[:-1], w2.shape[0]) if y.is_contiguous() else y.unflatten(0, x.shape[:-1])
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w1, w2, pre, h = ctx.saved_tensors
+        x2, w1, w2, slope, h = ctx.saved_tensors
+        need = ctx.needs_input_grad
         dy2, ldy = _rows(dy)
-        dw2 = _grad_weight(dy2, ldy, h, h.stride(0), w2.dtype)
-        db2 = _grad_bias(dy2, ldy)
-        dpre = _grad_input(dy2, ldy, w2, DGELU, pre)  # (dY . W2) * gelu'(pre)
+        dw2 = _grad_weight(dy2, ldy, h, h.stride(0), w2.dtype) if need[3] else None
+        db2 = _grad_bias(dy2, ldy) if need[4] else None
+        dpre = _grad_input(dy2, ldy, w2, DGELU, slope)  # (dY . W2) * gelu'(pre)
         ldp = dpre.stride(0)
-        dw1 = _grad_weight(dpre, ldp, x2, ctx.ldx, w1.dtype)
-        db1 = _grad_bias(dpre, ldp)
-        dx = _grad_input(dpre, ldp, w1).view(ctx.in_shape)
-        return dx, dw1, db1, dw2, db2, dy
+        dw1 = _grad_weight(dpre, ldp, x2, ctx.ldx, w1.dtype) if need[1] else None
+        db1 = _grad_bias(dpre, ldp) if need[2] else None
+        dx = None
+        if need[0]:
+            dx = _grad_input(dpre, ldp, w1)
+            dx = dx.view(ctx.in_shape) if dx.is_contiguous() else dx.unflatten(0, ctx.in_shape[:-1])
+        return dx, dw1, db1, dw2, db2, (dy if need[5] else None)
 
 
 def linear(x, weight, bias=None, gelu=False, residual=None):
