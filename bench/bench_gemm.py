@@ -70,7 +70,7 @@ def block_shapes(M, d):
 
 
 def planned(m, n, k):
-    three = (ctypes.c_int * 3)()
+    three = (ctypes.c_int * 4)()
     lib().tb_gemm_plan(m, n, k, three)
     return {"tile": f"{'pair ' if three[0] == 512 else ''}{256 if three[0] == 512 else three[0]}x{three[1]}", "splits": three[2]}
 
@@ -105,7 +105,7 @@ def main():
                     L.tb_gemm_force_splits(splits)
                     got = planned(m, n, k)
                     if got["splits"] != splits:
-                        continue  # the reduction is too short for that many parts
+                        continue  # no partial last round, or the reduction is too short for that many parts
                     table[f"{TILES[tile]}/{splits}"] = round(graph_us(run, flush, args.reps), 1)
             L.tb_gemm_force_tile(-1)
             L.tb_gemm_force_splits(0)

@@ -506,6 +506,80 @@ k_allgather_nvls(CommCtx c, const char* local, char* mc, long long off, long lon
   comm_barrier(c, sh);
 }
 
+// NVLS reduce-scatter: this rank's chunk [lo, hi) (bytes, multiples of 16) of the buffer is read through the multicast
+// address with multimem.ld_reduce -- the switch returns the sum over all ranks' copies -- scaled, stored into this
+// rank's own copy and handed to the same epilogues as k_reduce_scatter (accumulate into a gradient shard, or the fused
+// AdamW update).  Each rank pulls bytes/n through the switch instead of (n-1)/n * bytes/n from every peer separately.
+template <typename T, int EPI>
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
+k_reduce_scatter_nvls(CommCtx c, const char* mc, char* local, long long lo, long long hi, int smode, float sval, char* acc, AdamSet adams) {
+  __shared__ int sh[2];
+  if (threadIdx.x == 0) sh[1] = 0;
+  constexpr int N = VecOf<T>::N;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  T* acc_out = reinterpret_cast<T*>(acc);
+  AdamArgs adam = adams.a[0];
+  if (EPI == 2 && adam.s_dev != nullptr) adam.s = *adam.s_dev;
+  comm_barrier(c, sh);
+  if (!sh[1]) {
+    const long long nvec = (hi - lo) / 16;
+    for (long long v = tid; v < nvec; v += nth * 4) {
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v + u * nth < nvec) x[u] = multimem_ld_reduce<T>(mc + lo + (v + u * nth) * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long vv = v + u * nth;
+        if (vv < nvec) {
+          float f[N];
+          unpack<T>(x[u], f);
+          if (smode != SCALE_NONE) {
+#pragma unroll
+            for (int e = 0; e < N; ++e) f[e] = scaled(f[e], smode, sval);
+            x[u] = pack<T>(f);
+          }
+          st_vec(local + lo + vv * 16, x[u]);
+          if (EPI != 0) {
+            const T* r = reinterpret_cast<const T*>(&x[u]);  // the value as stored (rounded to T), like the peer-to-peer kernel
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+              const long long j = vv * N + e;
+              if (EPI == 1) acc_out[j] = from_f<T>(__fadd_rn(to_f<T>(acc_out[j]), to_f<T>(r[e])));
+              if (EPI == 2) adam_elem(adam, j, to_f<T>(r[e]));
+            }
+          }
+        }
+      }
+    }
+  }
+  comm_barrier(c, sh);  // every rank has read every copy: the buffers may be refilled
+}
+
+// NVLS broadcast: the root streams its buffer to the multicast address and the switch writes every rank's copy.
+__global__ void __launch_bounds__(TB_COMM_THREADS, 6)
+k_broadcast_nvls(CommCtx c, const char* local, char* mc, long long bytes, int root) {
+  __shared__ int sh[2];
+  if (threadIdx.x == 0) sh[1] = 0;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  comm_barrier(c, sh);  // every rank's buffer may be written from here on
+  if (!sh[1] && comm_rank(c) == root) {
+    const long long nvec = bytes / 16;
+    for (long long v = tid; v < nvec; v += nth * 4) {
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v + u * nth < nvec) x[u] = ld_vec(local + (v + u * nth) * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v + u * nth < nvec) multimem_st(mc + (v + u * nth) * 16, x[u]);
+    }
+  }
+  comm_barrier(c, sh);
+}
+
 // A barrier and nothing else (one block per rank).
 __global__ void k_barrier(CommCtx c) {
   __shared__ int sh[2];
@@ -830,6 +904,46 @@ int tb_reduce_scatter(TbComm* c, void* const* bufs, void* const* local_in, long 
   if (exact) RS(__half, true, 0);
   RS(__half, false, 0);
 #undef RS
+}
+
+// In-switch reduce-scatter: mc / local are the multicast and local addresses of the symmetric buffer; chunk r is
+// elements [offs[r], offs[r+1]).  Every chunk boundary must fall on a 16-byte boundary (the caller checks and otherwise
+// uses tb_reduce_scatter); dtype fp32 or bf16.  acc_out / adam as in tb_reduce_scatter (single entries).
+int tb_reduce_scatter_nvls(TbComm* c, const void* mc, void* local, long long numel, const long long* offs, int dtype, int average,
+                           void* acc_out, const AdamArgs* adam, cudaStream_t stream) {
+  if (numel <= 0) return 0;
+  if (c->emulated || (dtype != TB_F32 && dtype != TB_BF16)) return -4;
+  const int esz = elem_size(dtype);
+  long long most = 0;
+  for (int q = 0; q <= c->ctx.n; ++q)
+    if ((offs[q] * esz) & 15) return -4;
+  for (int q = 0; q < c->ctx.n; ++q) most = offs[q + 1] - offs[q] > most ? offs[q + 1] - offs[q] : most;
+  if (((uintptr_t)mc | (uintptr_t)local) & 15) return -4;
+  int smode;
+  float sval;
+  scale_mode(c->ctx.n, average, &smode, &sval);
+  AdamSet adams{};
+  if (adam != nullptr) adams.a[0] = *adam;
+  const long long lo = offs[c->rank] * esz, hi = offs[c->rank + 1] * esz;
+  const int blocks = blocks_for(c, most * esz, (long long)TB_COMM_THREADS * 16 * 4);
+#define RSN(T, EPI) return (int)launch(c, k_reduce_scatter_nvls<T, EPI>, blocks, stream, c->ctx, (const char*)mc, (char*)local, lo, hi, smode, sval, (char*)acc_out, adams)
+  if (dtype == TB_F32) {
+    if (adam != nullptr) RSN(float, 2);
+    if (acc_out != nullptr) RSN(float, 1);
+    RSN(float, 0);
+  }
+  if (adam != nullptr) RSN(__nv_bfloat16, 2);
+  if (acc_out != nullptr) RSN(__nv_bfloat16, 1);
+  RSN(__nv_bfloat16, 0);
+#undef RSN
+}
+
+// In-switch broadcast of `bytes` (a multiple of 16) from rank `root`.
+int tb_broadcast_nvls(TbComm* c, const void* local, void* mc, long long bytes, int root, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  if (c->emulated || (bytes & 15) || (((uintptr_t)mc | (uintptr_t)local) & 15)) return -4;
+  const int blocks = blocks_for(c, bytes, (long long)TB_COMM_THREADS * 16 * 4);
+  return (int)launch(c, k_broadcast_nvls, blocks, stream, c->ctx, (const char*)local, (char*)mc, bytes, root);
 }
 
 // Every rank's dst receives, for every rank q, len[q] bytes from srcs[q] + src_off[q] at dst + dst_off[q].

@@ -64,15 +64,18 @@ struct GemmArgs {
   __nv_bfloat16* aux_out;        // gelu'(pre-activation) out for EPI_GELU, [M, ldc]
   int* error;                    // host-mapped; set to 1 when a wait runs out
   int tma_store;                 // map_out (and map_pre) are valid: bf16 output blocks leave through TMA stores
-  // Split-K (splits > 1): the reduction range is cut into `splits` parts and each (tile, part) is one work item.  Parts
-  // 1 .. splits-1 ("producers") park their raw fp32 accumulator tile in `partials` and raise one flag per epilogue warp;
-  // part 0 ("consumer") adds the parked tiles to its own accumulator, in part order, and runs the ordinary epilogue
-  // (bias, GELU, residual, TMA store ...).  Every CTA works through producer items before consumer items and a
-  // producer never waits, so the scheme cannot deadlock whatever the grid; one kernel, no reduction pass, and the
-  // result does not depend on scheduling.
-  int splits;
-  float* partials;        // [tiles][splits - 1][BM * BN] floats
-  unsigned* split_flags;  // [tiles][splits - 1][8 epilogue warps], zero between launches (the consumer resets them)
+  // Split-K of the last wave.  Output tiles [0, whole_tiles) -- as many full rounds of one tile per CTA as there are --
+  // are computed whole.  The remaining tiles, too few to occupy the SMs, have their reduction cut into `splits`
+  // parts and each (tile, part) is a work item: parts 1 .. splits-1 ("producers") park their raw fp32 accumulator
+  // tile in `partials` and raise one flag per epilogue warp; part 0 ("consumer") adds the parked tiles to its own
+  // accumulator, in part order, and runs the ordinary epilogue (bias, GELU, residual, TMA store ...).  Items are
+  // ordered whole tiles, producers, consumers; every CTA works through its items in that order and a producer
+  // never waits, so the scheme cannot deadlock whatever the grid.  One kernel, no reduction pass, and the result
+  // does not depend on scheduling.
+  int splits;             // 1: nothing is split
+  int whole_tiles;        // tiles computed by one item each (0 when every tile is split)
+  float* partials;        // [split tile][splits - 1][column][row] floats
+  unsigned* split_flags;  // [split tile][splits - 1][8 epilogue warps], zero between launches (the consumer resets them)
 };
 
 // All-gather fused into the GEMM (B operand = a weight whose flat bytes are sharded over the ranks).
@@ -427,22 +430,24 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
   const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
   const int splits = g.splits > 1 ? g.splits : 1;
   const int out_tiles = tiles_m * tiles_n;
-  const int num_tiles = out_tiles * splits;  // work items: item -> output tile (item % out_tiles) and k-part
+  const int whole = splits > 1 ? g.whole_tiles : out_tiles, tail = out_tiles - whole;
+  const int num_tiles = whole + tail * splits;  // work items: whole tiles, then the tail's producers, then its consumers
   const int k_blocks_all = (g.K + BK - 1) / BK;
   const int k_per = (k_blocks_all + splits - 1) / splits;
-  // producers (parts 1 .. splits-1) come first in the item order, consumers (part 0) last
-  auto part_of = [&](int item) { return splits == 1 ? 0 : (item < out_tiles * (splits - 1) ? 1 + item / out_tiles : 0); };
+  // item -> output tile and k-part (-1: the whole reduction)
+  auto tile_of = [&](int item) { return item < whole ? item : whole + (item - whole) % tail; };
+  auto part_of = [&](int item) { return item < whole ? -1 : (item - whole < tail * (splits - 1) ? 1 + (item - whole) / tail : 0); };
   auto k_range = [&](int item, int* kb0, int* kb1) {
     const int part = part_of(item);
-    *kb0 = part * k_per;
-    *kb1 = (part + 1) * k_per < k_blocks_all ? (part + 1) * k_per : k_blocks_all;
+    *kb0 = part < 0 ? 0 : part * k_per;
+    *kb1 = part < 0 || (part + 1) * k_per > k_blocks_all ? k_blocks_all : (part + 1) * k_per;
   };
   constexpr uint32_t ACC_COLS = BN == 192 ? 256 : BN;  // column stride between the two accumulators
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;         // 256 or 512: a power of two
   // Tile t -> (m0, n0).  m runs fastest, so the CTAs sweep one weight panel at a time; with GATHER the panels
   // are visited starting from the one this rank's own shard feeds, the order in which the chunks arrive.
   auto tile_origin = [&](int item, int* m0, int* n0) {
-    const int tile = item % out_tiles;
+    const int tile = tile_of(item);
     int n_idx = tile / tiles_m;
     if (GATHER) n_idx = (n_idx + ga.n_start) % tiles_n;
     *m0 = (tile % tiles_m) * BM;
@@ -618,12 +623,12 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
       int m0, n0;
       tile_origin(tile, &m0, &n0);
       void* out = g.out;
-      const int part = part_of(tile), out_tile = tile % out_tiles;
-      // this warp's share of the parked partial tiles of `out_tile`: [part - 1][chunk][column][row]
-      float* parked = splits > 1 ? g.partials + (size_t)out_tile * (splits - 1) * (BM * BN) : nullptr;
-      unsigned* my_flags = splits > 1 ? g.split_flags + ((size_t)out_tile * (splits - 1)) * 8 + (warp - 2) : nullptr;
+      const int part = part_of(tile), split_tile = tile_of(tile) - whole;
+      // this warp's share of the parked partial tiles of its output tile: [part - 1][column][row]
+      float* parked = part >= 0 ? g.partials + (size_t)split_tile * (splits - 1) * (BM * BN) : nullptr;
+      unsigned* my_flags = part >= 0 ? g.split_flags + ((size_t)split_tile * (splits - 1)) * 8 + (warp - 2) : nullptr;
       const int tile_row = half * 128 + quarter * 32 + lane;
-      if (splits > 1 && part == 0) {  // consumer: every producer's matching warp must have parked its share
+      if (part == 0) {  // consumer: every producer's matching warp must have parked its share
         for (int p = 0; p < splits - 1 && ok; ++p) {
           bool seen = true;
           if (lane == 0) {
@@ -670,23 +675,29 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
           tmem_ld32(taddr + (c + 1) * 32, rb);
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
-          if (splits > 1) {
-            if (part > 0) {  // producer: park the raw accumulator, column by column (lanes = consecutive rows: coalesced)
-              float* dst = parked + (size_t)(part - 1) * (BM * BN) + (size_t)c * 32 * BM + tile_row;
+          if (part > 0) {  // producer: park the raw accumulator column by column (lanes = consecutive rows: full 128-byte lines)
+            float* dst = parked + (size_t)(part - 1) * (BM * BN) + (size_t)c * 32 * BM + tile_row;
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                __stcg(dst + (size_t)e * BM, __uint_as_float(ra[e]));
-                __stcg(dst + (size_t)(32 + e) * BM, __uint_as_float(rb[e]));
-              }
-              continue;
+            for (int e = 0; e < 32; ++e) {
+              __stcg(dst + (size_t)e * BM, __uint_as_float(ra[e]));
+              __stcg(dst + (size_t)(32 + e) * BM, __uint_as_float(rb[e]));
             }
+            continue;
+          }
+          if (part == 0) {  // consumer: fold the parked tiles in, in part order
             if (!ok) continue;
-            for (int p = 0; p < splits - 1; ++p) {  // consumer: fold the parked tiles in, in part order
+            for (int p = 0; p < splits - 1; ++p) {
               const float* src = parked + (size_t)p * (BM * BN) + (size_t)c * 32 * BM + tile_row;
+              float va[32], vb[32];
 #pragma unroll
               for (int e = 0; e < 32; ++e) {
-                ra[e] = __float_as_uint(__uint_as_float(ra[e]) + __ldcg(src + (size_t)e * BM));
-                rb[e] = __float_as_uint(__uint_as_float(rb[e]) + __ldcg(src + (size_t)(32 + e) * BM));
+                va[e] = __ldcg(src + (size_t)e * BM);
+                vb[e] = __ldcg(src + (size_t)(32 + e) * BM);
+              }
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                ra[e] = __float_as_uint(__uint_as_float(ra[e]) + va[e]);
+                rb[e] = __float_as_uint(__uint_as_float(rb[e]) + vb[e]);
               }
             }
           }
@@ -700,15 +711,13 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
           }
         }
       }
-      if (splits > 1) {
-        if (part > 0) {  // the parked share is complete: publish it
-          __threadfence();
-          __syncwarp();
-          if (lane == 0) st_release_gpu(my_flags + (part - 1) * 8, 1u);
-        } else {         // leave the flags at zero for the next launch that is handed these words
-          __syncwarp();
-          if (lane < splits - 1) my_flags[lane * 8] = 0u;
-        }
+      if (part > 0) {  // the parked share is complete: publish it
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(my_flags + (part - 1) * 8, 1u);
+      } else if (part == 0) {  // leave the flags at zero for the next launch that is handed these words
+        __syncwarp();
+        if (lane < splits - 1) my_flags[lane * 8] = 0u;
       }
       tc_fence_before();
       __syncwarp();
@@ -997,7 +1006,8 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * g.splits;
+  const int out_tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  const int tiles = g.splits > 1 ? g.whole_tiles + (out_tiles - g.whole_tiles) * g.splits : out_tiles;
   int ctas = tiles < g_sm_count ? tiles : g_sm_count;
   if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
   return (int)tb::launch(kernel, dim3(ctas), dim3(L::THREADS), L::TOTAL, stream, ma, mb, mo, mp, g, GatherArgs{});
@@ -1038,54 +1048,58 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   return (int)cudaGetLastError();
 }
 
-// Tile shape and split count with the least estimated time.  A work item is (output tile, k-part); items are dealt
-// round-robin to one CTA per SM, so the time is about  rounds x (k-blocks per part x cost of a k-block + fixed cost of
-// an item [+ cost of parking / folding partial tiles])  with rounds = ceil(items / SMs).  Costs are in units of one
-// 128 x 256 x 64 k-block and were fitted to measurements on B200 (tandem_b200 bench/bench_gemm.py --sweep): the
-// 256 x 256 tile moves a third less operand data per flop, the 128 x 128 tile is bound by shared-memory bandwidth,
-// and an item's fixed cost (pipeline fill, epilogue tail) is worth about five k-blocks.  Splitting is what lets the
-// weight-gradient shapes (few output tiles, K = tokens) and small-batch shapes (few rows per rank) use every SM.
-struct TileShape { int bm, bn; double per_kblock, fixed; };
-constexpr TileShape SHAPES[4] = {{256, 256, 1.75, 9.0}, {128, 256, 1.0, 5.0}, {128, 128, 0.62, 3.5}, {128, 192, 0.8, 4.5}};
+// Tile shape and tail split with the least estimated time.  One CTA per SM takes output tiles round-robin; the last,
+// partial round leaves SMs idle, so the tiles of that round ("tail") may have their reduction cut into parts that are
+// spread over the idle SMs (GemmArgs).  The estimate, in microseconds, is
+//     start-up + full rounds x (k-blocks x per-k-block + per-tile) + [tail: k-blocks per part x per-k-block + per-tile + fold]
+// with constants fitted to sweeps on B200 (bench/bench_gemm.py --sweep, CUDA-graph timing, cold L2): a k-block costs
+// 0.34 - 0.43 us on the 128-row tiles whatever their width (the main loop is bound by bytes in flight / load latency,
+// not by the tensor pipe) and 0.77 us on the 256 x 256 tile, whose two accumulators fill TMEM so that its epilogue
+// (about 5 us) cannot overlap the next tile; a kernel's start-up and drain cost about 5 us; folding parked partial
+// tiles costs about 6 us plus 9 us per extra part (producer drain, flag, dependent loads).  With those prices the
+// split only pays for the square weight gradients (a few dozen output tiles, K = tokens).
+struct TileShape { int id, bm, bn; double per_kblock, per_tile; };
+constexpr TileShape SHAPES[4] = {{0, 256, 256, 0.77, 5.3}, {1, 128, 256, 0.43, 0.5}, {2, 128, 128, 0.34, 0.6}, {5, 128, 192, 0.41, 1.0}};
 constexpr int MAX_SPLITS = 8;
+constexpr double START_US = 5.0, FOLD_US = 6.0, FOLD_PART_US = 9.0, FOLD_US_PER_MB = 0.35;
 
 int g_forced_tile = -1;   // 0: 256x256, 1: 128x256, 2: 128x128, 3 / 4: CTA pair 256x256 / 256x128, 5: 128x192; -1: planned
-int g_forced_splits = 0;  // > 0: that many k-parts (where the reduction is long enough); 0: planned
+int g_forced_splits = 0;  // > 0: that many k-parts for the tail (where the reduction is long enough); 0: planned
 
-void plan_gemm(int M, int N, int K, int sms, int* bm, int* bn, int* splits) {
+struct GemmPlan { int bm, bn, splits, whole_tiles; };
+
+GemmPlan plan_gemm(int M, int N, int K, int ctas) {
   const int k_blocks = (K + BK - 1) / BK;
+  if (g_forced_tile == 3 || g_forced_tile == 4) return {512, g_forced_tile == 3 ? 256 : 128, 1, 0};  // CTA-pair kernel (bm = 512 marks it)
   auto valid_splits = [&](int s) {  // every part gets at least two k-blocks and none is empty
     const int per = (k_blocks + s - 1) / s;
     return s == 1 || (per >= 2 && (s - 1) * per < k_blocks);
   };
-  if (g_forced_tile == 3 || g_forced_tile == 4) {  // CTA-pair kernel (bm = 512 marks it): no split-K
-    *bm = 512;
-    *bn = g_forced_tile == 3 ? 256 : 128;
-    *splits = 1;
-    return;
-  }
-  double best = 1e300;
-  for (int k = 0; k < 4; ++k) {
-    const TileShape& t = SHAPES[k];
-    const int id = k == 3 ? 5 : k;
-    if (g_forced_tile >= 0 && g_forced_tile != id) continue;
+  GemmPlan best{128, 128, 1, 0};
+  double best_us = 1e300;
+  for (const TileShape& t : SHAPES) {
+    if (g_forced_tile >= 0 && g_forced_tile != t.id) continue;
     if (g_forced_tile < 0 && t.bn > 128 && N <= 128) continue;
     const long long tiles = (long long)((M + t.bm - 1) / t.bm) * ((N + t.bn - 1) / t.bn);
+    const long long rounds = tiles / ctas, tail = tiles % ctas;
+    const double whole_us = rounds * (k_blocks * t.per_kblock + t.per_tile);
     for (int sp = 1; sp <= MAX_SPLITS; ++sp) {
-      if (g_forced_splits > 0 && sp != g_forced_splits && valid_splits(g_forced_splits)) continue;
-      if (!valid_splits(sp)) continue;
-      const long long rounds = (tiles * sp + sms - 1) / sms;
-      const int per = (k_blocks + sp - 1) / sp;
-      const double park = sp > 1 ? 1.5 * t.per_kblock * (sp - 1) : 0.0;  // a parked tile is written once and read once
-      const double cost = rounds * (per * t.per_kblock + t.fixed * t.per_kblock + park);
-      if (cost < best - 1e-9) {
-        best = cost;
-        *bm = t.bm;
-        *bn = t.bn;
-        *splits = sp;
+      if (!valid_splits(sp) || (sp > 1 && (tail == 0 || tail * sp > ctas))) continue;
+      if (g_forced_splits > 0 && sp != g_forced_splits && tail > 0 && valid_splits(g_forced_splits) && tail * g_forced_splits <= ctas) continue;
+      double us = START_US + whole_us;
+      if (tail > 0) {
+        const int per = (k_blocks + sp - 1) / sp;
+        us += per * t.per_kblock + t.per_tile;
+        if (sp > 1) us += FOLD_US + FOLD_PART_US * (sp - 1) + FOLD_US_PER_MB * (double)tail * (sp - 1) * t.bm * t.bn * 4 / 1e6;
+      }
+      if (us < best_us - 1e-9) {
+        best_us = us;
+        best = {t.bm, t.bn, sp, (int)(rounds * ctas)};
       }
     }
   }
+  if (best.splits == 1) best.whole_tiles = 0;
+  return best;
 }
 
 // Flag words for split-K, handed out round-robin to launches (a launch that is handed words still in use by an earlier
@@ -1119,13 +1133,15 @@ int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, i
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  int BM = 128, BN = 128, splits = 1;
-  plan_gemm(M, N, K, max_ctas > 0 && max_ctas < g_sm_count ? max_ctas : g_sm_count, &BM, &BN, &splits);
+  const int ctas = max_ctas > 0 && max_ctas < g_sm_count ? max_ctas : g_sm_count;
+  const GemmPlan plan = plan_gemm(M, N, K, ctas);
+  const int BM = plan.bm, BN = plan.bn;
+  int splits = plan.splits;
   const bool paired = BM == 512;  // a 256 x BN tile shared by a CTA pair: per CTA 128 rows of A, BN/2 rows of B
   unsigned* split_flags = nullptr;
   if (splits > 1) {
-    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const long long need = tiles * (splits - 1) * BM * BN * 4, words = tiles * (splits - 1) * 8;
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN), tail = tiles - plan.whole_tiles;
+    const long long need = tail * (splits - 1) * BM * BN * 4, words = tail * (splits - 1) * 8;
     if (workspace == nullptr || workspace_bytes < need || ((uintptr_t)workspace & 15) || words > SPLIT_FLAG_POOL) {
       splits = 1;  // no room to park partial tiles: compute unsplit (same result up to summation order)
     } else {
@@ -1154,7 +1170,7 @@ int tb_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, i
   CUtensorMap mo, mp;
   const int tma_store = make_store_maps(&mo, &mp, out, aux_out, M, N, ldc, flags);
   GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev, tma_store,
-             splits, (float*)workspace, split_flags};
+             splits, splits > 1 ? plan.whole_tiles : 0, (float*)workspace, split_flags};
   tb_note_launch(1);
 #define GO2(BN_) \
   do { \
@@ -1189,23 +1205,24 @@ long long tb_gemm_workspace_bytes(int M, int N, int K) {
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  int BM = 128, BN = 128, splits = 1;
-  plan_gemm(M, N, K, g_sm_count, &BM, &BN, &splits);
-  if (splits <= 1) return 0;
-  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  return tiles * (splits - 1) * BM * BN * 4;
+  const GemmPlan plan = plan_gemm(M, N, K, g_sm_count);
+  if (plan.splits <= 1) return 0;
+  const long long tiles = (long long)((M + plan.bm - 1) / plan.bm) * ((N + plan.bn - 1) / plan.bn);
+  return (tiles - plan.whole_tiles) * (plan.splits - 1) * plan.bm * plan.bn * 4;
 }
 
-// What the planner picks: writes {BM (512: CTA pair), BN, splits}.
-void tb_gemm_plan(int M, int N, int K, int* out3) {
+// What the planner picks: writes {BM (512: CTA pair), BN, parts the tail tiles are cut into, tiles computed whole}.
+void tb_gemm_plan(int M, int N, int K, int* out4) {
   if (g_sm_count == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  out3[0] = out3[1] = 128;
-  out3[2] = 1;
-  plan_gemm(M, N, K, g_sm_count, &out3[0], &out3[1], &out3[2]);
+  const GemmPlan plan = plan_gemm(M, N, K, g_sm_count);
+  out4[0] = plan.bm;
+  out4[1] = plan.bn;
+  out4[2] = plan.splits;
+  out4[3] = plan.whole_tiles;
 }
 
 // Pins the number of k-parts (0: planned) / the tile shape (-1: planned) for every later call.  For tuning and tests.
@@ -1240,7 +1257,7 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
   CUtensorMap mo, mp;
   const int tma_store = make_store_maps(&mo, &mp, out, aux_out, M, N, ldc, flags);
   GemmArgs g{M, N, K, ldc, flags, out, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)aux_in, (__nv_bfloat16*)aux_out, g_error_dev, tma_store,
-             1, nullptr, nullptr};
+             1, 0, nullptr, nullptr};
   GatherArgs ga{};
   for (int q = 0; q < n_ranks; ++q) {
     ga.shard[q] = (const char*)shards[q];

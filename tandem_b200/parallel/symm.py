@@ -104,6 +104,8 @@ def cuda_lib():
         "tb_all_reduce": ([vp, pp, pp, pp, ll, i, i, i, i, vp], i),
         "tb_all_reduce_nvls": ([vp, vp, ll, i, i, vp], i),
         "tb_all_gather_nvls": ([vp, vp, vp, ll, ll, ll, vp], i),
+        "tb_reduce_scatter_nvls": ([vp, vp, vp, ll, pll, i, i, vp, ctypes.POINTER(AdamArgs), vp], i),
+        "tb_broadcast_nvls": ([vp, vp, vp, ll, i, vp], i),
         "tb_reduce_scatter": ([vp, pp, pp, ll, pll, i, i, i, pp, ctypes.POINTER(AdamArgs), vp], i),
         "tb_gather_pull": ([vp, pp, pp, pll, pll, pll, pp, i, ll, vp], i),
         "tb_adamw": ([vp, vp, i, vp, vp, vp, ll, ctypes.POINTER(f), i, f, vp], i),
@@ -480,7 +482,18 @@ class SymmetricComm:
         acc = _ptr_array([accumulate_into.data_ptr()]) if accumulate_into is not None and accumulate_into.numel() else None
         adam_p = ctypes.pointer(adam) if adam is not None and offs[self.rank + 1] > offs[self.rank] else None
         if flat.numel():
-            if peers is not None:
+            esz = flat.element_size()
+            nbytes_ = flat.numel() * esz
+            mc = self._multicast_of(flat) if peers is not None and self.n > 1 and flat.dtype in (torch.float32, torch.bfloat16) else 0
+            want_nvls = self.algo == ALGO["nvls"] or (self.algo == ALGO["auto"] and self.n >= self.nvls_min_ranks
+                                                      and nbytes_ >= self.nvls_min_bytes and not self.exact16
+                                                      and not torch.are_deterministic_algorithms_enabled())
+            if mc and want_nvls and mc % 16 == 0 and flat.data_ptr() % 16 == 0 and all((o * esz) % 16 == 0 for o in offs):
+                # the switch adds the ranks' copies of this rank's chunk (multimem.ld_reduce); same epilogues
+                one = accumulate_into.data_ptr() if accumulate_into is not None and accumulate_into.numel() else None
+                check_rc(self.lib.tb_reduce_scatter_nvls(self._launch_comm, mc, flat.data_ptr(), flat.numel(), _ll_array(offs), code,
+                                                         int(average), one, adam_p, s), "reduce_scatter (NVLS)")
+            elif peers is not None:
                 check_rc(self.lib.tb_reduce_scatter(self._launch_comm, _ptr_array(peers), None, flat.numel(), _ll_array(offs), code,
                                                     int(average), int(self.exact16), acc, adam_p, s), "reduce_scatter")
             else:
@@ -565,7 +578,14 @@ class SymmetricComm:
         total = flat.numel() * flat.element_size()
         peers = self._peers_of(flat)
         if total and self.n > 1:
-            if peers is not None:
+            mc = self._multicast_of(flat) if peers is not None else 0
+            want_nvls = self.algo == ALGO["nvls"] or (self.algo == ALGO["auto"] and self.n >= self.nvls_min_ranks
+                                                      and total >= self.nvls_min_bytes)
+            if mc and want_nvls and total % 16 == 0 and mc % 16 == 0 and flat.data_ptr() % 16 == 0:
+                # the root writes once to the multicast address; the switch replicates into every rank's copy
+                check_rc(self.lib.tb_broadcast_nvls(self._launch_comm, flat.data_ptr(), mc, total, root,
+                                                    self._launch_stream.cuda_stream), "broadcast (NVLS)")
+            elif peers is not None:
                 if total >= (1 << 20) and self.n > 2:
                     # scatter + all-gather: rank q pulls slice q from the root, then everyone pulls the other
                     # slices from their new holders, so the root sends each byte once instead of n-1 times.

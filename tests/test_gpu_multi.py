@@ -12,7 +12,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+needs3 = pytest.mark.skipif(torch.cuda.device_count() < 3, reason="needs 3 GPUs")
 needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+needs8 = pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
 
 
 def data(rank, n, dtype, seed=0):
@@ -78,6 +80,73 @@ def test_collectives_on_four_gpus():
     from tandem_b200 import launch
 
     assert launch(gpu_collectives, 4, device="cuda") == [0, 1, 2, 3]
+
+
+@needs8
+def test_collectives_on_eight_gpus():
+    from tandem_b200 import launch
+
+    assert launch(gpu_collectives, 8, device="cuda") == list(range(8))
+
+
+def odd_group_collectives(g):
+    """A group size that is not a power of two: the kernels' predicated (runtime rank count) paths, 16-bit types
+    included, and the mean as a multiply by float(1/3) per operand (what ATen's div_ by a host scalar does on CUDA).
+    Behaviours of tests/test_engine_cuda.py:84-96 of the reference (world 3, n = 10,007, f32 / f16 / bf16 / int64)."""
+    r, w, dev = g.rank, g.size, g.device
+    n = 10_007
+    for dtype in (torch.float32, torch.float16, torch.bfloat16, torch.int64):
+        want = sum(data(q, n, dtype).double() for q in range(w))
+        for registered in (False, True):
+            x = g.empty(n, dtype) if registered else torch.empty(n, dtype=dtype, device=dev)
+            x.copy_(data(r, n, dtype))
+            g.all_reduce(x)
+            assert torch.equal(x.double().cpu(), want), ("all_reduce", dtype, registered)
+            if registered:
+                g.release(x)
+        sizes = [n // w] * w
+        sizes[0] += n - sum(sizes)
+        lo = sum(sizes[:r])
+        x = data(r, n, dtype).to(dev)
+        mine = g.reduce_scatter(x, sizes)
+        assert torch.equal(mine.double().cpu(), want[lo:lo + sizes[r]]), ("reduce_scatter", dtype)
+        x = torch.zeros(n, dtype=dtype, device=dev)
+        x[lo:lo + sizes[r]] = want.to(dtype)[lo:lo + sizes[r]].to(dev)
+        g.all_gather(x, sizes)
+        assert torch.equal(x.cpu(), want.to(dtype)), ("all_gather", dtype)
+        x = data(r, n, dtype, seed=3).to(dev)
+        g.broadcast(x, root=1)
+        assert torch.equal(x.cpu(), data(1, n, dtype, seed=3)), ("broadcast", dtype)
+        if dtype.is_floating_point:
+            x = (torch.randn(n, generator=torch.Generator().manual_seed(r)) * 3).to(dtype).to(dev)
+            every = [(torch.randn(n, generator=torch.Generator().manual_seed(q)) * 3).to(dtype) for q in range(w)]
+            g.all_reduce(x, op="avg")
+            exact = sum(t.double() for t in every) / w
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            assert torch.allclose(x.double().cpu(), exact, rtol=tol, atol=tol), ("avg", dtype)
+            if dtype == torch.float32:  # bit for bit: each operand times float(1/3), folded in ring order for its chunk
+                third = torch.tensor(1.0 / 3.0, dtype=torch.float32)
+                chunks = [t.float() * third for t in every]
+                bounds = [0]
+                for q in range(w):
+                    bounds.append(bounds[-1] + n // w + (1 if q < n % w else 0))
+                model = torch.empty(n)
+                for c in range(w):
+                    a, b = bounds[c], bounds[c + 1]
+                    acc = chunks[(c + 1) % w][a:b].clone()
+                    for j in range(2, w + 1):
+                        acc = acc + chunks[(c + j) % w][a:b]
+                    model[a:b] = acc
+                assert torch.equal(x.cpu(), model), "avg is not the ring-ordered sum of operands scaled by float(1/n)"
+    g.check()
+    return r
+
+
+@needs3
+def test_collectives_on_three_gpus():
+    from tandem_b200 import launch
+
+    assert launch(odd_group_collectives, 3, device="cuda") == [0, 1, 2]
 
 
 # ------------------------------------------------------------------ training equality
@@ -416,3 +485,138 @@ def test_zero2_adamw_fused_into_reduce_scatter_matches_unfused():
     for a, b in zip(fused[0][0], plain[0][0]):
         assert abs(a - b) < 1e-4, (fused[0][0], plain[0][0])
     assert torch.allclose(fused[0][1], plain[0][1], rtol=1e-5, atol=1e-6), (fused[0][1] - plain[0][1]).abs().max()
+
+
+def ddp_optimizer_rank(g, sharded):
+    """DDP on the torch kernels in fp32 with this library's bucket optimizers: replicated (one AdamW kernel per bucket)
+    or sharded (reduce-scatter with the AdamW update in its epilogue, then all-gather of the parameters)."""
+    from tandem_b200.data import synthetic
+    from tandem_b200.ddp import DDP, BucketAdamW, ShardedBucketAdamW
+    from tandem_b200.model import GPT
+
+    _setup_deterministic()
+    torch.manual_seed(0)
+    cfg = _cfg()
+    text = synthetic(20_000)
+    model = GPT(cfg).to(g.device)
+    wrapped = DDP(model, g, bucket_bytes=64 << 10, rebuild=False)
+    opt = (ShardedBucketAdamW if sharded else BucketAdamW)(wrapped, lr=3e-3, weight_decay=0.1)
+    losses = []
+    for step in range(STEPS):
+        x, y = text.batch(step, BATCH, cfg.seq, rank=g.rank, world=g.size, device=g.device)
+        loss = wrapped(x, y)
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.item())
+    g.check()
+    return losses, torch.cat([p.detach().reshape(-1) for p in model.parameters()]).cpu(), opt.state_bytes()
+
+
+@needs2
+def test_ddp_with_the_optimizer_sharded_into_the_reduce_scatter():
+    from tandem_b200 import launch
+
+    sharded = launch(ddp_optimizer_rank, 2, True, device="cuda")
+    replicated = launch(ddp_optimizer_rank, 2, False, device="cuda")
+    assert torch.equal(sharded[0][1], sharded[1][1])  # every rank ends with the same parameters
+    assert sharded[0][0] == replicated[0][0], (sharded[0][0], replicated[0][0])
+    assert torch.equal(sharded[0][1], replicated[0][1]), (sharded[0][1] - replicated[0][1]).abs().max()
+    assert sharded[0][2] * 2 <= replicated[0][2] + 64  # half the optimizer state per rank
+
+
+def graphed_rank(g, strategy, graphed):
+    """A sharded strategy on the hand-written kernels in bf16, stepped eagerly or replayed from one CUDA graph."""
+    from tandem_b200.data import synthetic
+    from tandem_b200.ddp import DDP, ShardedBucketAdamW
+    from tandem_b200.model import Config, GPT
+    from tandem_b200.optim import ShardedAdamW
+    from tandem_b200.parallel.graph import GraphedStep
+    from tandem_b200.zero import FSDP, ZeRO
+
+    torch.manual_seed(0)
+    cfg = Config(seq=128, layers=2, heads=2, dim=128, kernels="b200")
+    text = synthetic(50_000)
+    model = GPT(cfg).to(g.device).bfloat16()
+    if strategy == "ddp":
+        wrapped = DDP(model, g, bucket_bytes=256 << 10, rebuild=False)
+        closer = ShardedBucketAdamW(wrapped, lr=1e-3, weight_decay=0.1)
+    elif strategy == "zero2":
+        wrapped = closer = ZeRO(model, g, 2, ShardedAdamW(lr=1e-3, weight_decay=0.1), 256 << 10, fused_step=True, capturable=graphed)
+    else:
+        wrapped = closer = FSDP(model, g, ShardedAdamW(lr=1e-3, weight_decay=0.1), capturable=graphed)
+    batches = [text.batch(step, 8, cfg.seq, rank=g.rank, world=g.size, device=g.device) for step in range(8)]
+    losses = []
+    if graphed:
+        step_fn = GraphedStep(wrapped, closer, *batches[0], warmup=3)  # three eager steps on batch 0, then the capture
+        for x, y in batches[3:]:
+            losses.append(step_fn(x, y).item())
+    else:
+        for k, (x, y) in enumerate([batches[0]] * 3 + [batches[0]] + batches[3:]):  # the same sequence of batches
+            loss = wrapped(x, y)
+            loss.backward()
+            closer.step()
+            closer.zero_grad()
+            if k >= 4:
+                losses.append(loss.item())
+    g.check()
+    return losses
+
+
+@needs2
+@pytest.mark.parametrize("strategy", ["ddp", "zero2", "zero3"])
+def test_steps_replayed_from_a_cuda_graph_track_eager_steps(strategy):
+    from tandem_b200 import launch
+
+    eager = launch(graphed_rank, 2, strategy, False, device="cuda")
+    replay = launch(graphed_rank, 2, strategy, True, device="cuda")
+    for r in range(2):
+        assert len(eager[r]) == len(replay[r]) == 5
+        for a, b in zip(eager[r], replay[r]):
+            assert a == a and abs(a - b) < 2e-2, (strategy, eager[r], replay[r])
+
+
+def ddp_eight_rank(g):
+    """DDP with many small spans in flight on eight GPUs; every rank must end with the same weights, and they must
+    track one process that sees the whole batch (the mean over eight ranks is associated differently)."""
+    from tandem_b200.data import synthetic
+    from tandem_b200.ddp import DDP
+    from tandem_b200.model import GPT
+
+    _setup_deterministic()
+    torch.manual_seed(0)
+    cfg = _cfg()
+    text = synthetic(20_000)
+    model = GPT(cfg).to(g.device)
+    wrapped = DDP(model, g, bucket_bytes=64 << 10)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3, weight_decay=0.1, foreach=False)
+    for step in range(STEPS):
+        x, y = text.batch(step, 16, cfg.seq, rank=g.rank, world=g.size, device=g.device)
+        wrapped(x, y).backward()
+        opt.step()
+        opt.zero_grad()
+    g.check()
+    return torch.cat([p.detach().reshape(-1) for p in model.parameters()]).cpu()
+
+
+@needs8
+def test_ddp_on_eight_gpus_stays_in_step_and_tracks_one_process():
+    from tandem_b200 import launch
+    from tandem_b200.data import synthetic
+    from tandem_b200.model import GPT
+
+    ours = launch(ddp_eight_rank, 8, device="cuda")
+    assert all(torch.equal(ours[0], ours[r]) for r in range(1, 8))
+    _setup_deterministic()
+    torch.manual_seed(0)
+    cfg = _cfg()
+    text = synthetic(20_000)
+    model = GPT(cfg).cuda()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3, weight_decay=0.1, foreach=False)
+    for step in range(STEPS):
+        x, y = text.batch(step, 16, cfg.seq, device="cuda")
+        model(x, y).backward()
+        opt.step()
+        opt.zero_grad()
+    alone = torch.cat([p.detach().reshape(-1) for p in model.parameters()]).cpu()
+    assert torch.allclose(ours[0], alone, rtol=0, atol=5e-4), (ours[0] - alone).abs().max()
