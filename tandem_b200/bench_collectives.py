@@ -4,6 +4,10 @@ all_reduce / reduce_scatter / all_gather / broadcast, fp32 and bf16, 1 KB - 1 GB
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P -m tandem_b200.bench_collectives [--max-bytes 1073741824] [--out rows.jsonl]
 
+    python -m tandem_b200.bench_collectives --reference cpp|python --ranks N [--max-bytes ...]
+        the same sweep through the UNMODIFIED reference installed under baseline/_ref (its launch(), its Group, its
+        C++ or Python engine), one process per GPU started by the reference itself; rows carry "impl": "reference"
+
 Buffers are allocated once per size (ours: Group.empty(), i.e. symmetric memory, the
 way DDP buckets and ZeRO buffers are; NCCL: ordinary tensors).  Every number is
 device time from CUDA events around `iters` back-to-back calls, after warm-up, max
@@ -39,14 +43,93 @@ def timed(fn, iters, warmup, flush):
     return float(t.item())
 
 
+def reference_rank(g, min_bytes, max_bytes, ops, dtypes):
+    """Runs inside the reference's launch(): its collectives on its own transport, timed with CUDA events."""
+    import torch
+
+    n = g.size
+    rows = []
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=g.device)
+    sizes, b = [], min_bytes
+    while b <= max_bytes:
+        sizes.append(b)
+        b *= 4
+    for dname in dtypes:
+        dtype = getattr(torch, dname)
+        esz = torch.empty(0, dtype=dtype).element_size()
+        for nbytes in sizes:
+            numel = nbytes // esz
+            if numel % n:
+                continue
+            iters = 50 if nbytes <= (1 << 20) else (10 if nbytes <= (64 << 20) else 3)
+            x = torch.randn(numel, device=g.device).to(dtype)
+            for op in ops:
+                fn = {"all_reduce": lambda: g.all_reduce(x, op="avg"), "reduce_scatter": lambda: g.reduce_scatter(x),
+                      "all_gather": lambda: g.all_gather(x), "broadcast": lambda: g.broadcast(x, root=0)}[op]
+                factor = {"all_reduce": 2 * (n - 1) / n, "reduce_scatter": (n - 1) / n, "all_gather": (n - 1) / n, "broadcast": 1.0}[op]
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize(g.device)
+                if nbytes < (128 << 20):
+                    flush.zero_()
+                g.barrier()
+                a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(iters):
+                    fn()
+                e.record()
+                torch.cuda.synchronize(g.device)
+                ms = a.elapsed_time(e) / iters
+                rows.append({"op": op, "dtype": dname, "bytes": nbytes, "ranks": n, "impl": "reference", "engine": g.backend,
+                             "us": round(ms * 1e3, 2), "bus_GBps": round(nbytes / ms / 1e6 * factor, 1)})
+            del x
+    return rows
+
+
+def run_reference(args):
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "tandem")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/tandem is missing (reference not installed)"}))
+        return
+    sys.path.insert(0, ref)
+    os.environ["PYTHONPATH"] = ref + os.pathsep + root + os.pathsep + os.environ.get("PYTHONPATH", "")
+    import tandem
+
+    try:
+        per_rank = tandem.launch(reference_rank, args.ranks, args.min_bytes, args.max_bytes, args.ops.split(","), args.dtypes.split(","),
+                                 device="cuda", backend=args.reference)
+    except Exception as e:
+        print(json.dumps({"impl": "reference", "engine": args.reference, "unavailable": f"the reference failed to run: {repr(e)[:300]}"}))
+        return
+    rows = []
+    for k, row in enumerate(per_rank[0]):  # device time, max over ranks
+        row = dict(row)
+        row["us"] = max(r[k]["us"] for r in per_rank)
+        row["bus_GBps"] = min(r[k]["bus_GBps"] for r in per_rank)
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    if args.out:
+        with open(args.out, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default=None, choices=["cpp", "python"], help="sweep the reference's engine instead (no torchrun)")
+    ap.add_argument("--ranks", type=int, default=2, help="with --reference: how many GPUs")
     ap.add_argument("--min-bytes", type=int, default=1 << 10)
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--ops", default="all_reduce,reduce_scatter,all_gather,broadcast")
     ap.add_argument("--dtypes", default="float32,bfloat16")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
+    if args.reference:
+        run_reference(args)
+        return
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
