@@ -410,7 +410,7 @@ struct SmemLayout {
 };
 
 template <int BM, int BN, bool A_MN, bool B_MN, bool GATHER = false>
-__global__ void __launch_bounds__(GATHER ? 384 : 320, 1)
+__global__ void __launch_bounds__(GATHER ? 448 : 320, 1)
 k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_out,
        const __grid_constant__ CUtensorMap map_pre, const GemmArgs g, const GatherArgs ga) {
   const CUtensorMap* out_map = g.tma_store ? &map_out : nullptr;
@@ -567,8 +567,9 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
       }
     }
   } else if (GATHER && warp >= 10) {
-    // ------------------------------------------------------------------ weight fetchers (warps 10, 11)
-    const int ft = threadIdx.x - 320;  // 0..63
+    // ------------------------------------------------------------------ weight fetchers (warps 10 - 13)
+    const int ft = threadIdx.x - 320;  // 0..127: four fetch warps
+    constexpr int FT = 128, DEPTH = 8;  // eight independent 16-byte loads in flight per thread: 16 KB per CTA, ~2.4 MB per GPU
     const int nchunks = (int)((ga.w_bytes + ga.chunk_bytes - 1) / ga.chunk_bytes);
     const int first = (int)(((long long)ga.n_start * BN * g.K * 2) / ga.chunk_bytes);
     __threadfence_system();  // observe the owners' latest stores to their shards
@@ -585,21 +586,21 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
         const long long len = hi - lo;
         const bool al = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
         const long long nv = al ? len / 16 : 0;
-        for (long long v = ft; v < nv; v += 64 * 4) {  // four independent 16-byte loads in flight per thread
-          uint4 x[4];
+        for (long long v = ft; v < nv; v += FT * DEPTH) {
+          uint4 x[DEPTH];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (v + u * 64 < nv)
+          for (int u = 0; u < DEPTH; ++u)
+            if (v + u * FT < nv)
               asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                           : "=r"(x[u].x), "=r"(x[u].y), "=r"(x[u].z), "=r"(x[u].w) : "l"(src + (v + u * 64) * 16));
+                           : "=r"(x[u].x), "=r"(x[u].y), "=r"(x[u].z), "=r"(x[u].w) : "l"(src + (v + u * FT) * 16));
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (v + u * 64 < nv) *reinterpret_cast<uint4*>(dst + (v + u * 64) * 16) = x[u];
+          for (int u = 0; u < DEPTH; ++u)
+            if (v + u * FT < nv) *reinterpret_cast<uint4*>(dst + (v + u * FT) * 16) = x[u];
         }
-        for (long long i = nv * 16 + ft; i < len; i += 64) dst[i] = *reinterpret_cast<volatile const char*>(src + i);
+        for (long long i = nv * 16 + ft; i < len; i += FT) dst[i] = *reinterpret_cast<volatile const char*>(src + i);
       }
       __threadfence();
-      asm volatile("bar.sync 1, 64;" ::: "memory");  // the two fetch warps only
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the fetch warps only
       if (ft == 0) st_release_gpu(ga.ready + c, ga.epoch);
     }
   } else if (warp < 10) {
@@ -1248,7 +1249,12 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  constexpr int BM = 128, BN = 256;
+  // 256-row tiles (two MMAs per weight panel in shared memory: a third less operand traffic per flop) once the problem
+  // has enough of them for every SM; 128-row tiles otherwise.  The weight panel is 256 columns wide in both.
+  constexpr int BN = 256;
+  const int tiles_n = (N + BN - 1) / BN;
+  const bool tall = (long long)((M + 255) / 256) * tiles_n >= g_sm_count;
+  const int BM = tall ? 256 : 128;
   CUtensorMap ma, mb;
   int rc = make_map(&ma, A, K, M, lda, 64, BM);
   if (rc) return rc;
@@ -1272,21 +1278,20 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
   ga.epoch = epoch;
   ga.n = n_ranks;
   ga.chunk_bytes = chunk_bytes;
-  const int tiles_n = (N + BN - 1) / BN;
   ga.n_start = ((n_start % tiles_n) + tiles_n) % tiles_n;
-  auto kernel = k_gemm<BM, BN, false, false, true>;
-  using L = SmemLayout<BM, BN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+  const void* kernel = tall ? (const void*)k_gemm<256, BN, false, false, true> : (const void*)k_gemm<128, BN, false, false, true>;
+  const int smem = tall ? SmemLayout<256, BN>::TOTAL : SmemLayout<128, BN>::TOTAL;
+  static bool configured[2] = {false, false};
+  if (!configured[tall]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[tall] = true;
   }
   const int tiles = ((M + BM - 1) / BM) * tiles_n;
   int ctas = tiles < g_sm_count ? tiles : g_sm_count;
   void* params[] = {(void*)&ma, (void*)&mb, (void*)&mo, (void*)&mp, (void*)&g, (void*)&ga};
   tb_note_launch(1);
-  return (int)cudaLaunchCooperativeKernel((const void*)kernel, dim3(ctas), dim3(384), params, L::TOTAL, stream);
+  return (int)cudaLaunchCooperativeKernel(kernel, dim3(ctas), dim3(448), params, smem, stream);
 }
 
 void tb_gemm_force_tile(int which) { g_forced_tile = which; }

@@ -51,7 +51,28 @@ class NcclP2P:
             self._lanes = {"act": None}  # None: the default process group
             self._lanes["grad"] = self.dist.new_group(list(range(self.g.size)), backend="nccl")  # collective: every rank calls it
             self._side = torch.cuda.Stream(self.g.device)
+            self._connect_neighbours()
         return self._lanes[name]
+
+    def _connect_neighbours(self):
+        """NCCL sets up the connection between two ranks at their first transfer on a communicator, and that set-up
+        is a host-side rendezvous of both.  A receive posted ahead of time would sit in it until the sender reaches
+        its first send -- which may itself depend on this rank's progress.  So every pair of neighbouring stages
+        exchanges one element in both directions on both lanes here, symmetrically, before any real traffic."""
+        r, n = self.g.rank, self.g.size
+        for group in self._lanes.values():
+            ops, keep = [], []
+            for peer in (r - 1, r + 1):
+                if 0 <= peer < n:
+                    out = torch.zeros(1, device=self.g.device)
+                    inp = torch.zeros(1, device=self.g.device)
+                    keep += [out, inp]
+                    ops.append(self.dist.P2POp(self.dist.isend, out, peer, group=group))
+                    ops.append(self.dist.P2POp(self.dist.irecv, inp, peer, group=group))
+            if ops:
+                for w in self.dist.batch_isend_irecv(ops):
+                    w.wait()
+        torch.cuda.synchronize(self.g.device)
 
     def post_recv(self, shape, dtype, src, lane):
         """Starts a receive into a fresh buffer, independent of whatever is queued on the caller's stream.

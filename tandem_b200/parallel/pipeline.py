@@ -155,7 +155,8 @@ class Pipeline:
         """GPU stages.  Transfers use two NCCL lanes (activations down, gradients up), so paired actions fall
         apart into an asynchronous send and a receive that was posted ahead of time: as soon as one receive
         has been claimed the next one of its kind is posted, before this stage computes anything on what it just
-        received.  Sends never hold up the compute stream; they are collected and awaited when the step ends."""
+        received (the first of each kind is posted when the schedule first asks for it).  Sends never hold up the
+        compute stream; they are collected and awaited when the step ends."""
         g, up, down = self.g, self.g.rank - 1, self.g.rank + 1
         wire = g._p2p()
         takes_act = {"recv_act", "send_grad_recv_act"}
@@ -174,13 +175,13 @@ class Pipeline:
                 posted["grad"] = wire.post_recv(shape, dtype, down, "grad")
 
         def claim(kind):
+            if posted[kind] is None:
+                post(kind)  # the first of its kind in this step is posted when it is first needed
             handle, posted[kind] = posted[kind], None
             tensor = wire.claim(*handle)
             post(kind)  # the next one starts arriving while this one is being used
             return tensor
 
-        post("act")
-        post("grad")
         saved, losses, in_flight = {}, [], []
         act = grad = out = None
         for a in actions:

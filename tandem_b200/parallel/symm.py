@@ -116,6 +116,25 @@ def cuda_lib():
     for name, (argtypes, restype) in sig.items():
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = argtypes, restype
+    ull = ctypes.c_ulonglong
+    pi = ctypes.POINTER(i)
+    pull = ctypes.POINTER(ull)
+    for name, (argtypes, restype) in {
+        "tb_vmm_last_error": ([], ctypes.c_char_p),
+        "tb_vmm_probe": ([i, pi], i),
+        "tb_vmm_granularity": ([i, i, ll], ll),
+        "tb_vmm_create": ([ll, ll, i, pp, pi, pull], i),
+        "tb_vmm_import": ([i, ll, ll, i, pp, pull], i),
+        "tb_vmm_release": ([vp, ll, ull], i),
+        "tb_mc_create": ([ll, i, pi, pull], i),
+        "tb_mc_import": ([i, pull], i),
+        "tb_mc_add_device": ([ull, i], i),
+        "tb_mc_bind_and_map": ([ull, ull, ll, ll, i, pp], i),
+        "tb_mc_release": ([ull, vp, ll, i], i),
+        "tb_close_fd": ([i], i),
+    }.items():
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = argtypes, restype
     # TANDEM_PDL=0: launch the compute kernels without programmatic dependent launch (for A/B measurements)
     lib.tb_set_pdl.argtypes, lib.tb_set_pdl.restype = [i], None
     lib.tb_set_pdl(0 if os.environ.get("TANDEM_PDL", "1") == "0" else 1)
@@ -233,6 +252,7 @@ class SymmetricComm:
         self.segment_bytes = int(os.environ.get("TANDEM_SYMM_BYTES", str(1 << 30)))
         self.heap = Heap()
         self._torch_segments = []  # segments that came from torch's symmetric-memory allocator (kept alive here)
+        self._vmm_segments = []  # segments created through the driver's virtual-memory API (own, imported, multicast)
         self._nvls_error = None
         self._owned = []  # this rank's cudaMalloc'd segments
         self._opened = []  # peers' segments mapped here
@@ -284,6 +304,8 @@ class SymmetricComm:
         NCCL group in place (and TANDEM_NVLS != 0) the segment comes from torch's symmetric-memory
         allocator, which also binds it to an NVSwitch multicast object (for the multimem kernels);
         otherwise it is cudaMalloc'd here and exchanged through CUDA IPC."""
+        if self.n > 1 and os.environ.get("TANDEM_VMM", "0") != "0" and self._add_segment_vmm(nbytes):
+            return
         if self.n > 1 and os.environ.get("TANDEM_NVLS", "1") != "0" and self._add_segment_multicast(nbytes):
             return
         mine = ctypes.c_void_p()
@@ -306,6 +328,137 @@ class SymmetricComm:
             self._opened.append(out.value)
             bases.append(out.value)
         self.heap.add_segment(nbytes, bases)
+
+    # ---- segments created through the driver's virtual-memory API, with this library's own multicast binding
+    def _agree(self, ok):
+        """True if every rank says ok (an all-gather over the host control plane)."""
+        votes = torch.zeros(self.n, dtype=torch.int64)
+        votes[self.rank] = 1 if ok else 0
+        self.g._native("agree", lambda: self.g._engine.all_gather(votes.data_ptr(), votes.numel(), 4, [1] * self.n), None, 0, False, (votes,))
+        return bool(votes.min().item() == 1)
+
+    def _host_barrier(self):
+        self.g._native("barrier", self.g._engine.barrier, None, 0, False)
+
+    def _swap_fds(self, tag, mine=None, root=None):
+        """File descriptors between the ranks over abstract Unix datagram sockets (SCM_RIGHTS).
+        mine given, root None: everyone sends `mine` to everyone, returns {rank: fd} (own entry = mine).
+        root given: only the root sends `mine`; the others return {root: fd}."""
+        import socket
+        import struct
+
+        def address(q):
+            return b"\0tb2-" + self.g.job.encode() + b"-" + tag.encode() + b"-" + str(q).encode()
+
+        sock = socket.socket(socket.AF_UNIX, socket.SOCK_DGRAM)
+        try:
+            sock.bind(address(self.rank))
+            sock.settimeout(max(5.0, min(self.g.timeout, 120.0)))
+            self._host_barrier()  # every rank's socket exists
+            got = {}
+            if root is None or root == self.rank:
+                for q in range(self.n):
+                    if q != self.rank:
+                        socket.send_fds(sock, [struct.pack("i", self.rank)], [mine], 0, address(q))
+                got[self.rank] = mine
+            expect = self.n if root is None else 1
+            while len(got) < expect:
+                msg, fds, _flags, _addr = socket.recv_fds(sock, 16, 1)
+                got[struct.unpack("i", msg[:4])[0]] = fds[0]
+            self._host_barrier()  # nobody closes a socket a peer may still be sending to
+            return got
+        finally:
+            sock.close()
+
+    def _add_segment_vmm(self, nbytes):
+        """cuMemCreate + POSIX-fd exchange + mapping of every peer's segment; if the GPUs support it (and TANDEM_NVLS
+        is not 0), the segments are also bound to one multicast object whose mapping serves the multimem kernels.
+        Every step ends in an agreement between the ranks, so either all ranks use this segment or none does."""
+        lib, dev = self.lib, self.device.index
+        caps = (ctypes.c_int * 2)()
+        ok = lib.tb_vmm_probe(dev, caps) == 0 and caps[0] == 1
+        if not self._agree(ok):
+            self._nvls_error = "the driver cannot export device memory as file descriptors on every rank"
+            return False
+        want_mc = self._agree(caps[1] == 1) and os.environ.get("TANDEM_NVLS", "1") != "0"
+        gran = lib.tb_vmm_granularity(dev, self.n if want_mc else 1, nbytes)
+        sizes = torch.zeros(self.n, dtype=torch.int64)
+        sizes[self.rank] = gran
+        self.g._native("sizes", lambda: self.g._engine.all_gather(sizes.data_ptr(), sizes.numel(), 4, [1] * self.n), None, 0, False, (sizes,))
+        gran = int(sizes.max().item())
+        if gran <= 0:
+            return False
+        size = (nbytes + gran - 1) // gran * gran
+        ptr, fd, handle = ctypes.c_void_p(), ctypes.c_int(-1), ctypes.c_ulonglong(0)
+        created = lib.tb_vmm_create(size, gran, dev, ctypes.byref(ptr), ctypes.byref(fd), ctypes.byref(handle)) == 0
+        if not self._agree(created):
+            if created:
+                lib.tb_close_fd(fd.value)
+                lib.tb_vmm_release(ptr, size, handle.value)
+            self._nvls_error = lib.tb_vmm_last_error().decode()
+            return False
+        self._seg_count = getattr(self, "_seg_count", 0) + 1
+        tag = f"s{self._seg_count}"
+        fds = self._swap_fds(tag, fd.value)
+        bases, imported, good = [], [], True
+        for q in range(self.n):
+            if q == self.rank:
+                bases.append(ptr.value)
+                continue
+            p, h = ctypes.c_void_p(), ctypes.c_ulonglong(0)
+            if good and lib.tb_vmm_import(fds[q], size, gran, dev, ctypes.byref(p), ctypes.byref(h)) == 0:
+                imported.append((p.value, h.value))
+                bases.append(p.value)
+            else:
+                good = False
+            lib.tb_close_fd(fds[q])
+        lib.tb_close_fd(fd.value)
+
+        def undo():
+            for p, h in imported:
+                lib.tb_vmm_release(p, size, h)
+            self._host_barrier()  # nobody still maps this rank's memory
+            lib.tb_vmm_release(ptr, size, handle.value)
+
+        if not self._agree(good):
+            self._nvls_error = lib.tb_vmm_last_error().decode()
+            undo()
+            return False
+        mc_handle, mc_ptr = 0, 0
+        if want_mc:
+            mc_handle, mc_ptr = self._bind_multicast(tag, size, gran, handle.value)
+        self._vmm_segments.append({"size": size, "own": (ptr.value, handle.value), "imported": imported, "mc": (mc_handle, mc_ptr)})
+        self.heap.add_segment(size, bases, mc_ptr)
+        return True
+
+    def _bind_multicast(self, tag, size, gran, mem_handle):
+        """(multicast handle, multicast address) or (0, 0) when the object cannot be set up on every rank."""
+        lib, dev = self.lib, self.device.index
+        mc, fd = ctypes.c_ulonglong(0), ctypes.c_int(-1)
+        ok = True
+        if self.rank == 0:
+            ok = lib.tb_mc_create(size, self.n, ctypes.byref(fd), ctypes.byref(mc)) == 0
+        if not self._agree(ok):
+            self._nvls_error = lib.tb_vmm_last_error().decode()
+            return 0, 0
+        got = self._swap_fds(tag + "m", fd.value if self.rank == 0 else None, root=0)
+        if self.rank != 0:
+            ok = lib.tb_mc_import(got[0], ctypes.byref(mc)) == 0
+            lib.tb_close_fd(got[0])
+        else:
+            lib.tb_close_fd(fd.value)
+        ok = ok and lib.tb_mc_add_device(mc.value, dev) == 0
+        if not self._agree(ok):  # agreement doubles as "every device has joined"
+            self._nvls_error = lib.tb_vmm_last_error().decode()
+            return 0, 0
+        mapped = ctypes.c_void_p()
+        ok = lib.tb_mc_bind_and_map(mc.value, mem_handle, size, gran, dev, ctypes.byref(mapped)) == 0
+        if not self._agree(ok):
+            self._nvls_error = lib.tb_vmm_last_error().decode()
+            if ok:
+                lib.tb_mc_release(mc.value, mapped, size, dev)
+            return 0, 0
+        return mc.value, mapped.value
 
     def _add_segment_multicast(self, nbytes):
         try:
@@ -620,7 +773,16 @@ class SymmetricComm:
         for p in self._opened:
             self.lib.tb_ipc_close(p)
         self._opened = []
+        for seg in self._vmm_segments:  # multicast mappings and bindings go first, then the peers' mappings
+            mc, mc_ptr = seg["mc"]
+            if mc:
+                self.lib.tb_mc_release(mc, mc_ptr, seg["size"], self.device.index)
+            for p, h in seg["imported"]:
+                self.lib.tb_vmm_release(p, seg["size"], h)
         self.g._native("barrier", self.g._engine.barrier, None, 0, False)  # everyone has unmapped
+        for seg in self._vmm_segments:
+            self.lib.tb_vmm_release(seg["own"][0], seg["size"], seg["own"][1])
+        self._vmm_segments = []
         for p in self._owned:
             self.lib.tb_free(p)
         self._owned = []

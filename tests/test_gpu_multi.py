@@ -393,8 +393,55 @@ def test_ranks_sharing_one_gpu_stage_through_the_host():
     assert launch(shared_gpu_rank, 2, device="cuda", gpus=[0, 0]) == [("host", False, 3.0, 14.0)] * 2
 
 
+def nvls_checks(g):
+    """The four collectives through the NVSwitch multicast mapping (multimem.ld_reduce / multimem.st), forced on."""
+    from tandem_b200.parallel.symm import ALGO
+
+    rank, world = g.rank, g.size
+    ok = True
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (1 << 20, 300_000 * 8):
+            x = g.empty(n, dtype)
+            x.copy_(data(rank, n, dtype))
+            g._sym.all_reduce(x, False, x, 0, False, algo="nvls")
+            want = sum(data(q, n, dtype).double() for q in range(world))
+            ok = ok and torch.equal(x.double().cpu(), want)
+            x.copy_(data(rank, n, dtype))
+            g.all_reduce(x, op="avg")  # large enough to pick the NVLS kernel by itself where the group is large enough
+            ok = ok and torch.allclose(x.double().cpu(), want / world, rtol=1e-2, atol=1e-2)
+            g.release(x)
+    auto, g._sym.algo = g._sym.algo, ALGO["nvls"]
+    for dtype in (torch.float32, torch.bfloat16):
+        n = 1 << 20
+        # all-gather: each rank multicasts its own chunk (multimem.st)
+        full = data(7, n, dtype)
+        x = g.empty(n, dtype)
+        x.fill_(-7)
+        lo, hi = n * rank // world, n * (rank + 1) // world
+        x[lo:hi].copy_(full[lo:hi])
+        g.all_gather(x)
+        ok = ok and torch.equal(x.cpu(), full)
+        # reduce-scatter: the switch sums this rank's chunk (multimem.ld_reduce), with and without the accumulate epilogue
+        want = sum(data(q, n, dtype).double() for q in range(world))
+        x.copy_(data(rank, n, dtype))
+        mine = g.reduce_scatter(x)
+        ok = ok and torch.equal(mine.double().cpu(), want[lo:hi])
+        x.copy_(data(rank, n, dtype))
+        acc = torch.ones(hi - lo, dtype=dtype, device=g.device)
+        g.reduce_scatter(x, accumulate_into=acc)
+        ok = ok and torch.equal(acc.double().cpu(), want[lo:hi] + 1)
+        # broadcast: the root writes once to the multicast address
+        x.copy_(data(rank, n, dtype, seed=5))
+        g.broadcast(x, root=world - 1)
+        ok = ok and torch.equal(x.cpu(), data(world - 1, n, dtype, seed=5))
+        g.release(x)
+    g._sym.algo = auto
+    g.check()
+    return ok
+
+
 def nvls_rank(rank, world, init, out):
-    """All-reduce through the NVSwitch multicast mapping (multimem.ld_reduce / multimem.st)."""
+    """A heap bound to a multicast object by torch's symmetric memory (needs a NCCL process group)."""
     import torch.distributed as dist
 
     from tandem_b200 import Group
@@ -404,38 +451,40 @@ def nvls_rank(rank, world, init, out):
     g = Group(rank, world, f"cuda:{rank}", job=os.path.basename(init)[-12:])
     result = {"nvls": g._sym.nvls, "why": g._sym._nvls_error}
     if g._sym.nvls:
-        ok = True
-        for dtype in (torch.float32, torch.bfloat16):
-            for n in (1 << 20, 300_000 * 8):
-                x = g.empty(n, dtype)
-                x.copy_(data(rank, n, dtype))
-                g._sym.all_reduce(x, False, x, 0, False, algo="nvls")
-                want = sum(data(q, n, dtype).double() for q in range(world))
-                ok = ok and torch.equal(x.double().cpu(), want)
-                x.copy_(data(rank, n, dtype))
-                g.all_reduce(x, op="avg")  # large enough to pick the NVLS kernel by itself
-                ok = ok and torch.allclose(x.double().cpu(), want / world, rtol=1e-2, atol=1e-2)
-                g.release(x)
-        # all-gather through the switch: each rank multicasts its own chunk (multimem.st)
-        from tandem_b200.parallel.symm import ALGO
-
-        auto, g._sym.algo = g._sym.algo, ALGO["nvls"]
-        for dtype in (torch.float32, torch.bfloat16):
-            n = 1 << 20
-            full = data(7, n, dtype)
-            x = g.empty(n, dtype)
-            x.fill_(-7)
-            lo, hi = n * rank // world, n * (rank + 1) // world
-            x[lo:hi].copy_(full[lo:hi])
-            g.all_gather(x)
-            ok = ok and torch.equal(x.cpu(), full)
-            g.release(x)
-        g._sym.algo = auto
-        g.check()
-        result["ok"] = ok
+        result["ok"] = nvls_checks(g)
     g.close()
     dist.destroy_process_group()
     torch.save(result, f"{out}.{rank}")
+
+
+def own_multicast_rank(g):
+    """The same through this library's own set-up: launch() only, no torch.distributed anywhere."""
+    sym = g._sym
+    facts = {"vmm": bool(sym._vmm_segments), "nvls": sym.nvls, "why": sym._nvls_error}
+    # ordinary peer loads over the VMM mappings
+    x = g.empty(100_003, torch.float32)
+    x.copy_(data(g.rank, 100_003, torch.float32))
+    g.all_reduce(x)
+    facts["peer_ok"] = torch.equal(x.double().cpu(), sum(data(q, 100_003, torch.float32).double() for q in range(g.size)))
+    g.release(x)
+    if sym.nvls:
+        facts["ok"] = nvls_checks(g)
+    return facts
+
+
+@needs2
+def test_own_multicast_binding_through_launch(monkeypatch):
+    """cuMemCreate segments exchanged as file descriptors and bound to a multicast object by this library itself:
+    the product's own launcher gets the in-switch kernels without any process group."""
+    from tandem_b200 import launch
+
+    monkeypatch.setenv("TANDEM_VMM", "1")
+    res = launch(own_multicast_rank, 2, device="cuda")
+    assert all(r["vmm"] for r in res), res[0]["why"]
+    assert all(r["peer_ok"] for r in res)
+    if not res[0]["nvls"]:
+        pytest.skip(f"no NVSwitch multicast on this machine: {res[0]['why']}")
+    assert all(r["ok"] for r in res)
 
 
 @needs2
