@@ -21,6 +21,7 @@ device-to-host read of the loss.
 """
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -212,7 +213,9 @@ def run_ours(args):
 
         local = int(os.environ.get("LOCAL_RANK", str(rank)))
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # a stalled NCCL transfer ends the run with the name of the operation instead of sitting until the job is killed
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=int(os.environ.get("TANDEM_PG_TIMEOUT_S", "300"))))
     g = tandem_b200.Group.from_env(device="cuda")
     dev = g.device
     lib = cuda_lib()

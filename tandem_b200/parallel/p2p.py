@@ -93,6 +93,16 @@ class NcclP2P:
         """Starts a send ordered after the caller's stream; the caller keeps (work, tensor) until the step ends."""
         return self.dist.isend(tensor, dst, group=self.lane(lane)), tensor
 
+    def exchange(self, sends, recvs, shape, dtype):
+        """One grouped NCCL call on the default communicator: every (tensor, dst) of `sends` and one fresh buffer per
+        source in `recvs`, ordered after the caller's stream.  Returns (work, tensors to keep alive, received buffers);
+        the buffers are usable on the caller's stream after claim(work, buffer)."""
+        received = [torch.empty(shape, device=self.g.device, dtype=dtype) for _ in recvs]
+        ops = [self.dist.P2POp(self.dist.isend, t, dst) for t, dst in sends]
+        ops += [self.dist.P2POp(self.dist.irecv, buf, src) for buf, src in zip(received, recvs)]
+        works = self.dist.batch_isend_irecv(ops)
+        return _NcclWork("exchange", self.g, works, None, 0, ()), [t for t, _ in sends] + received, received
+
     def _done(self, name, works, result, nbytes, async_op, keep):
         work = _NcclWork(name, self.g, works, result, nbytes, keep)
         return work if async_op else work.wait()

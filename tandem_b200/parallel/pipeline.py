@@ -152,34 +152,49 @@ class Pipeline:
         return sum(losses) if self.last else None
 
     def _run_on_lanes(self, actions, xs, ys, dev, dtype, shape):
-        """GPU stages.  Transfers use two NCCL lanes (activations down, gradients up), so paired actions fall
-        apart into an asynchronous send and a receive that was posted ahead of time: as soon as one receive
-        has been claimed the next one of its kind is posted, before this stage computes anything on what it just
-        received (the first of each kind is posted when the schedule first asks for it).  Sends never hold up the
-        compute stream; they are collected and awaited when the step ends."""
+        """GPU stages over NCCL.  Nothing here blocks the host: a transfer is ordered after the compute stream when it
+        is issued, and claiming a received tensor makes the compute stream wait for it.  Sends are collected and
+        awaited when the step ends.
+
+        GPipe: activations travel down on one communicator and gradients up on another, and a stage never has both
+        phases in flight, so receives are posted ahead of time -- the next one of a kind as soon as the previous one
+        has been claimed (on a middle stage: as soon as the send that forwards it has been issued, so that on the
+        lane's stream a receive never stands in front of the send its own sender is waiting for).
+
+        1F1B: in the steady state a stage sends one way and receives the other at the same moment.  The pair is ONE
+        grouped NCCL call on one communicator (both directions inside one kernel), issued in the schedule's order,
+        which every stage shares; it needs no second NCCL kernel to make progress next to it.  Receives posted ahead
+        on a second communicator were measured to stall at 8 MB messages on two B200s (each side spinning in a
+        receive while the send that would release the other waited to be scheduled), so this schedule does not
+        use them."""
         g, up, down = self.g, self.g.rank - 1, self.g.rank + 1
         wire = g._p2p()
+        wire.lane("act")  # first use: both communicators exist and every neighbour pair is connected before real traffic
+        ahead = self.schedule == "gpipe"
         takes_act = {"recv_act", "send_grad_recv_act"}
         takes_grad = {"recv_grad", "send_act_recv_grad"}
-        acts_due = 0 if self.first else sum(a[0] in takes_act for a in actions)
-        grads_due = 0 if self.last else sum(a[0] in takes_grad for a in actions)
+        due = {"act": 0 if self.first else sum(a[0] in takes_act for a in actions),
+               "grad": 0 if self.last else sum(a[0] in takes_grad for a in actions)}
+        source = {"act": up, "grad": down}
+        forwards = {"act": not self.last, "grad": not self.first}  # does this stage pass that kind on?
         posted = {"act": None, "grad": None}
+        owed = {"act": False, "grad": False}  # a receive to post once the matching send has been issued
 
         def post(kind):
-            nonlocal acts_due, grads_due
-            if kind == "act" and acts_due:
-                acts_due -= 1
-                posted["act"] = wire.post_recv(shape, dtype, up, "act")
-            elif kind == "grad" and grads_due:
-                grads_due -= 1
-                posted["grad"] = wire.post_recv(shape, dtype, down, "grad")
+            owed[kind] = False
+            if due[kind]:
+                due[kind] -= 1
+                posted[kind] = wire.post_recv(shape, dtype, source[kind], kind)
 
         def claim(kind):
             if posted[kind] is None:
-                post(kind)  # the first of its kind in this step is posted when it is first needed
+                post(kind)  # the first of its kind in a step is posted when the schedule first asks for it
             handle, posted[kind] = posted[kind], None
             tensor = wire.claim(*handle)
-            post(kind)  # the next one starts arriving while this one is being used
+            if forwards[kind]:
+                owed[kind] = True
+            else:
+                post(kind)  # the next one arrives while this one is being used
             return tensor
 
         saved, losses, in_flight = {}, [], []
@@ -195,7 +210,8 @@ class Pipeline:
                         out = loss_fn(out, ys[i].to(dev), self.kernels) / self.m
                         losses.append(out.detach())
                     saved[i] = (inp, out)
-            elif kind == "B":
+                continue
+            if kind == "B":
                 i = a[1]
                 with self.timeline.span(f"B{i}"):
                     inp, res = saved.pop(i)
@@ -204,15 +220,34 @@ class Pipeline:
                     else:
                         res.backward(grad)
                     grad = None if self.first else inp.grad
-            else:
-                if kind in ("send_act", "send_act_recv_grad") and not self.last:
-                    in_flight.append(wire.post_send(out.detach().contiguous(), down, "act"))
-                if kind in ("send_grad", "send_grad_recv_act") and not self.first:
-                    in_flight.append(wire.post_send(grad.contiguous(), up, "grad"))
-                if kind in takes_act and not self.first:
-                    act = claim("act")
-                if kind in takes_grad and not self.last:
-                    grad = claim("grad")
-        for work, _tensor in in_flight:
+                continue
+            send_act = kind in ("send_act", "send_act_recv_grad") and not self.last
+            send_grad = kind in ("send_grad", "send_grad_recv_act") and not self.first
+            recv_act = kind in takes_act and not self.first
+            recv_grad = kind in takes_grad and not self.last
+            if not ahead:
+                sends = ([(out.detach().contiguous(), down)] if send_act else []) + ([(grad.contiguous(), up)] if send_grad else [])
+                recvs = ([up] if recv_act else []) + ([down] if recv_grad else [])
+                if sends or recvs:
+                    work, kept, received = wire.exchange(sends, recvs, shape, dtype)
+                    in_flight.append((work, kept))
+                    if recv_act:
+                        act = wire.claim(work, received[0])
+                    if recv_grad:
+                        grad = wire.claim(work, received[-1])
+                continue
+            if send_act:
+                in_flight.append(wire.post_send(out.detach().contiguous(), down, "act"))
+                if owed["act"]:
+                    post("act")
+            if send_grad:
+                in_flight.append(wire.post_send(grad.contiguous(), up, "grad"))
+                if owed["grad"]:
+                    post("grad")
+            if recv_act:
+                act = claim("act")
+            if recv_grad:
+                grad = claim("grad")
+        for work, _kept in in_flight:
             work.wait()
         return sum(losses) if self.last else None

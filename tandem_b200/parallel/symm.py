@@ -234,6 +234,40 @@ class Heap:
         return [b + off for b in self.segments[seg][1]]
 
 
+def swap_fds(job, tag, rank, n, barrier, timeout, mine=None, root=None):
+    """File descriptors between the ranks of a job over abstract Unix datagram sockets (SCM_RIGHTS).
+    root None: every rank sends `mine` to every other rank; returns {rank: fd} with the own entry = mine.
+    root given: only the root sends `mine`; the others return {root: fd}.  `barrier` is a host barrier over the
+    same ranks.  The received descriptors are new ones in this process; the caller closes them."""
+    import array
+    import socket
+    import struct
+
+    def address(q):
+        return b"\0tb2-" + job.encode() + b"-" + tag.encode() + b"-" + str(q).encode()
+
+    sock = socket.socket(socket.AF_UNIX, socket.SOCK_DGRAM)
+    try:
+        sock.bind(address(rank))
+        sock.settimeout(timeout)
+        barrier()  # every rank's socket exists
+        got = {}
+        if root is None or root == rank:
+            rights = [(socket.SOL_SOCKET, socket.SCM_RIGHTS, array.array("i", [mine]))]
+            for q in range(n):
+                if q != rank:
+                    sock.sendmsg([struct.pack("i", rank)], rights, 0, address(q))
+            got[rank] = mine
+        expect = n if root is None else 1
+        while len(got) < expect:
+            msg, fds, _flags, _addr = socket.recv_fds(sock, 16, 1)
+            got[struct.unpack("i", msg[:4])[0]] = fds[0]
+        barrier()  # nobody closes a socket a peer may still be sending to
+        return got
+    finally:
+        sock.close()
+
+
 class SymmetricComm:
     """The GPU side of a Group (one process per GPU)."""
 
@@ -341,34 +375,7 @@ class SymmetricComm:
         self.g._native("barrier", self.g._engine.barrier, None, 0, False)
 
     def _swap_fds(self, tag, mine=None, root=None):
-        """File descriptors between the ranks over abstract Unix datagram sockets (SCM_RIGHTS).
-        mine given, root None: everyone sends `mine` to everyone, returns {rank: fd} (own entry = mine).
-        root given: only the root sends `mine`; the others return {root: fd}."""
-        import socket
-        import struct
-
-        def address(q):
-            return b"\0tb2-" + self.g.job.encode() + b"-" + tag.encode() + b"-" + str(q).encode()
-
-        sock = socket.socket(socket.AF_UNIX, socket.SOCK_DGRAM)
-        try:
-            sock.bind(address(self.rank))
-            sock.settimeout(max(5.0, min(self.g.timeout, 120.0)))
-            self._host_barrier()  # every rank's socket exists
-            got = {}
-            if root is None or root == self.rank:
-                for q in range(self.n):
-                    if q != self.rank:
-                        socket.send_fds(sock, [struct.pack("i", self.rank)], [mine], 0, address(q))
-                got[self.rank] = mine
-            expect = self.n if root is None else 1
-            while len(got) < expect:
-                msg, fds, _flags, _addr = socket.recv_fds(sock, 16, 1)
-                got[struct.unpack("i", msg[:4])[0]] = fds[0]
-            self._host_barrier()  # nobody closes a socket a peer may still be sending to
-            return got
-        finally:
-            sock.close()
+        return swap_fds(self.g.job, tag, self.rank, self.n, self._host_barrier, max(5.0, min(self.g.timeout, 120.0)), mine, root)
 
     def _add_segment_vmm(self, nbytes):
         """cuMemCreate + POSIX-fd exchange + mapping of every peer's segment; if the GPUs support it (and TANDEM_NVLS

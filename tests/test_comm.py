@@ -189,3 +189,36 @@ def check_misuse(group):
 
 def test_misuse_raises_comm_error():
     assert launch(check_misuse, 2) == [[True] * 6] * 2
+
+
+def _pass_descriptors(g):
+    """Every rank writes its rank into a temporary file and hands the open descriptor to every peer; then rank 1
+    alone hands out a second file (the one-to-all form the multicast handle uses)."""
+    import os
+    import tempfile
+
+    from tandem_b200.parallel.symm import swap_fds
+
+    def scratch(text):
+        fd, path = tempfile.mkstemp()
+        os.unlink(path)
+        os.write(fd, text.encode())
+        return fd
+
+    mine = scratch(f"rank {g.rank}")
+    got = swap_fds(g.job, "t0", g.rank, g.size, g.barrier, 20.0, mine)
+    assert sorted(got) == list(range(g.size))
+    for q, fd in got.items():
+        assert os.pread(fd, 64, 0).decode() == f"rank {q}"
+        assert (fd == mine) == (q == g.rank)
+    for fd in got.values():
+        os.close(fd)
+    special = scratch("from the root") if g.rank == 1 else None
+    got = swap_fds(g.job, "t1", g.rank, g.size, g.barrier, 20.0, special, root=1)
+    assert list(got) == [1]
+    assert os.pread(got[1], 64, 0).decode() == "from the root"
+    os.close(got[1])
+
+
+def test_descriptors_travel_between_ranks():
+    launch(_pass_descriptors, 3, device="cpu")

@@ -460,15 +460,18 @@ def nvls_rank(rank, world, init, out):
 def own_multicast_rank(g):
     """The same through this library's own set-up: launch() only, no torch.distributed anywhere."""
     sym = g._sym
-    facts = {"vmm": bool(sym._vmm_segments), "nvls": sym.nvls, "why": sym._nvls_error}
-    # ordinary peer loads over the VMM mappings
-    x = g.empty(100_003, torch.float32)
-    x.copy_(data(g.rank, 100_003, torch.float32))
-    g.all_reduce(x)
-    facts["peer_ok"] = torch.equal(x.double().cpu(), sum(data(q, 100_003, torch.float32).double() for q in range(g.size)))
-    g.release(x)
-    if sym.nvls:
-        facts["ok"] = nvls_checks(g)
+    facts = {"vmm": bool(sym._vmm_segments), "nvls": sym.nvls, "why": sym._nvls_error, "peer_ok": False, "ok": False}
+    try:  # a rank never leaves early: its memory stays bound to the multicast object until every rank closes
+        # ordinary peer loads over the VMM mappings
+        x = g.empty(100_003, torch.float32)
+        x.copy_(data(g.rank, 100_003, torch.float32))
+        g.all_reduce(x)
+        facts["peer_ok"] = torch.equal(x.double().cpu(), sum(data(q, 100_003, torch.float32).double() for q in range(g.size)))
+        g.release(x)
+        if sym.nvls:
+            facts["ok"] = nvls_checks(g)
+    except Exception as e:
+        facts["why"] = repr(e)
     return facts
 
 
