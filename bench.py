@@ -293,6 +293,8 @@ def run_ours(args):
         per_step = step_fn.launches_per_step
     dev_ms, e2e_ms, h2d, d2h, launches, last = timed_loops(step_fn, batches, args.steps, args.warmup, dev, g.barrier, reduce_max)
     launches = per_step * args.steps
+    if pipelined:
+        last = reduce_max(float(last))  # only the last stage computes the loss
     clocks = sampler.stop() if rank == 0 else None
     nvls = bool(g._sym is not None and g._sym.nvls)
     g.close()
@@ -300,7 +302,7 @@ def run_ours(args):
         print(json.dumps(result_line(args, "ours", args.strategy, dev_ms, e2e_ms, h2d, d2h, int(launches), clocks, "bf16",
                                      {"kernels": kernels, "final_loss": last, "cuda_graph": bool(graphed), "nvls": nvls,
                                       "optimizer": ("sharded over ranks, fused into the reduce-scatter" if sharded_opt else "replicated")
-                                      if args.strategy == "ddp" else "sharded"})), flush=True)
+                                      if args.strategy == "ddp" else ("per stage (torch fused AdamW)" if pipelined else "sharded")})), flush=True)
     if world > 1:
         import torch.distributed as dist
 
@@ -370,7 +372,7 @@ def run_torch(args):
 
 
 # ---------------------------------------------------------------------------------------------- reference
-def reference_rank(g, steps, warmup, strategy):
+def reference_rank(g, steps, warmup, strategy, model_name):
     """Runs inside the reference's launch(): its GPT, its DDP / ZeRO / FSDP, torch AdamW as its bench does."""
     import torch
     from tandem.ddp import DDP
@@ -379,6 +381,7 @@ def reference_rank(g, steps, warmup, strategy):
     from tandem.zero import FSDP, ZeRO
 
     sys.path.insert(0, ROOT)
+    select_model(model_name)  # launch() starts fresh processes: this module's configuration is set again in each
     dev = g.device
     torch.manual_seed(0)
     model = GPT(Config(**MODEL)).to(dev)
@@ -447,7 +450,7 @@ def run_reference(args):
         out, engine, notes = None, None, []
         for engine in engines:
             try:
-                out = tandem.launch(reference_rank, args.gpus, args.steps, args.warmup, args.strategy, device="cuda", backend=engine)
+                out = tandem.launch(reference_rank, args.gpus, args.steps, args.warmup, args.strategy, args.model, device="cuda", backend=engine)
                 break
             except Exception as e:
                 notes.append(f"{engine}: {repr(e)[:200]}")
@@ -459,7 +462,7 @@ def run_reference(args):
         dev_ms = max(o["dev_ms"] for o in out)
         e2e_ms = max(o["e2e_ms"] for o in out)
         print(json.dumps(result_line(args, "reference", args.strategy, dev_ms, e2e_ms, out[0]["h2d"], out[0]["d2h"], 0,
-                                     out[0]["clocks"], "fp32", {"engine": args.ref_backend, "engine_fallbacks": ref_notes, "final_loss": out[0]["loss"]})),
+                                     out[0]["clocks"], "fp32", {"engine": args.ref_backend, "engine_fallbacks": ref_notes, "final_loss": out[-1]["loss"]})),
               flush=True)
     finally:
         if world > 1:

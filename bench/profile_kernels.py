@@ -1,6 +1,6 @@
 """Runs ONE kernel of this library a few times on a small, fixed case, so that a profiler can capture it:
 
-    python bench/profile_kernels.py gemm_fwd | gemm_dx | gemm_dw | attn | adamw | layernorm |
+    python bench/profile_kernels.py gemm_fwd | gemm_dx | gemm_dw | attn | attn_long | adamw | layernorm |
                                                allreduce | reduce_scatter_adam | gather_gemm
 
 Inputs are larger than the 126 MB L2 where the kernel is memory-bound, and at most a few hundred MB in
@@ -44,10 +44,10 @@ def run(which, reps=3):
             a, b = rnd(K, M), rnd(K, N)
             fn = lambda: gemm(a, b, M, N, K, M, N, True, True)
         info = {"flops": 2.0 * M * N * K, "bytes": 2.0 * (M * K + N * K + M * N)}
-    elif which == "attn":
+    elif which in ("attn", "attn_long"):
         from tandem_b200.ops import causal_attention
 
-        B, T, H, hd = 16, 512, 12, 64
+        B, T, H, hd = (16, 512, 12, 64) if which == "attn" else (8, 2048, 16, 128)  # the flagship's and the 1.3B model's shapes
         qkv = rnd(B, T, 3 * H * hd).requires_grad_()
         dy = rnd(B, T, H * hd)
 

@@ -334,11 +334,11 @@ class SymmetricComm:
 
     # ------------------------------------------------------------------ heap
     def _add_segment(self, nbytes):
-        """Collective: every rank allocates a segment and maps everyone else's.  With a torch.distributed
-        NCCL group in place (and TANDEM_NVLS != 0) the segment comes from torch's symmetric-memory
-        allocator, which also binds it to an NVSwitch multicast object (for the multimem kernels);
-        otherwise it is cudaMalloc'd here and exchanged through CUDA IPC."""
-        if self.n > 1 and os.environ.get("TANDEM_VMM", "0") != "0" and self._add_segment_vmm(nbytes):
+        """Collective: every rank allocates a segment and maps everyone else's.  First choice is this library's own
+        path (cuMemCreate, descriptors over Unix sockets, its own multicast binding for the multimem kernels;
+        TANDEM_VMM=0 skips it).  If the ranks do not all succeed: torch's symmetric-memory allocator when a
+        torch.distributed NCCL group is in place (and TANDEM_NVLS != 0), else cudaMalloc + CUDA IPC (no multicast)."""
+        if self.n > 1 and os.environ.get("TANDEM_VMM", "1") != "0" and self._add_segment_vmm(nbytes):
             return
         if self.n > 1 and os.environ.get("TANDEM_NVLS", "1") != "0" and self._add_segment_multicast(nbytes):
             return
@@ -580,6 +580,25 @@ class SymmetricComm:
         self._half ^= 1
         return self.heap.peers(*self._scratch[self._half])
 
+    def _wide_scratch(self, nbytes, stream):
+        """Peer addresses of one staging block of at least nbytes, kept for later calls.  Every rank makes the same
+        calls in the same order, so all ranks grow it together.  Unlike the two alternating halves there is only one
+        such block per call kind: a barrier launch keeps this rank from overwriting what a slower peer still reads from the
+        previous call."""
+        if not hasattr(self, "_wide"):
+            self._wide = {}
+        lane = 0 if self._launch_comm is self.comm else 1  # blocking and asynchronous calls never share a block
+        held = self._wide.get(lane)
+        if held is None or held[1] < nbytes:
+            if held is not None:
+                torch.cuda.synchronize(self.device)
+                self._ptr_cache.clear()
+                self.heap.give(*held[0])
+            size = (nbytes + (8 << 20) - 1) // (8 << 20) * (8 << 20)
+            self._wide[lane] = held = (self._take(size), size)
+        check_rc(self.lib.tb_barrier(self._launch_comm, stream), "barrier")
+        return self.heap.peers(*held[0])
+
     def check(self):
         if self._status[0] != 0:
             code, rank, peer, epoch, block = (int(self._status[k]) for k in range(5))
@@ -657,10 +676,9 @@ class SymmetricComm:
                 check_rc(self.lib.tb_reduce_scatter(self._launch_comm, _ptr_array(peers), None, flat.numel(), _ll_array(offs), code,
                                                     int(average), int(self.exact16), acc, adam_p, s), "reduce_scatter")
             else:
-                if flat.numel() * flat.element_size() > self.scratch_half:
-                    raise self._error("reduce_scatter of an unregistered tensor larger than the scratch area: "
-                                      "allocate it with Group.empty() or raise TANDEM_SCRATCH_BYTES")
-                scratch = self._next_scratch()
+                # not in the heap: through the scratch area, or through a staging block that grows to the largest
+                # such call (the kernel needs the whole operand of every rank at once, so it cannot go piecewise)
+                scratch = self._next_scratch() if nbytes_ <= self.scratch_half else self._wide_scratch(nbytes_, s)
                 check_rc(self.lib.tb_memcpy_async(scratch[self.rank], flat.data_ptr(), flat.numel() * flat.element_size(), s), "memcpy")
                 check_rc(self.lib.tb_reduce_scatter(self._launch_comm, _ptr_array(scratch), None,
                                                     flat.numel(), _ll_array(offs), code, int(average), int(self.exact16),

@@ -68,6 +68,32 @@ def gpu_collectives(g):
     return r
 
 
+def wide_reduce_scatter(g):
+    """Tensors outside the heap and larger than the scratch area: staged through a block that grows on demand."""
+    r, w, dev = g.rank, g.size, g.device
+    for n in (600_001, 1_500_000, 700_000):
+        want = sum(data(q, n, torch.float32).double() for q in range(w))
+        sizes = [n // w] * w
+        sizes[0] += n - sum(sizes)
+        lo = sum(sizes[:r])
+        for async_op in (False, True):
+            x = data(r, n, torch.float32).to(dev)
+            mine = g.reduce_scatter(x, sizes, async_op=async_op)
+            if async_op:
+                mine = mine.wait()
+            assert torch.equal(mine.double().cpu(), want[lo:lo + sizes[r]]), (n, async_op)
+    g.check()
+    return r
+
+
+@needs2
+def test_reduce_scatter_of_a_tensor_larger_than_the_scratch_area(monkeypatch):
+    from tandem_b200 import launch
+
+    monkeypatch.setenv("TANDEM_SCRATCH_BYTES", str(1 << 20))
+    assert launch(wide_reduce_scatter, 2, device="cuda") == [0, 1]
+
+
 @needs2
 def test_collectives_on_two_gpus():
     from tandem_b200 import launch
@@ -604,12 +630,12 @@ def graphed_rank(g, strategy, graphed):
         for x, y in batches[3:]:
             losses.append(step_fn(x, y).item())
     else:
-        for k, (x, y) in enumerate([batches[0]] * 3 + [batches[0]] + batches[3:]):  # the same sequence of batches
+        for k, (x, y) in enumerate([batches[0]] * 3 + batches[3:]):  # the same sequence of batches (a capture runs nothing)
             loss = wrapped(x, y)
             loss.backward()
             closer.step()
             closer.zero_grad()
-            if k >= 4:
+            if k >= 3:
                 losses.append(loss.item())
     g.check()
     return losses
@@ -625,7 +651,7 @@ def test_steps_replayed_from_a_cuda_graph_track_eager_steps(strategy):
     for r in range(2):
         assert len(eager[r]) == len(replay[r]) == 5
         for a, b in zip(eager[r], replay[r]):
-            assert a == a and abs(a - b) < 2e-2, (strategy, eager[r], replay[r])
+            assert a == a and abs(a - b) < 5e-3, (strategy, eager[r], replay[r])
 
 
 def ddp_eight_rank(g):
