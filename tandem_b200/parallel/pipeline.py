@@ -33,6 +33,51 @@ def split_units(n_units, stages):
     return out
 
 
+def unit_costs(units, seq):
+    """Relative compute per unit: the weights of its Linear layers (GEMM work per token is proportional to them) plus,
+    for a unit with causal attention, seq x dim for the score and value products.  Embedding lookups cost nothing.
+    With a large vocabulary the output projection weighs as much as several transformer blocks, which is why an even
+    split by unit count leaves the last stage with the most work."""
+    costs = []
+    for unit in units:
+        c = 0.0
+        for module in unit.modules():
+            if isinstance(module, torch.nn.Linear):
+                c += module.weight.numel()
+        attn = getattr(unit, "attn", None)
+        if attn is not None:
+            width = next(attn.parameters()).shape[-1]
+            c += float(seq) * width
+        costs.append(c)
+    return costs
+
+
+def split_by_cost(costs, stages):
+    """Contiguous (lo, hi) ranges, one per stage and none empty, that minimise the largest stage cost."""
+    n = len(costs)
+    if stages > n:
+        raise ValueError("more stages than units")
+    prefix = [0.0]
+    for c in costs:
+        prefix.append(prefix[-1] + c)
+    inf = float("inf")
+    best = [[inf] * (n + 1) for _ in range(stages + 1)]  # best[s][i]: the first i units on s stages
+    cut = [[0] * (n + 1) for _ in range(stages + 1)]
+    best[0][0] = 0.0
+    for s in range(1, stages + 1):
+        for i in range(s, n - (stages - s) + 1):
+            for j in range(s - 1, i):
+                worst = max(best[s - 1][j], prefix[i] - prefix[j])
+                if worst < best[s][i]:
+                    best[s][i], cut[s][i] = worst, j
+    out, hi = [], n
+    for s in range(stages, 0, -1):
+        lo = cut[s][hi]
+        out.append((lo, hi))
+        hi = lo
+    return out[::-1]
+
+
 def plan(schedule, stages, rank, m):
     """The stage's step as a list of actions:
       ("F", i) / ("B", i)          compute micro-batch i forward / backward
@@ -63,18 +108,27 @@ def plan(schedule, stages, rank, m):
 
 
 class Pipeline:
-    def __init__(self, model, group, micro_batches, schedule="1f1b", timeline=None):
+    def __init__(self, model, group, micro_batches, schedule="1f1b", timeline=None, balance="units"):
+        """balance="units": stages get equal numbers of units (the reference's split, tandem/pipeline.py:20-32);
+        balance="cost": the contiguous split that minimises the largest stage's estimated compute (unit_costs)."""
         if schedule not in ("gpipe", "1f1b"):
             raise ValueError(f"unknown schedule {schedule}")
+        if balance not in ("units", "cost"):
+            raise ValueError(f"unknown balance {balance}")
         self.g, self.m, self.schedule = group, micro_batches, schedule
         units = model.units()
-        lo, hi = split_units(len(units), group.size)[group.rank]
+        if balance == "cost":
+            self.ranges = split_by_cost(unit_costs(units, model.config.seq), group.size)
+        else:
+            self.ranges = split_units(len(units), group.size)
+        lo, hi = self.ranges[group.rank]
         self.units = torch.nn.ModuleList(units[lo:hi])
         self.first, self.last = group.rank == 0, group.rank == group.size - 1
         self.dim = model.config.dim
         self.kernels = getattr(model.config, "kernels", "torch")
         self.timeline = timeline or Timeline(enabled=False)
         self.act_dtype = None  # None: the dtype of this stage's parameters
+        self.wire = None  # None: NCCL lanes between GPU stages, the group's own send / recv elsewhere
 
     def parameters(self):
         return self.units.parameters()
@@ -105,8 +159,11 @@ class Pipeline:
             return torch.empty(shape, device=dev, dtype=dtype)
 
         actions = plan(self.schedule, g.size, g.rank, self.m)
-        if dev.type == "cuda" and getattr(g, "transport", "device") == "device" and g.size > 1:
-            return self._run_on_lanes(actions, xs, ys, dev, dtype, shape)
+        wire = self.wire
+        if wire is None and dev.type == "cuda" and getattr(g, "transport", "device") == "device" and g.size > 1:
+            wire = g._p2p()
+        if wire is not None:
+            return self._run_on_lanes(wire, actions, xs, ys, dev, dtype, shape)
         for a in actions:
             kind = a[0]
             if kind == "F":
@@ -151,7 +208,7 @@ class Pipeline:
                     g.sendrecv(grad.contiguous(), up, act, up)
         return sum(losses) if self.last else None
 
-    def _run_on_lanes(self, actions, xs, ys, dev, dtype, shape):
+    def _run_on_lanes(self, wire, actions, xs, ys, dev, dtype, shape):
         """GPU stages over NCCL.  Nothing here blocks the host: a transfer is ordered after the compute stream when it
         is issued, and claiming a received tensor makes the compute stream wait for it.  Sends are collected and
         awaited when the step ends.
@@ -167,8 +224,7 @@ class Pipeline:
         on a second communicator were measured to stall at 8 MB messages on two B200s (each side spinning in a
         receive while the send that would release the other waited to be scheduled), so this schedule does not
         use them."""
-        g, up, down = self.g, self.g.rank - 1, self.g.rank + 1
-        wire = g._p2p()
+        up, down = self.g.rank - 1, self.g.rank + 1
         wire.lane("act")  # first use: both communicators exist and every neighbour pair is connected before real traffic
         ahead = self.schedule == "gpipe"
         takes_act = {"recv_act", "send_grad_recv_act"}
@@ -230,11 +286,12 @@ class Pipeline:
                 recvs = ([up] if recv_act else []) + ([down] if recv_grad else [])
                 if sends or recvs:
                     work, kept, received = wire.exchange(sends, recvs, shape, dtype)
-                    in_flight.append((work, kept))
                     if recv_act:
-                        act = wire.claim(work, received[0])
-                    if recv_grad:
-                        grad = wire.claim(work, received[-1])
+                        act = wire.claim(work, received[0])  # orders this stage after the whole exchange
+                    elif recv_grad:
+                        grad = wire.claim(work, received[0])
+                    else:
+                        in_flight.append((work, kept))
                 continue
             if send_act:
                 in_flight.append(wire.post_send(out.detach().contiguous(), down, "act"))

@@ -10,6 +10,7 @@ import torch
 from tandem_b200 import launch
 from tandem_b200.model import loss_fn
 from tandem_b200.pipeline import Pipeline, plan, split_units
+from tandem_b200.parallel.pipeline import split_by_cost, unit_costs
 from tandem_b200.profile import Timeline
 
 from training import Batches, flat_weights, optimize, plain_adamw, seeded_model
@@ -67,6 +68,130 @@ def test_bit_identical_to_accumulation(schedule, stages, accumulated):
         assert order == forwards + [f"B{i}" for i in range(MICRO)]
     else:  # stage 0 warms up with `stages` forwards, then its first backward comes straight away
         assert order[:stages + 1] == forwards[:stages] + ["B0"]
+
+
+class GlooWire:
+    """The transfer interface of parallel/p2p.py (lanes, receives posted ahead, grouped exchanges) over gloo, so that
+    the scheduling a GPU stage does -- what is posted when, on which lane, in which order -- runs on CPU ranks."""
+
+    def __init__(self, group, rendezvous):
+        import torch.distributed as dist
+
+        self.dist = dist
+        dist.init_process_group("gloo", init_method=f"file://{rendezvous}", rank=group.rank, world_size=group.size)
+        self.lanes = {"act": None, "grad": dist.new_group(list(range(group.size)), backend="gloo")}
+        self.log = []
+
+    def lane(self, name):
+        return self.lanes[name]
+
+    def post_recv(self, shape, dtype, src, lane):
+        buf = torch.empty(shape, dtype=dtype)
+        self.log.append(("recv", lane, src))
+        return self.dist.irecv(buf, src, group=self.lanes[lane]), buf
+
+    def claim(self, work, buf):
+        work.wait()
+        return buf
+
+    def post_send(self, tensor, dst, lane):
+        self.log.append(("send", lane, dst))
+        return self.dist.isend(tensor, dst, group=self.lanes[lane]), tensor
+
+    def exchange(self, sends, recvs, shape, dtype):
+        received = [torch.empty(shape, dtype=dtype) for _ in recvs]
+        works = [self.dist.isend(t, dst) for t, dst in sends] + [self.dist.irecv(b, src) for b, src in zip(received, recvs)]
+        self.log.append(("exchange", len(sends), len(recvs)))
+
+        class Both:
+            def wait(self):
+                for w in works:
+                    w.wait()
+
+        return Both(), [t for t, _ in sends] + received, received
+
+    def close(self):
+        self.dist.destroy_process_group()
+
+
+def lanes_rank(group, schedule, rendezvous):
+    pipe = Pipeline(seeded_model(), group, MICRO, schedule)
+    pipe.wire = GlooWire(group, rendezvous)
+    opt = plain_adamw(pipe.parameters())
+    batches = Batches(rows=ROWS)
+    losses = []
+    for k in range(OPT_STEPS):
+        loss = pipe.train_step(*batches(k))
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.item() if loss is not None else None)
+    log = pipe.wire.log
+    pipe.wire.close()
+    return losses, flat_weights(pipe.parameters()), log
+
+
+@pytest.mark.parametrize("schedule", ["gpipe", "1f1b"])
+@pytest.mark.parametrize("stages", [2, 4])
+def test_gpu_stage_scheduling_on_cpu_ranks(schedule, stages, accumulated, tmp_path):
+    want_losses, unit_weights = accumulated
+    ours = launch(lanes_rank, stages, schedule, str(tmp_path / "rendezvous"), slot_bytes=1024)
+    for rank, (lo, hi) in enumerate(split_units(len(unit_weights), stages)):
+        assert torch.equal(ours[rank][1], torch.cat(unit_weights[lo:hi])), f"stage {rank}: weights differ"
+    assert ours[-1][0] == want_losses
+    for rank in range(stages):
+        log = ours[rank][2][:len(ours[rank][2]) // OPT_STEPS]  # one step
+        if schedule == "1f1b":
+            assert all(entry[0] == "exchange" for entry in log)
+            continue
+        # GPipe: a receive is never posted before the send that forwards the previous tensor of its kind, so on a
+        # lane's stream no receive stands in front of a send its own sender may be waiting for
+        for lane in ("act", "grad"):
+            on_lane = [e[0] for e in log if e[1] == lane]
+            forwards = "send" in on_lane and "recv" in on_lane
+            if forwards:
+                assert on_lane == ["recv", "send"] * MICRO, (rank, lane, on_lane)
+            else:
+                assert len(on_lane) == MICRO and len(set(on_lane)) == 1
+
+
+def test_split_by_cost_minimises_the_heaviest_stage():
+    import itertools
+
+    assert split_by_cost([1, 1, 1], 3) == [(0, 1), (1, 2), (2, 3)]
+    assert split_by_cost([5, 1, 1, 1, 1, 5], 2) == [(0, 3), (3, 6)]
+    costs = [0.0] + [13.6] * 24 + [51.5]  # embedding, 24 blocks, a 50k-row output projection
+    assert split_by_cost(costs, 2) == [(0, 15), (15, 26)]
+    gen = torch.Generator().manual_seed(0)
+    for _ in range(30):  # against brute force over every placement of the cuts
+        n, stages = int(torch.randint(3, 9, (1,), generator=gen)), int(torch.randint(1, 4, (1,), generator=gen))
+        costs = torch.randint(0, 20, (n,), generator=gen).tolist()
+        got = split_by_cost(costs, stages)
+        assert got[0][0] == 0 and got[-1][1] == n and all(a[1] == b[0] for a, b in zip(got, got[1:])) and all(lo < hi for lo, hi in got)
+        heaviest = max(sum(costs[lo:hi]) for lo, hi in got)
+        best = min(max(sum(costs[a:b]) for a, b in zip((0,) + cuts, cuts + (n,)))
+                   for cuts in itertools.combinations(range(1, n), stages - 1))
+        assert heaviest == best
+
+
+def test_unit_costs_count_linear_weights_and_attention():
+    model = seeded_model()
+    costs = unit_costs(model.units(), model.config.seq)
+    assert costs[0] == 0  # an embedding lookup
+    width = model.config.dim
+    assert costs[1] == 12 * width * width + model.config.seq * width
+    assert costs[-1] == model.config.vocab * width
+
+
+def cost_balanced_rank(group):
+    pipe = Pipeline(seeded_model(), group, MICRO, "1f1b", balance="cost")
+    loss = pipe.train_step(*Batches(rows=ROWS)(0))
+    return pipe.ranges, None if loss is None else loss.item()
+
+
+def test_cost_balanced_stages_compute_the_same_loss(accumulated):
+    ours = launch(cost_balanced_rank, 2, slot_bytes=1024)
+    assert ours[0][0] == ours[1][0] and ours[0][0][0][0] == 0
+    assert ours[-1][1] == accumulated[0][0]
 
 
 def test_split_units_is_even_and_contiguous():
