@@ -104,8 +104,23 @@ k_ln_fwd(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ 
 // add (optional): a second gradient of the same input, summed into dx in fp32 before the one rounding
 // -- the residual branch's gradient in a pre-LayerNorm block, which autograd would otherwise add with a
 // separate pass over the activations.
+// Rows are software-pipelined: while a warp works on one row, the 16-byte loads of its next row (dy and x, kept
+// packed as bf16 so that they cost half the registers) are already in flight, and the residual gradient of the
+// current row is requested before the row's reductions start.  With one row per warp in flight the kernel ran at
+// the pace of one memory round trip per row (0.42 of the copy bandwidth); two rows per warp and two blocks per SM
+// keep about 100 KB per SM on the way.
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
 template <int MAXV>
-__global__ void __launch_bounds__(256, MAXV <= 4 ? 2 : 1)  // two blocks per SM where the row fits: a capture showed 171 registers and 12 % occupancy
+__global__ void __launch_bounds__(256, MAXV <= 4 ? 2 : 1)
 k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
          const float* __restrict__ mean_in, const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ add,
          __nv_bfloat16* __restrict__ dx, float* __restrict__ part, int M, int D) {
@@ -119,25 +134,57 @@ k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__
   for (int j = 0; j < MAXV; ++j)
 #pragma unroll
     for (int e = 0; e < 8; ++e) dw[j][e] = db[j][e] = 0.f;
-  for (int row = blockIdx.x * warps + warp; row < M; row += gridDim.x * warps) {
-    const float mean = mean_in[row], rstd = rstd_in[row];
-    float g[MAXV][8], xh[MAXV][8];
+  const int stride = gridDim.x * warps;
+  int row = blockIdx.x * warps + warp;
+  constexpr bool AHEAD = MAXV <= 4;  // wider rows have no registers left for a second row
+  uint4 ndy[MAXV], nx[MAXV];  // the next row, packed
+  float nmean = 0.f, nrstd = 0.f;
+  auto fetch = [&](int r) {
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int vi = lane + 32 * j;
+      if (vi < nvec) {
+        ndy[j] = __ldg(reinterpret_cast<const uint4*>(dy + (size_t)r * D + vi * 8));
+        nx[j] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * D + vi * 8));
+      }
+    }
+    nmean = mean_in[r];
+    nrstd = rstd_in[r];
+  };
+  if (AHEAD && row < M) fetch(row);
+  for (; row < M; row += stride) {
+    if (!AHEAD) fetch(row);
+    uint4 cdy[MAXV], cx[MAXV], cadd[MAXV];
+    const float mean = nmean, rstd = nrstd;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      cdy[j] = ndy[j];
+      cx[j] = nx[j];
+    }
+    if (AHEAD && row + stride < M) fetch(row + stride);
+    if (add != nullptr) {  // may alias dx: this row's dx is written only after these loads have been consumed
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const int vi = lane + 32 * j;
+        if (vi < nvec) cadd[j] = *reinterpret_cast<const uint4*>(add + (size_t)row * D + vi * 8);
+      }
+    }
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
       const int vi = lane + 32 * j;
       if (vi < nvec) {
         float dyv[8], xv[8], wv[8];
-        load8(dy + (size_t)row * D + vi * 8, dyv);
-        load8(x + (size_t)row * D + vi * 8, xv);
+        unpack8(cdy[j], dyv);
+        unpack8(cx[j], xv);
         load8(w + vi * 8, wv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          xh[j][e] = (xv[e] - mean) * rstd;
-          g[j][e] = dyv[e] * wv[e];
-          s1 += g[j][e];
-          s2 += g[j][e] * xh[j][e];
-          dw[j][e] += dyv[e] * xh[j][e];
+          const float xh = (xv[e] - mean) * rstd;
+          const float gv = dyv[e] * wv[e];
+          s1 += gv;
+          s2 += gv * xh;
+          dw[j][e] += dyv[e] * xh;
           db[j][e] += dyv[e];
         }
       }
@@ -148,12 +195,18 @@ k_ln_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__
     for (int j = 0; j < MAXV; ++j) {
       const int vi = lane + 32 * j;
       if (vi < nvec) {
-        float o[8];
+        float dyv[8], xv[8], wv[8], o[8];
+        unpack8(cdy[j], dyv);
+        unpack8(cx[j], xv);
+        load8(w + vi * 8, wv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = rstd * (g[j][e] - s1 - xh[j][e] * s2);
+        for (int e = 0; e < 8; ++e) {
+          const float xh = (xv[e] - mean) * rstd;  // the same operations as above: the same values
+          o[e] = rstd * (dyv[e] * wv[e] - s1 - xh * s2);
+        }
         if (add != nullptr) {
           float a[8];
-          load8(add + (size_t)row * D + vi * 8, a);
+          unpack8(cadd[j], a);
 #pragma unroll
           for (int e = 0; e < 8; ++e) o[e] += a[e];
         }
@@ -453,7 +506,9 @@ int tb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float
 }
 
 // scratch: fp32 [blocks * 2 * D] with blocks = tb_layernorm_bwd_blocks(M).
-int tb_layernorm_bwd_blocks(int M) { return grid_for(M, 8 * 4, 592); }
+// Few rows: one row per warp on as many SMs as it takes (at 1024 rows four rows per warp would leave 116 SMs idle);
+// many rows: several rows per warp, so that the row look-ahead has something to fetch.
+int tb_layernorm_bwd_blocks(int M) { return M < 8192 ? grid_for(M, 8, 296) : grid_for(M, 8 * 4, 592); }
 
 int tb_layernorm_bwd_add(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, const void* add, void* dx,
                          void* dw, void* db, float* scratch, int M, int D, cudaStream_t s);
@@ -478,6 +533,7 @@ int tb_layernorm_bwd_add(const void* dy, const void* x, const void* w, const flo
   } while (0)
   if (D <= 256 * 1) LN(1);
   else if (D <= 256 * 2) LN(2);
+  else if (D <= 256 * 3) LN(3);
   else if (D <= 256 * 4) LN(4);
   else LN(8);
 #undef LN
