@@ -246,8 +246,7 @@ def run_ours(args):
     elif args.strategy in ("gpipe", "1f1b"):
         from tandem_b200.pipeline import Pipeline
 
-        # one stage per GPU, stage traffic on NCCL p2p; units dealt out by estimated compute (the 50k-row output
-        # projection weighs about four transformer blocks)
+        # one stage per GPU, stage traffic on NCCL p2p; --balance cost deals units out by estimated compute
         wrapped = Pipeline(model, g, MICRO_BATCHES, args.strategy, balance=args.balance)
         opt = torch.optim.AdamW(wrapped.parameters(), lr=LR, weight_decay=WD, fused=True)
         closer = None
@@ -485,7 +484,7 @@ def main():
                     help="the reference's engine: its Python engine, its C++ engine, or auto (C++ with a fall-back to Python)")
     ap.add_argument("--opt", default="auto", choices=["auto", "replicated", "sharded"],
                     help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: sharded from 4 GPUs)")
-    ap.add_argument("--balance", default="cost", choices=["cost", "units"], help="gpipe / 1f1b (ours): how units are dealt out to stages")
+    ap.add_argument("--balance", default="units", choices=["cost", "units"], help="gpipe / 1f1b (ours): how units are dealt out to stages")
     ap.add_argument("--fuse", type=int, default=1, help="zero3: gather each block's qkv weight inside its GEMM kernel")
     ap.add_argument("--graph", type=int, default=1, help="record the step once as a CUDA graph and replay it (ours: ddp, zero1, zero2, zero3)")
     args = ap.parse_args()

@@ -74,7 +74,7 @@ struct GemmArgs {
   // does not depend on scheduling.
   int splits;             // 1: nothing is split
   int whole_tiles;        // tiles computed by one item each (0 when every tile is split)
-  float* partials;        // [split tile][splits - 1][column][row] floats
+  float* partials;        // [split tile][splits - 1][column quad][row][4] floats
   unsigned* split_flags;  // [split tile][splits - 1][8 epilogue warps], zero between launches (the consumer resets them)
 };
 
@@ -625,7 +625,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
       tile_origin(tile, &m0, &n0);
       void* out = g.out;
       const int part = part_of(tile), split_tile = tile_of(tile) - whole;
-      // this warp's share of the parked partial tiles of its output tile: [part - 1][column][row]
+      // this warp's share of the parked partial tiles of its output tile: [part - 1][column quad][row][4]
       float* parked = part >= 0 ? g.partials + (size_t)split_tile * (splits - 1) * (BM * BN) : nullptr;
       unsigned* my_flags = part >= 0 ? g.split_flags + ((size_t)split_tile * (splits - 1)) * 8 + (warp - 2) : nullptr;
       const int tile_row = half * 128 + quarter * 32 + lane;
@@ -676,29 +676,43 @@ k_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtens
           tmem_ld32(taddr + (c + 1) * 32, rb);
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
-          if (part > 0) {  // producer: park the raw accumulator column by column (lanes = consecutive rows: full 128-byte lines)
-            float* dst = parked + (size_t)(part - 1) * (BM * BN) + (size_t)c * 32 * BM + tile_row;
+          // Parked layout: [part - 1][column quad][row][4 floats].  A lane's four consecutive columns are one 16-byte
+          // vector and consecutive lanes (rows) are consecutive vectors, so a warp moves 512 contiguous bytes per
+          // instruction, 16 instructions per 64 columns.
+          if (part > 0) {  // producer: park the raw accumulator
+            float4* dst = reinterpret_cast<float4*>(parked + (size_t)(part - 1) * (BM * BN)) + (size_t)c * 8 * BM + tile_row;
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              __stcg(dst + (size_t)e * BM, __uint_as_float(ra[e]));
-              __stcg(dst + (size_t)(32 + e) * BM, __uint_as_float(rb[e]));
+            for (int q = 0; q < 8; ++q) {
+              __stcg(dst + (size_t)q * BM, make_float4(__uint_as_float(ra[4 * q]), __uint_as_float(ra[4 * q + 1]),
+                                                       __uint_as_float(ra[4 * q + 2]), __uint_as_float(ra[4 * q + 3])));
+              __stcg(dst + (size_t)(8 + q) * BM, make_float4(__uint_as_float(rb[4 * q]), __uint_as_float(rb[4 * q + 1]),
+                                                             __uint_as_float(rb[4 * q + 2]), __uint_as_float(rb[4 * q + 3])));
             }
             continue;
           }
           if (part == 0) {  // consumer: fold the parked tiles in, in part order
             if (!ok) continue;
             for (int p = 0; p < splits - 1; ++p) {
-              const float* src = parked + (size_t)p * (BM * BN) + (size_t)c * 32 * BM + tile_row;
-              float va[32], vb[32];
+              const float4* src = reinterpret_cast<const float4*>(parked + (size_t)p * (BM * BN)) + (size_t)c * 8 * BM + tile_row;
+              // all sixteen loads of a part are issued before the first add: one trip to L2 per part, not one per batch
+              // the compiler happens to pick (volatile asm statements keep their order)
+              float4 v[16];
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                va[e] = __ldcg(src + (size_t)e * BM);
-                vb[e] = __ldcg(src + (size_t)(32 + e) * BM);
-              }
+              for (int q = 0; q < 16; ++q)
+                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(v[q].x), "=f"(v[q].y), "=f"(v[q].z), "=f"(v[q].w)
+                             : "l"(src + (size_t)q * BM)
+                             : "memory");
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                ra[e] = __float_as_uint(__uint_as_float(ra[e]) + va[e]);
-                rb[e] = __float_as_uint(__uint_as_float(rb[e]) + vb[e]);
+              for (int q = 0; q < 8; ++q) {
+                ra[4 * q] = __float_as_uint(__uint_as_float(ra[4 * q]) + v[q].x);
+                ra[4 * q + 1] = __float_as_uint(__uint_as_float(ra[4 * q + 1]) + v[q].y);
+                ra[4 * q + 2] = __float_as_uint(__uint_as_float(ra[4 * q + 2]) + v[q].z);
+                ra[4 * q + 3] = __float_as_uint(__uint_as_float(ra[4 * q + 3]) + v[q].w);
+                rb[4 * q] = __float_as_uint(__uint_as_float(rb[4 * q]) + v[8 + q].x);
+                rb[4 * q + 1] = __float_as_uint(__uint_as_float(rb[4 * q + 1]) + v[8 + q].y);
+                rb[4 * q + 2] = __float_as_uint(__uint_as_float(rb[4 * q + 2]) + v[8 + q].z);
+                rb[4 * q + 3] = __float_as_uint(__uint_as_float(rb[4 * q + 3]) + v[8 + q].w);
               }
             }
           }
@@ -1057,12 +1071,13 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
 // 0.34 - 0.43 us on the 128-row tiles whatever their width (the main loop is bound by bytes in flight / load latency,
 // not by the tensor pipe) and 0.77 us on the 256 x 256 tile, whose two accumulators fill TMEM so that its epilogue
 // (about 5 us) cannot overlap the next tile; a kernel's start-up and drain cost about 5 us; folding parked partial
-// tiles costs about 6 us plus 9 us per extra part (producer drain, flag, dependent loads).  With those prices the
-// split only pays for the square weight gradients (a few dozen output tiles, K = tokens).
+// tiles costs about 2.5 us plus 1.7 us per extra part (producer drain, flag, one trip to L2 per part) plus 0.3 us per
+// parked megabyte.  With those prices the split pays where a round of tiles is less than about half full and the
+// reduction is long: the weight gradients (K = tokens) and, at 1024 - 2048 tokens, the K = 3072 products.
 struct TileShape { int id, bm, bn; double per_kblock, per_tile; };
-constexpr TileShape SHAPES[4] = {{0, 256, 256, 0.77, 5.3}, {1, 128, 256, 0.43, 0.5}, {2, 128, 128, 0.34, 0.6}, {5, 128, 192, 0.41, 1.0}};
+constexpr TileShape SHAPES[4] = {{0, 256, 256, 0.77, 5.3}, {1, 128, 256, 0.43, 0.5}, {2, 128, 128, 0.34, 0.6}, {5, 128, 192, 0.41, 0.6}};
 constexpr int MAX_SPLITS = 8;
-constexpr double START_US = 5.0, FOLD_US = 6.0, FOLD_PART_US = 9.0, FOLD_US_PER_MB = 0.35;
+constexpr double START_US = 5.0, FOLD_US = 2.5, FOLD_PART_US = 1.7, FOLD_US_PER_MB = 0.3;
 
 int g_forced_tile = -1;   // 0: 256x256, 1: 128x256, 2: 128x128, 3 / 4: CTA pair 256x256 / 256x128, 5: 128x192; -1: planned
 int g_forced_splits = 0;  // > 0: that many k-parts for the tail (where the reduction is long enough); 0: planned
