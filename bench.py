@@ -226,9 +226,11 @@ def run_ours(args):
     if pure_bf16:
         model = model.bfloat16()  # fp32 master weights live in the optimizer
     graphed = bool(args.graph) and args.strategy in ("ddp", "zero1", "zero2", "zero3")
-    # measured at 2 GPUs the replicated update is faster (7.4 vs 8.1 ms: without the switch the reduce-scatter + all-gather
-    # pair costs more than it saves); from 4 ranks the reduce-scatter runs in the switch and the saving grows with N
-    sharded_opt = args.opt == "sharded" or (args.opt == "auto" and world >= 4)
+    # measured: the replicated update is the faster one at this model size (2 GPUs: 7.4 vs 8.1 ms, 4 GPUs: 5.4 vs 6.5 ms).
+    # Sharding saves (N-1)/N of 0.37 ms of optimizer traffic but puts a reduce-scatter -> all-gather chain per bucket on
+    # the path to the next forward, where the all-reduce overlaps backward completely.  It is what to use when the
+    # optimizer state does not fit (1/N of the memory), so it stays selectable.
+    sharded_opt = args.opt == "sharded"
     if args.strategy == "ddp":
         wrapped = DDP(model, g, rebuild=False)
         # replicated: all-reduce + one AdamW kernel per bucket on every rank; sharded: reduce-scatter with the AdamW
@@ -483,8 +485,8 @@ def main():
     ap.add_argument("--ref-backend", default=os.environ.get("TANDEM_REF_BACKEND", "python"), choices=["auto", "python", "cpp"],
                     help="the reference's engine: its Python engine, its C++ engine, or auto (C++ with a fall-back to Python)")
     ap.add_argument("--opt", default="auto", choices=["auto", "replicated", "sharded"],
-                    help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: sharded from 4 GPUs)")
-    ap.add_argument("--balance", default="units", choices=["cost", "units"], help="gpipe / 1f1b (ours): how units are dealt out to stages")
+                    help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: replicated)")
+    ap.add_argument("--balance", default="cost", choices=["cost", "units"], help="gpipe / 1f1b (ours): how units are dealt out to stages")
     ap.add_argument("--fuse", type=int, default=1, help="zero3: gather each block's qkv weight inside its GEMM kernel")
     ap.add_argument("--graph", type=int, default=1, help="record the step once as a CUDA graph and replay it (ours: ddp, zero1, zero2, zero3)")
     args = ap.parse_args()

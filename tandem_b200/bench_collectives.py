@@ -174,6 +174,29 @@ def main():
                     ours = lambda: g.all_gather(mine)
                     nccl = lambda: dist.all_gather_into_tensor(theirs, chunk)
                     factor = (n - 1) / n
+                elif op == "reduce_scatter_adamw":
+                    # the fused form DDP's sharded optimizer and ZeRO use: bf16 gradients averaged over the ranks, AdamW on
+                    # this rank's chunk (fp32 master weights and moments, bf16 shadow) inside the same kernel.  The NCCL
+                    # column is the unfused sequence: reduce-scatter, then torch's fused AdamW on an fp32 copy of the chunk.
+                    if numel % n or dtype != torch.bfloat16:
+                        continue
+                    from tandem_b200.parallel.symm import AdamArgs
+
+                    per = numel // n
+                    p32, m32, v32 = (torch.zeros(per, device="cuda") for _ in range(3))
+                    shadow = torch.zeros(per, device="cuda", dtype=torch.bfloat16)
+                    args_ = AdamArgs.make(p32, m32, v32, (1 - 3e-5, 0.1, 0.999, 0.001, 0.0316, 1e-8, -3e-4), True, shadow)
+                    ours = lambda: g.reduce_scatter(mine, op="avg", adam=args_)
+                    q32 = torch.zeros(per, device="cuda", requires_grad=True)
+                    opt = torch.optim.AdamW([q32], lr=3e-4, weight_decay=0.1, fused=True)
+
+                    def nccl():
+                        dist.reduce_scatter_tensor(chunk, theirs, op=dist.ReduceOp.AVG)
+                        q32.grad = chunk.float()
+                        opt.step()
+                        shadow.copy_(q32.detach())
+
+                    factor = (n - 1) / n
                 else:
                     ours = lambda: g.broadcast(mine, root=0)
                     nccl = lambda: dist.broadcast(theirs, 0)
@@ -183,6 +206,13 @@ def main():
                 row = {"op": op, "dtype": dname, "bytes": nbytes, "ranks": n, "ours_us": round(t_ours * 1e3, 2),
                        "nccl_us": round(t_nccl * 1e3, 2), "ours_bus_GBps": round(nbytes / t_ours / 1e6 * factor, 1),
                        "nccl_bus_GBps": round(nbytes / t_nccl / 1e6 * factor, 1), "ratio": round(t_nccl / t_ours, 3)}
+                if op == "reduce_scatter_adamw":
+                    # what the fused kernel cannot beat: this GPU's links carry (n-1)/n of the buffer (measured peer
+                    # bandwidth 770 GB/s per direction), its HBM the chunk's optimizer state twice and the operands once
+                    link_us = nbytes * (n - 1) / n / 770e3
+                    hbm_us = (nbytes + (numel // n) * (4 * 3 * 2 + 2)) / 6552e3
+                    row["roofline_us"] = round(max(link_us, hbm_us), 2)
+                    row["fraction_of_roofline"] = round(max(link_us, hbm_us) / (t_ours * 1e3), 3)
                 rows.append(row)
                 if rank == 0:
                     print(json.dumps(row), flush=True)
