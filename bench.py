@@ -223,6 +223,9 @@ def run_ours(args):
     kernels = args.kernels
     model = GPT(Config(kernels=kernels, **MODEL)).to(dev)
     pure_bf16 = kernels == "b200"
+    fp32 = args.precision == "fp32"  # the reference's precision: this runtime's engine and strategies on torch's fp32 kernels
+    if fp32 and pure_bf16:
+        raise SystemExit("--precision fp32 needs --kernels torch (the hand-written kernels compute in bf16)")
     if pure_bf16:
         model = model.bfloat16()  # fp32 master weights live in the optimizer
     graphed = bool(args.graph) and args.strategy in ("ddp", "zero1", "zero2", "zero3")
@@ -263,7 +266,7 @@ def run_ours(args):
             opt.step()
             opt.zero_grad()
             return loss if loss is not None else torch.zeros((), device=dev)
-        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=not pure_bf16):
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=not pure_bf16 and not fp32):
             loss = wrapped(x, y)
         loss.backward()
         finish()
@@ -274,7 +277,7 @@ def run_ours(args):
         from tandem_b200.parallel.graph import GraphedStep
 
         ex = torch.zeros(per_rank, MODEL["seq"], dtype=torch.long, device=dev)
-        step_fn = GraphedStep(wrapped, closer, ex, ex.clone(), autocast=None if pure_bf16 else torch.bfloat16)
+        step_fn = GraphedStep(wrapped, closer, ex, ex.clone(), autocast=None if pure_bf16 or fp32 else torch.bfloat16)
 
     def reduce_max(v):
         if world == 1:
@@ -302,7 +305,7 @@ def run_ours(args):
     nvls = bool(g._sym is not None and g._sym.nvls)
     g.close()
     if rank == 0:
-        print(json.dumps(result_line(args, "ours", args.strategy, dev_ms, e2e_ms, h2d, d2h, int(launches), clocks, "bf16",
+        print(json.dumps(result_line(args, "ours", args.strategy, dev_ms, e2e_ms, h2d, d2h, int(launches), clocks, "fp32" if fp32 else "bf16",
                                      {"kernels": kernels, "final_loss": last, "cuda_graph": bool(graphed), "nvls": nvls,
                                       "optimizer": ("sharded over ranks, fused into the reduce-scatter" if sharded_opt else "replicated")
                                       if args.strategy == "ddp" else ("per stage (torch fused AdamW)" if pipelined else "sharded")})), flush=True)
@@ -445,6 +448,7 @@ def run_reference(args):
             return
         sys.path.insert(0, ref)
         os.environ["PYTHONPATH"] = ref + os.pathsep + ROOT + os.pathsep + os.environ.get("PYTHONPATH", "")
+        os.environ.setdefault("TANDEM_TIMEOUT", "180")  # the reference's own limit on its waits: a stuck engine ends in its CommError
         import tandem
 
         # "auto": the reference's C++ engine (its faster one, selected with backend="cpp" and built by the reference
@@ -482,10 +486,12 @@ def main():
     ap.add_argument("--model", default="85.8m", choices=["85.8m", "1.3b", "pp24"],
                     help="85.8m: the flagship; 1.3b: the ZeRO-3 configuration; pp24: the 24-layer pipeline configuration")
     ap.add_argument("--kernels", default=os.environ.get("TANDEM_BENCH_KERNELS", "b200"), choices=["torch", "b200"])
-    ap.add_argument("--ref-backend", default=os.environ.get("TANDEM_REF_BACKEND", "python"), choices=["auto", "python", "cpp"],
+    ap.add_argument("--ref-backend", default=os.environ.get("TANDEM_REF_BACKEND", "auto"), choices=["auto", "python", "cpp"],
                     help="the reference's engine: its Python engine, its C++ engine, or auto (C++ with a fall-back to Python)")
     ap.add_argument("--opt", default="auto", choices=["auto", "replicated", "sharded"],
                     help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: replicated)")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"],
+                    help="fp32 (with --kernels torch): no autocast, the reference's precision, for a same-precision comparison")
     ap.add_argument("--balance", default="cost", choices=["cost", "units"], help="gpipe / 1f1b (ours): how units are dealt out to stages")
     ap.add_argument("--fuse", type=int, default=1, help="zero3: gather each block's qkv weight inside its GEMM kernel")
     ap.add_argument("--graph", type=int, default=1, help="record the step once as a CUDA graph and replay it (ours: ddp, zero1, zero2, zero3)")
