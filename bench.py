@@ -490,6 +490,7 @@ def main():
                     help="the reference's engine: its Python engine, its C++ engine, or auto (C++ with a fall-back to Python)")
     ap.add_argument("--opt", default="auto", choices=["auto", "replicated", "sharded"],
                     help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: replicated)")
+    ap.add_argument("--global-batch", type=int, default=0, help="analysis: another global batch than the configuration's (ours and torch arms)")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"],
                     help="fp32 (with --kernels torch): no autocast, the reference's precision, for a same-precision comparison")
     ap.add_argument("--balance", default="cost", choices=["cost", "units"], help="gpipe / 1f1b (ours): how units are dealt out to stages")
@@ -498,6 +499,10 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     select_model(args.model)
+    if args.global_batch:
+        # analysis only: e.g. --gpus 1 --global-batch 2 is one rank's share of the flagship at 8 GPUs, without communication
+        global GLOBAL_BATCH, PUBLISHED_TOKENS_PER_S
+        GLOBAL_BATCH, PUBLISHED_TOKENS_PER_S = args.global_batch, None
     if args.impl == "reference":
         run_reference(args)
     elif args.impl == "torch":
