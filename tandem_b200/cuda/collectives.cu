@@ -314,6 +314,42 @@ __device__ __forceinline__ void adam_elem(const AdamArgs& a, long long j, float 
   if (a.shadow != nullptr) a.shadow[j] = __float2bfloat16_rn(p);
 }
 
+// The same for N consecutive elements (N = 4 or 8: one 16-byte gradient vector).  Where the optimizer state is 16-byte
+// aligned at j0 it moves as float4 vectors (and the shadow as one 8- or 16-byte store) instead of 4-byte accesses that
+// use an eighth of every sector they touch; same arithmetic, same results.
+template <int N>
+__device__ __forceinline__ void adam_vec(const AdamArgs& a, long long j0, const float* g) {
+  const uintptr_t state = (uintptr_t)(a.param + j0) | (uintptr_t)(a.exp_avg + j0) | (uintptr_t)(a.exp_avg_sq + j0);
+  const bool aligned = (state & 15) == 0 && (a.shadow == nullptr || ((uintptr_t)(a.shadow + j0) & (N * 2 - 1)) == 0);
+  if (!aligned) {
+#pragma unroll
+    for (int e = 0; e < N; ++e) adam_elem(a, j0 + e, g[e]);
+    return;
+  }
+  float p[N], m[N], v[N];
+#pragma unroll
+  for (int q = 0; q < N / 4; ++q) {
+    *reinterpret_cast<float4*>(p + 4 * q) = *reinterpret_cast<const float4*>(a.param + j0 + 4 * q);
+    *reinterpret_cast<float4*>(m + 4 * q) = *reinterpret_cast<const float4*>(a.exp_avg + j0 + 4 * q);
+    *reinterpret_cast<float4*>(v + 4 * q) = *reinterpret_cast<const float4*>(a.exp_avg_sq + j0 + 4 * q);
+  }
+#pragma unroll
+  for (int e = 0; e < N; ++e) adam_update(p[e], m[e], v[e], g[e], a.s);
+#pragma unroll
+  for (int q = 0; q < N / 4; ++q) {
+    *reinterpret_cast<float4*>(a.param + j0 + 4 * q) = *reinterpret_cast<const float4*>(p + 4 * q);
+    *reinterpret_cast<float4*>(a.exp_avg + j0 + 4 * q) = *reinterpret_cast<const float4*>(m + 4 * q);
+    *reinterpret_cast<float4*>(a.exp_avg_sq + j0 + 4 * q) = *reinterpret_cast<const float4*>(v + 4 * q);
+  }
+  if (a.shadow != nullptr) {
+    __nv_bfloat162 h[N / 2];
+#pragma unroll
+    for (int e = 0; e < N / 2; ++e) h[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+    if (N == 8) *reinterpret_cast<uint4*>(a.shadow + j0) = *reinterpret_cast<const uint4*>(h);
+    else *reinterpret_cast<uint2*>(a.shadow + j0) = *reinterpret_cast<const uint2*>(h);
+  }
+}
+
 template <typename T, bool EXACT, int EPI, int NR>  // EPI 0: store only, 1: += into acc_out, 2: fused AdamW (T must be float)
 __global__ void __launch_bounds__(TB_COMM_THREADS, 6)
 k_reduce_scatter(CommCtx c, PeerPtrs buf, Locals lin, long long numel, Bounds bounds, int smode, float sval, Locals acc,
@@ -344,10 +380,15 @@ k_reduce_scatter(CommCtx c, PeerPtrs buf, Locals lin, long long numel, Bounds bo
       if (EPI != 0) {
         const long long i0 = off / (long long)sizeof(T);
         const T* e = reinterpret_cast<const T*>(&r);
+        if (EPI == 1) {
 #pragma unroll
-        for (int j = 0; j < N; ++j) {
-          if (EPI == 1) acc_out[i0 - lo + j] = from_f<T>(__fadd_rn(to_f<T>(acc_out[i0 - lo + j]), to_f<T>(e[j])));
-          if (EPI == 2) adam_elem(adam, i0 - lo + j, to_f<T>(e[j]));
+          for (int j = 0; j < N; ++j) acc_out[i0 - lo + j] = from_f<T>(__fadd_rn(to_f<T>(acc_out[i0 - lo + j]), to_f<T>(e[j])));
+        }
+        if (EPI == 2) {
+          float gv[N];
+#pragma unroll
+          for (int j = 0; j < N; ++j) gv[j] = to_f<T>(e[j]);
+          adam_vec<N>(adam, i0 - lo, gv);
         }
       }
     });
@@ -543,11 +584,15 @@ k_reduce_scatter_nvls(CommCtx c, const char* mc, char* local, long long lo, long
           st_vec(local + lo + vv * 16, x[u]);
           if (EPI != 0) {
             const T* r = reinterpret_cast<const T*>(&x[u]);  // the value as stored (rounded to T), like the peer-to-peer kernel
+            if (EPI == 1) {
 #pragma unroll
-            for (int e = 0; e < N; ++e) {
-              const long long j = vv * N + e;
-              if (EPI == 1) acc_out[j] = from_f<T>(__fadd_rn(to_f<T>(acc_out[j]), to_f<T>(r[e])));
-              if (EPI == 2) adam_elem(adam, j, to_f<T>(r[e]));
+              for (int e = 0; e < N; ++e) acc_out[vv * N + e] = from_f<T>(__fadd_rn(to_f<T>(acc_out[vv * N + e]), to_f<T>(r[e])));
+            }
+            if (EPI == 2) {
+              float gv[N];
+#pragma unroll
+              for (int e = 0; e < N; ++e) gv[e] = to_f<T>(r[e]);
+              adam_vec<N>(adam, vv * N, gv);
             }
           }
         }
