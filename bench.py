@@ -241,7 +241,8 @@ def run_ours(args):
         opt = (ShardedBucketAdamW if sharded_opt else BucketAdamW)(wrapped, lr=LR, weight_decay=WD)
         closer = opt
     elif args.strategy in ("zero1", "zero2"):
-        wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD), fused_step=True, capturable=graphed)
+        wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD), fused_step=bool(args.fused_step),
+                       capturable=graphed)
         closer = wrapped
     elif args.strategy == "zero3":
         # the GEMM that gathers its own weight keeps a host-side epoch per call, so it is not recorded into graphs
@@ -490,6 +491,7 @@ def main():
                     help="the reference's engine: its Python engine, its C++ engine, or auto (C++ with a fall-back to Python)")
     ap.add_argument("--opt", default="auto", choices=["auto", "replicated", "sharded"],
                     help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: replicated)")
+    ap.add_argument("--fused-step", type=int, default=1, help="zero2: AdamW inside the reduce-scatter kernels (1) or as its own kernel in step() (0)")
     ap.add_argument("--global-batch", type=int, default=0, help="analysis: another global batch than the configuration's (ours and torch arms)")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"],
                     help="fp32 (with --kernels torch): no autocast, the reference's precision, for a same-precision comparison")
