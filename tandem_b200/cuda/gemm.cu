@@ -1218,10 +1218,11 @@ long long tb_gemm_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (g_sm_count == 0) {
     int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      g_sm_count = 0;
+    cudaGetLastError();
   }
-  const GemmPlan plan = plan_gemm(M, N, K, g_sm_count);
+  const GemmPlan plan = plan_gemm(M, N, K, g_sm_count > 0 ? g_sm_count : 148);
   if (plan.splits <= 1) return 0;
   const long long tiles = (long long)((M + plan.bm - 1) / plan.bm) * ((N + plan.bn - 1) / plan.bn);
   return (tiles - plan.whole_tiles) * (plan.splits - 1) * plan.bm * plan.bn * 4;
@@ -1231,10 +1232,12 @@ long long tb_gemm_workspace_bytes(int M, int N, int K) {
 void tb_gemm_plan(int M, int N, int K, int* out4) {
   if (g_sm_count == 0) {
     int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      g_sm_count = 0;
+    cudaGetLastError();
   }
-  const GemmPlan plan = plan_gemm(M, N, K, g_sm_count);
+  // without a device (a build machine) the plan is the one a B200's 148 SMs would get
+  const GemmPlan plan = plan_gemm(M, N, K, g_sm_count > 0 ? g_sm_count : 148);
   out4[0] = plan.bm;
   out4[1] = plan.bn;
   out4[2] = plan.splits;
