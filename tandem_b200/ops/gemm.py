@@ -28,8 +28,11 @@ def _repack(t2):
     return out
 
 
-def gemm(a, b, M, N, K, lda, ldb, a_mn, b_mn, flags=0, bias=None, aux_in=None, aux_out=None, out=None, out_dtype=torch.bfloat16):
-    """out[M, N] = op(a) . op(b) (+ epilogue).  Returns a [M, N] view with a 16-byte-aligned row stride."""
+def gemm(a, b, M, N, K, lda, ldb, a_mn, b_mn, flags=0, bias=None, aux_in=None, aux_out=None, out=None, out_dtype=torch.bfloat16,
+         workspace=None):
+    """out[M, N] = op(a) . op(b) (+ epilogue).  Returns a [M, N] view with a 16-byte-aligned row stride.
+    workspace: a uint8 tensor of at least gemm_workspace(M, N, K) bytes, for callers that launch on another stream
+    than the one their memory belongs to (else it is allocated here)."""
     if out is None:
         out = empty_padded(M, N, out_dtype, a.device)
     ldc = out.stride(0) if M > 1 else pad8(N)
@@ -40,7 +43,10 @@ def gemm(a, b, M, N, K, lda, ldb, a_mn, b_mn, flags=0, bias=None, aux_in=None, a
     # Problems with too few output tiles for the SMs (weight gradients, small per-rank batches) are computed with the
     # reduction cut into parts inside the one kernel; it parks partial tiles in this workspace.
     need = lib().tb_gemm_workspace_bytes(M, N, K)
-    workspace = torch.empty(need, dtype=torch.uint8, device=a.device) if need else None
+    if need and (workspace is None or workspace.numel() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    if not need:
+        workspace = None
     rc = lib().tb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), flags,
                             bias.data_ptr() if bias is not None else None,
                             aux_in.data_ptr() if aux_in is not None else None,
@@ -83,6 +89,59 @@ def _grad_bias(dy2, ldy):
     return out
 
 
+# The two products of a layer's backward that share dY -- the weight (and bias) gradient and the input gradient --
+# do not depend on each other.  With few tokens per rank neither fills the GPU (48-144 CTAs for 148 SMs), so the
+# parameter gradients run on a second stream beside the input gradient; the streams fork and join inside one backward
+# call, which a CUDA-graph capture records as two branches.  Everything the side stream touches is allocated on the
+# caller's stream beforehand and outlives the join, so the caching allocator's per-stream pools never see a block
+# used by a stream it does not know about.
+SIDE_BELOW_TOKENS = 4096  # with more tokens each product fills the SMs by itself and the fork only adds two event waits
+_side_streams = {}
+
+
+def _parameter_grads_beside(dy2, ldy, x2, ldx, dtype, want_w, want_b):
+    """(dW, dB, join): starts dW = dY^T . X and dB = column sums of dY on the side stream when the problem is small;
+    join() makes the caller's stream wait for them (call it after queuing the input gradient)."""
+    M, N = dy2.shape
+    K = x2.shape[1]
+    if not (want_w or want_b):
+        return None, None, lambda: None
+    if M >= SIDE_BELOW_TOKENS or not dy2.is_cuda:
+        dw = _grad_weight(dy2, ldy, x2, ldx, dtype) if want_w else None
+        db = _grad_bias(dy2, ldy) if want_b else None
+        return dw, db, lambda: None
+    dev = dy2.device
+    main = torch.cuda.current_stream(dev)
+    side = _side_streams.get(dev.index)
+    if side is None:
+        side = _side_streams[dev.index] = torch.cuda.Stream(dev)
+    dw = db = scratch = workspace = None
+    if want_w:
+        if pad8(K) != K:  # a padded product needs a compaction copy afterwards: keep that case on one stream
+            dw = _grad_weight(dy2, ldy, x2, ldx, dtype)
+            want_w = False
+        else:
+            dw = torch.empty(N, K, dtype=dtype, device=dev)
+            need = lib().tb_gemm_workspace_bytes(N, K, M)
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev) if need else None
+    if want_b:
+        db = torch.empty(N, dtype=torch.bfloat16, device=dev)
+        scratch = torch.empty(32 * N, dtype=torch.float32, device=dev)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        if want_w:
+            gemm(dy2, x2, N, K, M, ldy, ldx, True, True, 0, out=dw, workspace=workspace)
+        if want_b:
+            check_rc(lib().tb_col_sum(dy2.data_ptr(), M, N, ldy, db.data_ptr(), scratch.data_ptr(), side.cuda_stream), "col_sum")
+    keep = (scratch, workspace)  # released by the caller's frame, after the join
+
+    def join():
+        main.wait_stream(side)
+        return keep
+
+    return dw, db, join
+
+
 # Weights whose all-gather the next forward GEMM performs itself: data_ptr of the weight's place in the local flat
 # buffer -> (GatheredLinear, event to wait for afterwards or None).  ZeRO-3 fills it when it starts a unit's gather.
 GATHERED = {}
@@ -118,14 +177,13 @@ class _Linear(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w = ctx.saved_tensors
         dy2, ldy = _rows(dy)
-        dx = dw = db = dres = None
+        dx = dres = None
+        dw, db, join = _parameter_grads_beside(dy2, ldy, x2, ctx.ldx, w.dtype, ctx.needs_input_grad[1],
+                                                ctx.has_bias and ctx.needs_input_grad[2])
         if ctx.needs_input_grad[0]:
             dx = _grad_input(dy2, ldy, w)
             dx = dx.view(ctx.in_shape) if dx.is_contiguous() else dx.unflatten(0, ctx.in_shape[:-1])
-        if ctx.needs_input_grad[1]:
-            dw = _grad_weight(dy2, ldy, x2, ctx.ldx, w.dtype)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = _grad_bias(dy2, ldy)
+        join()
         if ctx.has_res and ctx.needs_input_grad[3]:
             dres = dy
         return dx, dw, db, dres
@@ -156,16 +214,16 @@ class _MLP(torch.autograd.Function):
         x2, w1, w2, slope, h = ctx.saved_tensors
         need = ctx.needs_input_grad
         dy2, ldy = _rows(dy)
-        dw2 = _grad_weight(dy2, ldy, h, h.stride(0), w2.dtype) if need[3] else None
-        db2 = _grad_bias(dy2, ldy) if need[4] else None
+        dw2, db2, join2 = _parameter_grads_beside(dy2, ldy, h, h.stride(0), w2.dtype, need[3], need[4])
         dpre = _grad_input(dy2, ldy, w2, DGELU, slope)  # (dY . W2) * gelu'(pre)
+        join2()
         ldp = dpre.stride(0)
-        dw1 = _grad_weight(dpre, ldp, x2, ctx.ldx, w1.dtype) if need[1] else None
-        db1 = _grad_bias(dpre, ldp) if need[2] else None
+        dw1, db1, join1 = _parameter_grads_beside(dpre, ldp, x2, ctx.ldx, w1.dtype, need[1], need[2])
         dx = None
         if need[0]:
             dx = _grad_input(dpre, ldp, w1)
             dx = dx.view(ctx.in_shape) if dx.is_contiguous() else dx.unflatten(0, ctx.in_shape[:-1])
+        join1()
         return dx, dw1, db1, dw2, db2, (dy if need[5] else None)
 
 
