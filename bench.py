@@ -238,7 +238,10 @@ def run_ours(args):
         wrapped = DDP(model, g, rebuild=False)
         # replicated: all-reduce + one AdamW kernel per bucket on every rank; sharded: reduce-scatter with the AdamW
         # update in its epilogue + all-gather of the parameters (same values, 1/N of the optimizer traffic per rank)
-        opt = (ShardedBucketAdamW if sharded_opt else BucketAdamW)(wrapped, lr=LR, weight_decay=WD)
+        if sharded_opt:
+            opt = ShardedBucketAdamW(wrapped, lr=LR, weight_decay=WD)
+        else:  # each span is updated as soon as its all-reduce has finished, beside the rest of backward
+            opt = BucketAdamW(wrapped, lr=LR, weight_decay=WD, during_backward=bool(args.update_during_backward))
         closer = opt
     elif args.strategy in ("zero1", "zero2"):
         wrapped = ZeRO(model, g, int(args.strategy[-1]), ShardedAdamW(lr=LR, weight_decay=WD), fused_step=bool(args.fused_step),
@@ -491,6 +494,7 @@ def main():
                     help="the reference's engine: its Python engine, its C++ engine, or auto (C++ with a fall-back to Python)")
     ap.add_argument("--opt", default="auto", choices=["auto", "replicated", "sharded"],
                     help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: replicated)")
+    ap.add_argument("--update-during-backward", type=int, default=1, help="ddp, replicated optimizer: update each span right after its all-reduce (1) or all spans after backward (0)")
     ap.add_argument("--fused-step", type=int, default=1, help="zero2: AdamW inside the reduce-scatter kernels (1) or as its own kernel in step() (0)")
     ap.add_argument("--global-batch", type=int, default=0, help="analysis: another global batch than the configuration's (ours and torch arms)")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"],

@@ -273,6 +273,19 @@ def _mirror_parameters(ddp, symmetric):
     return out
 
 
+class _AfterEvent:
+    """What a reducer returns when its last piece of work ran on a stream of its own: waiting is a stream dependency."""
+
+    def __init__(self, event, device):
+        self._event, self._device = event, device
+
+    def wait(self):
+        torch.cuda.current_stream(self._device).wait_event(self._event)
+
+    def is_completed(self):
+        return self._event.query()
+
+
 class BucketAdamW:
     """AdamW over a DDP wrapper's spans, replicated on every rank: one fused kernel per span.
 
@@ -283,9 +296,15 @@ class BucketAdamW:
     it runs torch's operation sequence, so results equal torch's per-parameter AdamW bit for bit.
 
     Create it once the span layout is final: pass rebuild=False to DDP, or create it after the first backward.
+
+    during_backward (GPU ranks): a span is updated as soon as its all-reduce has finished, on a stream of its own
+    beside the rest of backward, instead of all spans after backward (the update streams through HBM while the
+    remaining backward GEMMs keep the tensor pipes busy; nothing in backward reads a parameter again once its
+    gradient is complete).  `step()` then only closes the step.  As with the sharded form, every backward that
+    reduces also updates: accumulate over several backward passes under `no_sync()`.
     """
 
-    def __init__(self, ddp, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2):
+    def __init__(self, ddp, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, during_backward=False):
         from .optim import ShardedAdamW
 
         self.ddp = ddp
@@ -298,13 +317,44 @@ class BucketAdamW:
             master = flat if flat.dtype == torch.float32 else flat.float()
             self.slots.append({"bucket": span, "flat": flat, "master": master, "m": torch.zeros_like(master), "v": torch.zeros_like(master)})
         dev = ddp.params[0].device
+        self.during_backward = bool(during_backward) and dev.type == "cuda"
         if dev.type == "cuda":  # step counter and per-step constants live on the device: the step is graph-capturable
             self._step_dev = torch.zeros(1, dtype=torch.float64, device=dev)
             self._scalars_dev = torch.zeros(8, dtype=torch.float32, device=dev)
+        if self.during_backward:
+            self._slot_of = {id(s["bucket"]): s for s in self.slots}
+            self._update_stream = torch.cuda.Stream(dev)
+            self._reduce = ddp.reducer
+            self._prepare_next()  # the constants of step 1
+            ddp.reducer = self._reduce_then_update
+
+    def _prepare_next(self):
+        from ..ops.elementwise import adam_prepare
+
+        adam_prepare(self._step_dev, (self.rule.lr, self.rule.betas, self.rule.eps, self.rule.weight_decay), self._scalars_dev)
+
+    def _reduce_then_update(self, span):
+        from ..ops.elementwise import adamw_step_dev
+
+        s = self._slot_of[id(span)]
+        reduced = self._reduce(span)
+        dev = s["flat"].device
+        side = self._update_stream
+        side.wait_stream(torch.cuda.current_stream(dev))  # the gradients, and every use of these parameters in backward
+        with torch.cuda.stream(side), torch.no_grad():
+            reduced.wait()  # a stream dependency on the all-reduce
+            shadow = None if s["master"] is s["flat"] else s["flat"]
+            adamw_step_dev(s["master"], span.flat, s["m"], s["v"], self._scalars_dev, shadow)
+            done = torch.cuda.Event()
+            done.record(side)
+        return _AfterEvent(done, dev)
 
     @torch.no_grad()
     def step(self):
         self.step_count += 1.0
+        if self.during_backward:
+            self._prepare_next()  # the updates ran during backward; these are the next step's constants
+            return
         on_gpu = self.slots[0]["flat"].is_cuda
         if on_gpu:
             from ..ops.elementwise import adam_prepare, adamw_step_dev

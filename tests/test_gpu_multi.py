@@ -603,6 +603,20 @@ def test_ddp_with_the_optimizer_sharded_into_the_reduce_scatter():
     assert sharded[0][2] * 2 <= replicated[0][2] + 64  # half the optimizer state per rank
 
 
+@needs2
+def test_optimizer_during_backward_on_two_gpus():
+    """The replicated optimizer applied span by span behind each all-reduce gives what applying it after backward gives."""
+    from tandem_b200 import launch
+    from test_gpu_ops import optimizer_timing_rank
+
+    after = launch(optimizer_timing_rank, 2, False, False, device="cuda")
+    during = launch(optimizer_timing_rank, 2, True, True, device="cuda")
+    for r in range(2):
+        assert after[r][0] == during[r][0]
+        assert torch.equal(after[r][1], during[r][1])
+    assert torch.equal(during[0][1], during[1][1])
+
+
 def graphed_rank(g, strategy, graphed):
     """A sharded strategy on the hand-written kernels in bf16, stepped eagerly or replayed from one CUDA graph."""
     from tandem_b200.data import synthetic

@@ -404,3 +404,46 @@ def test_gemm_with_fused_weight_gather(n, rank):
         y = op2(x, None)
         close(y, x.float() @ w.float().t() + b2.float())
         assert torch.equal(full[before:before + N * K + N], flat[before:before + N * K + N])
+
+
+def optimizer_timing_rank(g, during_backward, graphed):
+    """DDP on the hand-written kernels in bf16 with the replicated optimizer applied after backward or span by span
+    during it; eager or replayed from a CUDA graph."""
+    from tandem_b200.data import synthetic
+    from tandem_b200.ddp import DDP, BucketAdamW
+    from tandem_b200.model import Config, GPT
+    from tandem_b200.parallel.graph import GraphedStep
+
+    torch.manual_seed(0)
+    cfg = Config(seq=128, layers=2, heads=2, dim=128, kernels="b200")
+    text = synthetic(50_000)
+    model = GPT(cfg).to(g.device).bfloat16()
+    wrapped = DDP(model, g, bucket_bytes=128 << 10, rebuild=False)
+    opt = BucketAdamW(wrapped, lr=1e-3, weight_decay=0.1, during_backward=during_backward)
+    batches = [text.batch(step, 8, cfg.seq, rank=g.rank, world=g.size, device=g.device) for step in range(8)]
+    losses = []
+    if graphed:
+        step_fn = GraphedStep(wrapped, opt, *batches[0], warmup=3)
+        for x, y in batches[3:]:
+            losses.append(step_fn(x, y).item())
+    else:
+        for k, (x, y) in enumerate([batches[0]] * 3 + batches[3:]):
+            loss = wrapped(x, y)
+            loss.backward()
+            opt.step()
+            opt.zero_grad()
+            if k >= 3:
+                losses.append(loss.item())
+    g.check()
+    return losses, torch.cat([p.detach().float().reshape(-1) for p in model.parameters()]).cpu()
+
+
+def test_optimizer_during_backward_equals_optimizer_after_backward():
+    from tandem_b200 import launch
+
+    after = launch(optimizer_timing_rank, 1, False, False, device="cuda")[0]
+    during = launch(optimizer_timing_rank, 1, True, False, device="cuda")[0]
+    replayed = launch(optimizer_timing_rank, 1, True, True, device="cuda")[0]
+    assert after[0] == during[0], (after[0], during[0])
+    assert torch.equal(after[1], during[1])  # the same arithmetic on the same gradients: bit for bit
+    assert after[0] == replayed[0] and torch.equal(after[1], replayed[1])
