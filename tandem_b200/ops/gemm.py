@@ -7,6 +7,8 @@ whose element-wise work rides in the GEMM epilogues: bias add, exact GELU
 only multiplies by it), and the residual add that follows the projection.
 The reference computes these with nn.Linear / F.gelu / `+` (tandem/model.py:36-58)."""
 
+import os
+
 import torch
 
 from ._lib import check_rc, empty_padded, lib, need_bf16, pad8, stream
@@ -95,7 +97,8 @@ def _grad_bias(dy2, ldy):
 # call, which a CUDA-graph capture records as two branches.  Everything the side stream touches is allocated on the
 # caller's stream beforehand and outlives the join, so the caching allocator's per-stream pools never see a block
 # used by a stream it does not know about.
-SIDE_BELOW_TOKENS = 4096  # with more tokens each product fills the SMs by itself and the fork only adds two event waits
+# with more tokens each product fills the SMs by itself and the fork only adds two event waits (TANDEM_SIDE_TOKENS=0: never fork)
+SIDE_BELOW_TOKENS = int(os.environ.get("TANDEM_SIDE_TOKENS", "4096"))
 _side_streams = {}
 
 
