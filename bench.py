@@ -10,7 +10,11 @@ in tokens/s, on N GPUs of one node.
                   fp32 master weights (default strategy: ddp).
 --impl reference  the unmodified reference package installed under baseline/_ref, through its own
                   launch() / DDP / model and stock fp32 code path.
---impl torch      torch DistributedDataParallel over NCCL with bf16 autocast (context only).
+--impl torch      torch DistributedDataParallel / FSDP over NCCL with bf16 autocast (context only).
+
+--strategy ddp | zero1 | zero2 | zero3 | gpipe | 1f1b and --model 85.8m | 1.3b | pp24 select the other training
+configurations of the benchmark plan (1.3B under ZeRO-3; the 24-layer model as a pipeline); analysis switches:
+--global-batch, --precision fp32 (with --kernels torch), --opt, --fused-step, --update-during-backward, --balance.
 
 Data are synthetic: token ids uniform in [0, vocab) from a seed; weights are random-init.
 The global batch is fixed, so per-GPU work shrinks as N grows ("strong" scaling).
