@@ -29,6 +29,7 @@
 // Every mbarrier wait is bounded; a wait that runs out sets a host-visible error word and the CTA
 // winds down (frees its TMEM, returns).  The reference has no GEMM of its own: its Linear layers
 // call cuBLAS through torch (tandem/model.py:36-37,53-54,75).
+#include <atomic>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -1079,14 +1080,17 @@ constexpr TileShape SHAPES[4] = {{0, 256, 256, 0.77, 5.3}, {1, 128, 256, 0.43, 0
 constexpr int MAX_SPLITS = 8;
 constexpr double START_US = 5.0, FOLD_US = 2.5, FOLD_PART_US = 1.7, FOLD_US_PER_MB = 0.3;
 
-int g_forced_tile = -1;   // 0: 256x256, 1: 128x256, 2: 128x128, 3 / 4: CTA pair 256x256 / 256x128, 5: 128x192; -1: planned
-int g_forced_splits = 0;  // > 0: that many k-parts for the tail (where the reduction is long enough); 0: planned
+// Tuning and test hooks (tb_gemm_force_tile / tb_gemm_force_splits): process-wide, read once per call into locals.
+// Atomic so that a setter racing with a launch on another thread (an autograd worker) yields one value or the other.
+std::atomic<int> g_forced_tile{-1};   // 0: 256x256, 1: 128x256, 2: 128x128, 3 / 4: CTA pair 256x256 / 256x128, 5: 128x192; -1: planned
+std::atomic<int> g_forced_splits{0};  // > 0: that many k-parts for the tail (where the reduction is long enough); 0: planned
 
 struct GemmPlan { int bm, bn, splits, whole_tiles; };
 
 GemmPlan plan_gemm(int M, int N, int K, int ctas) {
   const int k_blocks = (K + BK - 1) / BK;
-  if (g_forced_tile == 3 || g_forced_tile == 4) return {512, g_forced_tile == 3 ? 256 : 128, 1, 0};  // CTA-pair kernel (bm = 512 marks it)
+  const int forced_tile = g_forced_tile.load(std::memory_order_relaxed), forced_splits = g_forced_splits.load(std::memory_order_relaxed);
+  if (forced_tile == 3 || forced_tile == 4) return {512, forced_tile == 3 ? 256 : 128, 1, 0};  // CTA-pair kernel (bm = 512 marks it)
   auto valid_splits = [&](int s) {  // every part gets at least two k-blocks and none is empty
     const int per = (k_blocks + s - 1) / s;
     return s == 1 || (per >= 2 && (s - 1) * per < k_blocks);
@@ -1094,14 +1098,14 @@ GemmPlan plan_gemm(int M, int N, int K, int ctas) {
   GemmPlan best{128, 128, 1, 0};
   double best_us = 1e300;
   for (const TileShape& t : SHAPES) {
-    if (g_forced_tile >= 0 && g_forced_tile != t.id) continue;
-    if (g_forced_tile < 0 && t.bn > 128 && N <= 128) continue;
+    if (forced_tile >= 0 && forced_tile != t.id) continue;
+    if (forced_tile < 0 && t.bn > 128 && N <= 128) continue;
     const long long tiles = (long long)((M + t.bm - 1) / t.bm) * ((N + t.bn - 1) / t.bn);
     const long long rounds = tiles / ctas, tail = tiles % ctas;
     const double whole_us = rounds * (k_blocks * t.per_kblock + t.per_tile);
     for (int sp = 1; sp <= MAX_SPLITS; ++sp) {
       if (!valid_splits(sp) || (sp > 1 && (tail == 0 || tail * sp > ctas))) continue;
-      if (g_forced_splits > 0 && sp != g_forced_splits && tail > 0 && valid_splits(g_forced_splits) && tail * g_forced_splits <= ctas) continue;
+      if (forced_splits > 0 && sp != forced_splits && tail > 0 && valid_splits(forced_splits) && tail * forced_splits <= ctas) continue;
       double us = START_US + whole_us;
       if (tail > 0) {
         const int per = (k_blocks + sp - 1) / sp;
@@ -1245,7 +1249,7 @@ void tb_gemm_plan(int M, int N, int K, int* out4) {
 }
 
 // Pins the number of k-parts (0: planned) / the tile shape (-1: planned) for every later call.  For tuning and tests.
-void tb_gemm_force_splits(int n) { g_forced_splits = n; }
+void tb_gemm_force_splits(int n) { g_forced_splits.store(n, std::memory_order_relaxed); }
 
 // out[M, N] = A[M, K] . W[N, K]^T (+ epilogue) where W is gathered by the kernel itself: rank q's shard (peer
 // address shards[q]) holds bytes [shard_lo[q], shard_hi[q]) of the unit's flat buffer; W is the byte range
@@ -1312,7 +1316,7 @@ int tb_gemm_gathered(const void* A, void* out, int M, int N, int K, int lda, int
   return (int)cudaLaunchCooperativeKernel(kernel, dim3(ctas), dim3(448), params, smem, stream);
 }
 
-void tb_gemm_force_tile(int which) { g_forced_tile = which; }
+void tb_gemm_force_tile(int which) { g_forced_tile.store(which, std::memory_order_relaxed); }
 
 // 1 (default): bf16 outputs leave through TMA stores; 0: the epilogue warps store them.  For measurements.
 void tb_gemm_tma_store(int on) { g_tma_store_enabled = on; }

@@ -39,6 +39,16 @@ def no_gemm_timeouts():
     assert not gemm_error(), "a GEMM wait ran out"
 
 
+@pytest.fixture(autouse=True)
+def planner_left_alone():
+    """Whatever a test pins (tile shape, number of k-parts) is unpinned again when it ends, also when it fails."""
+    yield
+    from tandem_b200.ops._lib import lib
+
+    lib().tb_gemm_force_tile(-1)
+    lib().tb_gemm_force_splits(0)
+
+
 @pytest.fixture
 def force_tile():
     """Pins the GEMM's tile shape (0: 256x256, 1: 128x256, 2: 128x128, 3/4: CTA-pair 256x256 / 256x128, 5: 128x192) for one test."""
