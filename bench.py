@@ -456,7 +456,7 @@ def run_reference(args):
             return
         sys.path.insert(0, ref)
         os.environ["PYTHONPATH"] = ref + os.pathsep + ROOT + os.pathsep + os.environ.get("PYTHONPATH", "")
-        os.environ.setdefault("TANDEM_TIMEOUT", "180")  # the reference's own limit on its waits: a stuck engine ends in its CommError
+        os.environ.setdefault("TANDEM_TIMEOUT", "120")  # the reference's own limit on its waits: a stuck engine ends in its CommError
         import tandem
 
         # "auto": the reference's C++ engine (its faster one, selected with backend="cpp" and built by the reference
