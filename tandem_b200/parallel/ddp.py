@@ -297,8 +297,8 @@ class BucketAdamW:
 
     Create it once the span layout is final: pass rebuild=False to DDP, or create it after the first backward.
 
-    during_backward (GPU ranks): a span is updated as soon as its all-reduce has finished, on a stream of its own
-    beside the rest of backward, instead of all spans after backward (the update streams through HBM while the
+    during_backward: a span is updated as soon as its all-reduce has finished (on GPU ranks on a stream of its own
+    beside the rest of backward) instead of all spans after backward (the update streams through HBM while the
     remaining backward GEMMs keep the tensor pipes busy; nothing in backward reads a parameter again once its
     gradient is complete).  `step()` then only closes the step.  As with the sharded form, every backward that
     reduces also updates: accumulate over several backward passes under `no_sync()`.
@@ -317,15 +317,17 @@ class BucketAdamW:
             master = flat if flat.dtype == torch.float32 else flat.float()
             self.slots.append({"bucket": span, "flat": flat, "master": master, "m": torch.zeros_like(master), "v": torch.zeros_like(master)})
         dev = ddp.params[0].device
-        self.during_backward = bool(during_backward) and dev.type == "cuda"
-        if dev.type == "cuda":  # step counter and per-step constants live on the device: the step is graph-capturable
+        self.during_backward = bool(during_backward)
+        self._on_gpu = dev.type == "cuda"
+        if self._on_gpu:  # step counter and per-step constants live on the device: the step is graph-capturable
             self._step_dev = torch.zeros(1, dtype=torch.float64, device=dev)
             self._scalars_dev = torch.zeros(8, dtype=torch.float32, device=dev)
         if self.during_backward:
             self._slot_of = {id(s["bucket"]): s for s in self.slots}
-            self._update_stream = torch.cuda.Stream(dev)
             self._reduce = ddp.reducer
-            self._prepare_next()  # the constants of step 1
+            if self._on_gpu:
+                self._update_stream = torch.cuda.Stream(dev)
+                self._prepare_next()  # the constants of step 1
             ddp.reducer = self._reduce_then_update
 
     def _prepare_next(self):
@@ -338,6 +340,13 @@ class BucketAdamW:
 
         s = self._slot_of[id(span)]
         reduced = self._reduce(span)
+        if not self._on_gpu:  # CPU ranks: the same order of events, with torch's operation sequence
+            reduced.wait()
+            shadow = None if s["master"] is s["flat"] else s["flat"]
+            with torch.no_grad():
+                self.rule.state["b"] = [self.step_count, s["m"], s["v"]]
+                self.rule.update("b", s["master"], span.flat.float(), shadow)
+            return reduced
         dev = s["flat"].device
         side = self._update_stream
         side.wait_stream(torch.cuda.current_stream(dev))  # the gradients, and every use of these parameters in backward
@@ -353,7 +362,8 @@ class BucketAdamW:
     def step(self):
         self.step_count += 1.0
         if self.during_backward:
-            self._prepare_next()  # the updates ran during backward; these are the next step's constants
+            if self._on_gpu:
+                self._prepare_next()  # the updates ran during backward; these are the next step's constants
             return
         on_gpu = self.slots[0]["flat"].is_cuda
         if on_gpu:

@@ -111,6 +111,37 @@ def test_bucket_adamw_equals_per_parameter_adamw():
     assert launch(bucket_optimizer_rank, 2) == [True, True]
 
 
+def eager_update_rank(group):
+    """BucketAdamW updating each span right behind its all-reduce, during backward, against the same optimizer
+    stepping after backward; also under gradient accumulation with no_sync()."""
+    from tandem_b200.ddp import BucketAdamW
+
+    during, after = seeded_model(), seeded_model()
+    wrap_a = DDP(during, group, bucket_bytes=64 << 10, rebuild=False)
+    opt_a = BucketAdamW(wrap_a, lr=LEARNING_RATE, weight_decay=WEIGHT_DECAY, during_backward=True)
+    wrap_b = DDP(after, group, bucket_bytes=64 << 10, rebuild=False)
+    opt_b = BucketAdamW(wrap_b, lr=LEARNING_RATE, weight_decay=WEIGHT_DECAY)
+    batches = Batches(group.rank, group.size)
+    for k in range(4):
+        losses = []
+        for wrapper, opt in ((wrap_a, opt_a), (wrap_b, opt_b)):
+            with wrapper.no_sync():  # the first of two backward passes only accumulates: no update may happen here
+                before = flat_weights(wrapper.module.parameters()).clone()
+                wrapper(*batches(2 * k)).backward()
+                assert torch.equal(flat_weights(wrapper.module.parameters()), before)
+            loss = wrapper(*batches(2 * k + 1))
+            loss.backward()
+            opt.step()
+            opt.zero_grad()
+            losses.append(loss.item())
+        assert losses[0] == losses[1], k
+    return torch.equal(flat_weights(during.parameters()), flat_weights(after.parameters()))
+
+
+def test_bucket_adamw_during_backward_equals_after_backward():
+    assert launch(eager_update_rank, 2) == [True, True]
+
+
 def sharded_optimizer_rank(group):
     """ShardedBucketAdamW (reduce-scatter, update of the owned chunk, all-gather, all during backward) against
     torch's per-parameter AdamW behind a plain DDP wrapper on a twin model fed the same batches."""
