@@ -33,7 +33,7 @@ def _repack(t2):
 def gemm(a, b, M, N, K, lda, ldb, a_mn, b_mn, flags=0, bias=None, aux_in=None, aux_out=None, out=None, out_dtype=torch.bfloat16,
          workspace=None):
     """out[M, N] = op(a) . op(b) (+ epilogue).  Returns a [M, N] view with a 16-byte-aligned row stride.
-    workspace: a uint8 tensor of at least gemm_workspace(M, N, K) bytes, for callers that launch on another stream
+    workspace: a uint8 tensor of at least lib().tb_gemm_workspace_bytes(M, N, K) bytes, for callers that launch on another stream
     than the one their memory belongs to (else it is allocated here)."""
     if out is None:
         out = empty_padded(M, N, out_dtype, a.device)
