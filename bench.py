@@ -460,8 +460,11 @@ def run_reference(args):
         import tandem
 
         # "auto": the reference's C++ engine (its faster one, selected with backend="cpp" and built by the reference
-        # itself on first use) when there is communication to do, its Python engine if that build or run fails.
-        engines = {"auto": ["cpp", "python"] if args.gpus > 1 else ["python"], "cpp": ["cpp"], "python": ["python"]}[args.ref_backend]
+        # itself on first use) where it has been seen to run clean on this hardware -- 2 GPUs, the group size its own
+        # benchmarks use -- with its Python engine as the fall-back; its Python engine at the other sizes (measured at
+        # 1, 2, 4 and 8 GPUs).  Its C++ engine waits on interprocess CUDA events without a limit, so a stall at a
+        # size it was never run at would not end in an error that a fall-back could catch.
+        engines = {"auto": ["cpp", "python"] if args.gpus == 2 else ["python"], "cpp": ["cpp"], "python": ["python"]}[args.ref_backend]
         out, engine, notes = None, None, []
         for engine in engines:
             try:
@@ -495,7 +498,7 @@ def main():
                     help="85.8m: the flagship; 1.3b: the ZeRO-3 configuration; pp24: the 24-layer pipeline configuration")
     ap.add_argument("--kernels", default=os.environ.get("TANDEM_BENCH_KERNELS", "b200"), choices=["torch", "b200"])
     ap.add_argument("--ref-backend", default=os.environ.get("TANDEM_REF_BACKEND", "auto"), choices=["auto", "python", "cpp"],
-                    help="the reference's engine: its Python engine, its C++ engine, or auto (C++ with a fall-back to Python)")
+                    help="the reference's engine: its Python engine, its C++ engine, or auto (C++ at 2 GPUs with a fall-back to Python; Python elsewhere)")
     ap.add_argument("--opt", default="auto", choices=["auto", "replicated", "sharded"],
                     help="ddp: AdamW replicated on every rank, or sharded and fused into the gradient reduce-scatter (auto: replicated)")
     ap.add_argument("--update-during-backward", type=int, default=1, help="ddp, replicated optimizer: update each span right after its all-reduce (1) or all spans after backward (0)")
