@@ -194,6 +194,8 @@ def load_optimizer_state(wrapped, opt, state):
         opt._step_dev.fill_(opt.step_count)
         if sharded:
             opt._prepare()  # the sharded optimizer keeps the NEXT step's constants ready on the device
+        elif getattr(opt, "during_backward", False):
+            opt._prepare_next()  # so does the replicated one when it updates during backward
     for s in opt.slots:
         span = s["bucket"]
         if sharded:
