@@ -31,6 +31,12 @@ def build(g, strategy, dtype=torch.float32):
         w = DDP(model, g, bucket_bytes=32 << 10, rebuild=False)
         opt = ShardedBucketAdamW(w, lr=3e-3, weight_decay=0.1)
         return w, opt, lambda: (opt.step(), opt.zero_grad())
+    if strategy in ("ddp-bucket-adamw", "ddp-bucket-adamw-during-backward"):
+        from tandem_b200.ddp import BucketAdamW
+
+        w = DDP(model, g, bucket_bytes=32 << 10, rebuild=False)
+        opt = BucketAdamW(w, lr=3e-3, weight_decay=0.1, during_backward=strategy.endswith("during-backward"))
+        return w, opt, lambda: (opt.step(), opt.zero_grad())
     opt = ShardedAdamW(lr=3e-3, weight_decay=0.1)
     w = ZeRO(model, g, int(strategy[-1]), opt, 8 << 10) if strategy != "zero3" else FSDP(model, g, opt)
     return w, opt, lambda: (w.step(), w.zero_grad())
@@ -70,7 +76,7 @@ def resume(g, strategy, path, dtype=torch.float32, stale_steps=0):
     return more, weights(w)
 
 
-@pytest.mark.parametrize("strategy", ["ddp", "ddp-sharded-adamw", "zero1", "zero2", "zero3"])
+@pytest.mark.parametrize("strategy", ["ddp", "ddp-sharded-adamw", "ddp-bucket-adamw", "ddp-bucket-adamw-during-backward", "zero1", "zero2", "zero3"])
 def test_resume_is_bit_identical(strategy):
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "ck.pt")
